@@ -1,0 +1,76 @@
+"""ctypes binding of ``libglmssd_attn.so`` (the C ABI declared in ``include/glmssd_attn.h``).
+
+There is no fallback: if the library is missing or an entry point is absent the import fails."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+i32, i64, f32, vp = C.c_int, C.c_int64, C.c_float, C.c_void_p
+
+
+class DecodeArgs(C.Structure):
+    """Mirror of ``struct gs_mla_decode_args``."""
+    _fields_ = [
+        ("q", vp), ("cache", vp), ("cache_rows", i64), ("seq_lens", vp), ("seq_base", vp), ("page_table", vp),
+        ("page_table_stride", C.c_int32), ("page_rows", C.c_int32), ("scale", f32), ("tail_causal", C.c_int32),
+        ("o", vp), ("part_out", vp), ("workspace", vp), ("workspace_bytes", i64),
+        ("n_seq", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("d_qk", C.c_int32), ("d_v", C.c_int32),
+        ("max_seq_len", C.c_int32), ("impl", C.c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/glmssd_attn.h declares
+SIGNATURES = {
+    "gs_mla_attn": (i32, [vp, vp, vp, vp, i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]),
+    "gs_f32_to_f16": (i32, [vp, vp, i64, vp]),
+    "gs_mla_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
+    "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
+    "gs_mla_combine_parts": (i32, [vp, i32, i64, i32, i32, vp, vp]),
+    "gs_prefill_attn": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]),
+    "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),
+    "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "gs_rope_f16_inplace": (i32, [vp, i32, i32, i32, i32, i64, f32, vp]),
+    "gs_attn_last_error_string": (C.c_char_p, []),
+    "gs_attn_version": (C.c_char_p, []),
+    "gs_mla_decode_status": (i32, [vp, C.POINTER(C.c_int32), vp]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python {os.path.join(HERE, 'build.py')}` "
+                          "(there is no fallback implementation)")
+    L = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)  # AttributeError if the export is missing
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+class GsError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        msg = load().gs_attn_last_error_string().decode(errors="replace")
+        super().__init__(f"{where} failed with cudaError {code}: {msg}")
+        self.code = code
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise GsError(code, where)

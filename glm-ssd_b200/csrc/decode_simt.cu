@@ -1,0 +1,346 @@
+// CUDA-core split-KV decode ("gather" kernel) and the partial combine.
+//
+// This kernel takes any addressing (explicit position lists as in the reference ABI, dense ranges,
+// paged), any head count, f32 or f16 queries and any number of query tokens.  It is the path for
+// shapes the tcgen05 kernel does not cover (position lists, f32 queries, T > 2) and the second
+// opinion the tcgen05 kernel is tested against; it is not the fast path.
+//
+// Arithmetic follows the reference kernel's contract (crates/cuda/kernels/ops.cu:420-424):
+//   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
+// with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
+#include "internal.cuh"
+
+namespace gs {
+
+namespace {
+
+constexpr int KT = 16;   // keys per shared-memory tile
+constexpr int HG = 32;   // heads per CTA
+constexpr int NT = 256;  // threads per CTA
+
+struct SimtParams {
+    const void *q;
+    const __half *cache;
+    const int32_t *seq_lens, *seq_base, *page_table, *sel;
+    int page_table_stride, page_rows, sel_stride;
+    float scale;
+    int tail_causal;
+    float *ws_acc, *ws_ml;
+    int T, H, d_qk, d_v, splits;
+};
+
+template <typename QT>
+__global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
+    const int split = blockIdx.x, hg = blockIdx.y, bt = blockIdx.z;
+    const int b = bt / P.T, t = bt % P.T;
+    const int h0 = hg * HG;
+    const int nh = min(HG, P.H - h0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int d_qk = P.d_qk, d_v = P.d_v;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *sq = reinterpret_cast<float *>(smem_raw);             // [HG][d_qk]
+    __half *tile = reinterpret_cast<__half *>(sq + HG * d_qk);   // [KT][d_qk]
+    float *sp = reinterpret_cast<float *>(tile + KT * d_qk);     // [HG][KT]
+    float *s_m = sp + HG * KT, *s_l = s_m + HG, *s_f = s_l + HG;  // [HG] each
+
+    // attended rows of this (sequence, token)
+    RowMap rows;
+    int n;
+    if (P.sel) {
+        rows = RowMap{P.sel + (int64_t) t * P.sel_stride, nullptr, 0, 1};
+        n = P.seq_lens[t];
+    } else {
+        const int len = P.seq_lens[b];
+        n = P.tail_causal ? len - (P.T - 1 - t) : len;
+        rows = RowMap{nullptr, P.page_table ? P.page_table + (int64_t) b * P.page_table_stride : nullptr,
+                      P.seq_base ? (int64_t) P.seq_base[b] : 0, P.page_rows};
+    }
+    n = max(n, 0);
+    const int per = (n + P.splits - 1) / P.splits;
+    const int s0 = min(n, split * per), s1 = min(n, s0 + per);
+
+    const QT *qg = reinterpret_cast<const QT *>(P.q) + ((int64_t) bt * P.H + h0) * d_qk;
+    for (int i = tid; i < nh * d_qk; i += NT) sq[i] = (float) qg[i];
+    for (int i = nh * d_qk + tid; i < HG * d_qk; i += NT) sq[i] = 0.f;
+    if (tid < HG) {
+        s_m[tid] = -INFINITY;
+        s_l[tid] = 0.f;
+    }
+    float acc[HG][2];
+#pragma unroll
+    for (int h = 0; h < HG; h++) acc[h][0] = acc[h][1] = 0.f;
+    __syncthreads();
+
+    const int vec_per_row = d_qk / 8;
+    for (int kb = s0; kb < s1; kb += KT) {
+        const int nk = min(KT, s1 - kb);
+        for (int i = tid; i < KT * vec_per_row; i += NT) {
+            const int kk = i / vec_per_row, c = i % vec_per_row;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (kk < nk) val = reinterpret_cast<const uint4 *>(P.cache + rows(kb + kk) * d_qk)[c];
+            reinterpret_cast<uint4 *>(tile + kk * d_qk)[c] = val;
+        }
+        __syncthreads();
+        // scores: each warp takes two keys, every lane a strided slice of the row
+        for (int kk = warp * 2; kk < warp * 2 + 2; kk++) {
+            float d[HG];
+#pragma unroll
+            for (int h = 0; h < HG; h++) d[h] = 0.f;
+            const __half2 *krow = reinterpret_cast<const __half2 *>(tile + kk * d_qk);
+            for (int r2 = lane; r2 < d_qk / 2; r2 += 32) {
+                const float2 kf = __half22float2(krow[r2]);
+#pragma unroll
+                for (int h = 0; h < HG; h++) {
+                    const float2 qf = reinterpret_cast<const float2 *>(sq + h * d_qk)[r2];
+                    d[h] = fmaf(qf.x, kf.x, fmaf(qf.y, kf.y, d[h]));
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < HG; h++) {
+                const float v = warp_sum(d[h]);
+                if (lane == h) sp[h * KT + kk] = kk < nk ? v * P.scale : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // online softmax: one warp per head, lanes over the tile's keys
+        for (int h = warp; h < nh; h += NT / 32) {
+            const float s = lane < KT ? sp[h * KT + lane] : -INFINITY;
+            const float m_old = s_m[h];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            const float p = s == -INFINITY ? 0.f : expf(s - m_new);
+            const float psum = warp_sum(p);
+            if (lane < KT) sp[h * KT + lane] = p;
+            if (lane == 0) {
+                const float f = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                s_f[h] = f;
+                s_l[h] = s_l[h] * f + psum;
+                s_m[h] = m_new;
+            }
+        }
+        __syncthreads();
+        // PV: thread owns value columns tid and tid + 256
+        {
+            float v0[KT], v1[KT];
+#pragma unroll
+            for (int k = 0; k < KT; k++) {
+                v0[k] = tid < d_v ? __half2float(tile[k * d_qk + tid]) : 0.f;
+                v1[k] = tid + NT < d_v ? __half2float(tile[k * d_qk + tid + NT]) : 0.f;
+            }
+#pragma unroll
+            for (int h = 0; h < HG; h++) {
+                if (h < nh) {
+                    const float f = s_f[h];
+                    float a0 = acc[h][0] * f, a1 = acc[h][1] * f;
+#pragma unroll
+                    for (int k = 0; k < KT; k++) {
+                        const float p = sp[h * KT + k];
+                        a0 = fmaf(p, v0[k], a0);
+                        a1 = fmaf(p, v1[k], a1);
+                    }
+                    acc[h][0] = a0;
+                    acc[h][1] = a1;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // one (acc, m, l) record per (sequence, token, split, head)
+    const int64_t seg = (int64_t) bt * P.splits + split;
+#pragma unroll
+    for (int h = 0; h < HG; h++) {
+        if (h < nh) {
+            float *dst = P.ws_acc + (seg * P.H + h0 + h) * d_v;
+            if (tid < d_v) dst[tid] = acc[h][0];
+            if (tid + NT < d_v) dst[tid + NT] = acc[h][1];
+        }
+    }
+    if (tid < nh) {
+        float *ml = P.ws_ml + (seg * P.H + h0 + tid) * 2;
+        ml[0] = s_m[tid];
+        ml[1] = s_l[tid];
+    }
+}
+
+// ---- combine --------------------------------------------------------------------------------------
+// One CTA per (output row, 128-column chunk); 32 column quads x 8 segment lanes.
+constexpr int CB_COLS = 128;
+constexpr int CB_LANES = 8;
+constexpr int CB_NT = (CB_COLS / 4) * CB_LANES;  // 256
+constexpr int CB_MAX_SEG = 1024;
+
+__global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
+    const int row = blockIdx.x;  // (b, t, h)
+    const int col0 = blockIdx.y * CB_COLS;
+    const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
+    int first, nseg, row_in_seg;
+    if (C.desc) {
+        const int2 d = C.desc[b];
+        first = d.x;
+        nseg = d.y;
+        row_in_seg = t * C.H + h;
+    } else {
+        first = (b * C.T + t) * C.regular_segments;
+        nseg = C.regular_segments;
+        row_in_seg = h;
+    }
+    nseg = min(nseg, CB_MAX_SEG);
+    __shared__ float s_w[CB_MAX_SEG];
+    __shared__ float s_red[CB_NT / 32];
+    __shared__ float s_M, s_L;
+    __shared__ float4 s_part[CB_LANES][CB_COLS / 4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // pass 1: M = max m_s
+    float mx = -INFINITY;
+    for (int s = tid; s < nseg; s += CB_NT) mx = fmaxf(mx, C.ml[(int64_t) (first + s) * C.seg_stride_ml + row_in_seg * 2]);
+    mx = warp_max(mx);
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    if (tid == 0) {
+        float m = -INFINITY;
+        for (int w = 0; w < CB_NT / 32; w++) m = fmaxf(m, s_red[w]);
+        s_M = m;
+    }
+    __syncthreads();
+    const float M = s_M;
+    // pass 2: weights and L
+    float lsum = 0.f;
+    for (int s = tid; s < nseg; s += CB_NT) {
+        const float *ml = C.ml + (int64_t) (first + s) * C.seg_stride_ml + row_in_seg * 2;
+        const float m = ml[0];
+        const float w = m == -INFINITY ? 0.f : expf(m - M);
+        s_w[s] = w;
+        lsum += ml[1] * w;
+    }
+    lsum = warp_sum(lsum);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = lsum;
+    __syncthreads();
+    if (tid == 0) {
+        float l = 0.f;
+        for (int w = 0; w < CB_NT / 32; w++) l += s_red[w];
+        s_L = l;
+    }
+    __syncthreads();
+    const float L = s_L;
+    // pass 3: weighted sum of the accumulators
+    const int quad = tid % (CB_COLS / 4), sl = tid / (CB_COLS / 4);
+    const int col = col0 + quad * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < C.d_v) {
+        for (int s = sl; s < nseg; s += CB_LANES) {
+            const float w = s_w[s];
+            if (w != 0.f) {
+                const float4 v = *reinterpret_cast<const float4 *>(
+                    C.acc + (int64_t) (first + s) * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col);
+                a.x = fmaf(v.x, w, a.x);
+                a.y = fmaf(v.y, w, a.y);
+                a.z = fmaf(v.z, w, a.z);
+                a.w = fmaf(v.w, w, a.w);
+            }
+        }
+    }
+    s_part[sl][quad] = a;
+    __syncthreads();
+    if (sl == 0 && col < C.d_v) {
+#pragma unroll
+        for (int j = 1; j < CB_LANES; j++) {
+            const float4 v = s_part[j][quad];
+            a.x += v.x;
+            a.y += v.y;
+            a.z += v.z;
+            a.w += v.w;
+        }
+        if (C.part_out) {
+            const int64_t rows_total = (int64_t) C.n_seq * C.T * C.H;
+            *reinterpret_cast<float4 *>(C.part_out + (int64_t) row * C.d_v + col) = a;
+            if (blockIdx.y == 0 && quad == 0) {
+                C.part_out[rows_total * C.d_v + (int64_t) row * 2] = M;
+                C.part_out[rows_total * C.d_v + (int64_t) row * 2 + 1] = L;
+            }
+        }
+        if (C.o) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            *reinterpret_cast<float4 *>(C.o + (int64_t) row * C.d_v + col) =
+                make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
+    }
+}
+
+}  // namespace
+
+int launch_combine(const CombinePlan &c, cudaStream_t st) {
+    const int rows = c.n_seq * c.T * c.H;
+    if (rows <= 0) return 0;
+    if (c.d_v % 4 != 0) return fail_invalid("combine: d_v must be a multiple of 4");
+    dim3 grid(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
+    k_combine<<<grid, CB_NT, 0, st>>>(c);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
+    if (p.d_qk % 8 != 0 || p.d_qk > 576 || p.d_v > 512 || p.d_v > p.d_qk || p.d_v % 4 != 0)
+        return fail_invalid("decode: need d_qk % 8 == 0, d_qk <= 576, d_v <= min(512, d_qk), d_v % 4 == 0");
+    const int groups = p.n_seq * p.T;
+    if (groups <= 0 || p.H <= 0) return 0;
+    const int n_hg = (p.H + HG - 1) / HG;
+    int splits = p.splits;
+    if (splits <= 0) {
+        // enough CTAs for two waves, but no split shorter than four tiles of the longest sequence
+        const int want = (2 * p.sm_count + groups * n_hg - 1) / (groups * n_hg);
+        const int max_len = p.max_seq_len > 0 ? p.max_seq_len : (int) (p.cache_rows > (1 << 30) ? (1 << 30) : p.cache_rows);
+        const int by_len = (max_len + 4 * KT - 1) / (4 * KT);
+        splits = want < by_len ? want : by_len;
+        if (splits < 1) splits = 1;
+        if (splits > kSimtMaxSplits) splits = kSimtMaxSplits;
+    }
+    if ((int64_t) groups * splits > p.max_segments) return fail_invalid("decode: workspace too small for the splits");
+    SimtParams P;
+    P.q = p.q;
+    P.cache = p.cache;
+    P.seq_lens = p.seq_lens;
+    P.seq_base = p.seq_base;
+    P.page_table = p.page_table;
+    P.sel = p.sel;
+    P.page_table_stride = p.page_table_stride;
+    P.page_rows = p.page_rows > 0 ? p.page_rows : 1;
+    P.sel_stride = p.sel_stride;
+    P.scale = p.scale;
+    P.tail_causal = p.tail_causal;
+    P.ws_acc = p.ws_acc;
+    P.ws_ml = p.ws_ml;
+    P.T = p.T;
+    P.H = p.H;
+    P.d_qk = p.d_qk;
+    P.d_v = p.d_v;
+    P.splits = splits;
+    const size_t smem = (size_t) HG * p.d_qk * 4 + (size_t) KT * p.d_qk * 2 + (size_t) HG * KT * 4 + 3 * HG * 4;
+    dim3 grid(splits, n_hg, groups);
+    // attributes are set on every call: a cached flag would go stale across a device reset
+    if (p.q_is_f32) {
+        GS_TRY(cudaFuncSetAttribute(k_decode_gather<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        k_decode_gather<float><<<grid, NT, smem, st>>>(P);
+    } else {
+        GS_TRY(cudaFuncSetAttribute(k_decode_gather<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        k_decode_gather<__half><<<grid, NT, smem, st>>>(P);
+    }
+    GS_TRY(cudaGetLastError());
+    CombinePlan c;
+    c.acc = p.ws_acc;
+    c.ml = p.ws_ml;
+    c.desc = nullptr;
+    c.regular_segments = splits;
+    c.seg_stride_acc = (int64_t) p.H * p.d_v;
+    c.seg_stride_ml = (int64_t) p.H * 2;
+    c.n_seq = p.n_seq;
+    c.T = p.T;
+    c.H = p.H;
+    c.d_v = p.d_v;
+    c.o = p.o;
+    c.part_out = p.part_out;
+    return launch_combine(c, st);
+}
+
+}  // namespace gs

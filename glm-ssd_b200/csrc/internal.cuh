@@ -1,0 +1,59 @@
+// Internal launch interfaces between the translation units of the attention library.
+#pragma once
+#include "common.cuh"
+
+namespace gs {
+
+// A decode call with every argument resolved (see gs_mla_decode_args for the meaning).
+struct DecodeProblem {
+    const void *q;        // f16, or f32 when q_is_f32
+    bool q_is_f32;
+    const __half *cache;
+    int64_t cache_rows;
+    const int32_t *seq_lens;
+    const int32_t *seq_base;
+    const int32_t *page_table;
+    int page_table_stride, page_rows;
+    const int32_t *sel;   // legacy explicit position lists [T][sel_stride] (n_seq == 1), lengths in seq_lens[T]
+    int sel_stride;
+    float scale;
+    int tail_causal;
+    float *o;
+    float *part_out;
+    // workspace pieces
+    int32_t *status;
+    float *ws_acc;
+    float *ws_ml;
+    int2 *ws_desc;        // per-sequence (first_segment, n_segments), written by the tcgen05 kernel
+    int64_t max_segments;
+    int n_seq, T, H, d_qk, d_v;
+    int max_seq_len;
+    int splits;           // CUDA-core kernel: splits per (sequence, token); 0 = choose
+    int sm_count;
+};
+
+// Combine descriptor: how the segments of an output row are found.
+struct CombinePlan {
+    const float *acc;      // segment s, row r of the segment: acc + s*seg_stride_acc + r*d_v
+    const float *ml;       // segment s, row r of the segment: ml + s*seg_stride_ml + r*2
+    const int2 *desc;      // per sequence (first_segment, n_segments), or nullptr => regular
+    int regular_segments;  // desc == nullptr: segments per (sequence, token) group, consecutive
+    int64_t seg_stride_acc;  // floats between the accumulator blocks of consecutive segments
+    int64_t seg_stride_ml;   // floats between the (m, l) blocks of consecutive segments
+    int n_seq, T, H, d_v;
+    float *o;              // may be nullptr
+    float *part_out;       // may be nullptr
+};
+
+int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
+int launch_combine(const CombinePlan &c, cudaStream_t st);
+bool decode_umma_supported(const DecodeProblem &p, const char **why);
+int launch_decode_umma(const DecodeProblem &p, cudaStream_t st);
+
+int launch_prefill_simt(const __half *q, const __half *k, const __half *v, void *o, int o_f16, int S, int H, int d,
+                        int p0, float scale, cudaStream_t st);
+bool prefill_umma_supported(int S, int H, int d, int p0, const char **why);
+int launch_prefill_umma(const __half *q, const __half *k, const __half *v, void *o, int o_f16, int S, int H, int d,
+                        int p0, float scale, cudaStream_t st);
+
+}  // namespace gs

@@ -1,0 +1,186 @@
+// Fused RoPE + KV-append, plain append, and in-place RoPE for prefill inputs.
+//
+// The reference appends the new latent rows with a bare f32 -> f16 conversion
+// (crates/cuda/kernels/gemm.cu:155-163, called from crates/engine/src/forward.rs:857-860).  The fused
+// kernel does the same rounding and, for cache rows that carry a rotary part, rotates the last d_rope
+// columns at the row's absolute position in the same pass, so the rotated f32 row never exists in
+// memory.  Convention: adjacent pairs (2i, 2i+1), angle = pos * base^(-2i/d_rope); the inverse
+// frequencies are computed on the host in double and rounded to f32, cos/sin are the full-range
+// f32 functions (this file must not be built with fast-math).
+#include <math.h>
+
+#include "internal.cuh"
+
+namespace gs {
+namespace {
+
+constexpr int ROPE_MAX_PAIRS = 64;
+struct RopeTable {
+    float inv_freq[ROPE_MAX_PAIRS];
+};
+
+static void fill_table(RopeTable &t, int d_rope, float base) {
+    for (int i = 0; i < d_rope / 2; i++) t.inv_freq[i] = (float) pow((double) base, -2.0 * i / (double) d_rope);
+}
+
+// Separately rounded products (no fused multiply-add) so the result matches a plain C evaluation.
+__device__ __forceinline__ float2 rotate(float2 v, float cs, float sn) {
+    return make_float2(__fsub_rn(__fmul_rn(v.x, cs), __fmul_rn(v.y, sn)), __fadd_rn(__fmul_rn(v.x, sn), __fmul_rn(v.y, cs)));
+}
+
+__global__ void k_f32_to_f16_scalar(const float *__restrict__ x, __half *__restrict__ y, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __float2half_rn(x[i]);
+}
+
+__global__ void k_f32_to_f16_rows(const float *__restrict__ x, __half *__restrict__ y, int64_t n) {
+    // two values per thread, 4-byte stores
+    const int64_t i = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i + 1 < n) {
+        const float2 v = *reinterpret_cast<const float2 *>(x + i);
+        *reinterpret_cast<__half2 *>(y + i) = __floats2half2_rn(v.x, v.y);
+    } else if (i < n) {
+        y[i] = __float2half_rn(x[i]);
+    }
+}
+
+struct AppendParams {
+    const float *kv;
+    __half *cache;
+    const int32_t *pos0, *seq_base, *page_table;
+    int64_t pos0_host;
+    int page_table_stride, page_rows;
+    int T, d_row, d_rope;
+    RopeTable tab;
+};
+
+// grid (T, n_seq); thread j handles column pair (2j, 2j+1)
+__global__ void k_rope_append(const AppendParams P) {
+    const int t = blockIdx.x, b = blockIdx.y;
+    const int64_t pos = (P.pos0 ? (int64_t) P.pos0[b] : P.pos0_host) + t;
+    int64_t row;
+    if (P.page_table) {
+        row = (int64_t) P.page_table[(int64_t) b * P.page_table_stride + pos / P.page_rows] * P.page_rows +
+              pos % P.page_rows;
+    } else if (P.pos0) {
+        row = (P.seq_base ? (int64_t) P.seq_base[b] : 0) + pos;
+    } else {
+        row = t;  // host-position form: `cache` already points at the first new row
+    }
+    const float *src = P.kv + ((int64_t) b * P.T + t) * P.d_row;
+    __half *dst = P.cache + row * P.d_row;
+    const int d0 = P.d_row - P.d_rope;
+    for (int j = threadIdx.x; j < P.d_row / 2; j += blockDim.x) {
+        const int c = 2 * j;
+        float2 v = *reinterpret_cast<const float2 *>(src + c);
+        if (c >= d0) {
+            const float ang = (float) pos * P.tab.inv_freq[(c - d0) >> 1];
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            v = rotate(v, cs, sn);
+        }
+        *reinterpret_cast<__half2 *>(dst + c) = __floats2half2_rn(v.x, v.y);
+    }
+}
+
+// x f16 [S][H][d]: rotate the last d_rope columns of every head in place
+__global__ void k_rope_f16(__half *x, int64_t n_pairs, int H, int d, int d_rope, int64_t pos0, const RopeTable tab) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int ppr = d_rope / 2;
+    const int pair = (int) (i % ppr);
+    const int64_t sh = i / ppr;  // s * H + h
+    const int64_t s = sh / H;
+    __half2 *p = reinterpret_cast<__half2 *>(x + sh * d + (d - d_rope)) + pair;
+    const float2 v = __half22float2(*p);
+    const float ang = (float) (pos0 + s) * tab.inv_freq[pair];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    const float2 r = rotate(v, cs, sn);
+    *p = __floats2half2_rn(r.x, r.y);
+}
+
+int check_rope(int d_row, int d_rope) {
+    if (d_row <= 0 || d_row % 2 != 0) return fail_invalid("append: d_row must be positive and even");
+    if (d_rope < 0 || d_rope % 2 != 0 || d_rope > d_row || d_rope / 2 > ROPE_MAX_PAIRS)
+        return fail_invalid("append: d_rope must be even, <= d_row and <= 128");
+    return 0;
+}
+
+}  // namespace
+}  // namespace gs
+
+using namespace gs;
+
+GS_EXPORT int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream) {
+    if (n <= 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(y) & 3)) {
+        // odd alignment: one value per thread
+        k_f32_to_f16_scalar<<<(unsigned) ((n + 255) / 256), 256, 0, (cudaStream_t) stream>>>(x, (__half *) y, n);
+        GS_TRY(cudaGetLastError());
+        return 0;
+    }
+    const int64_t pairs = (n + 1) / 2;
+    k_f32_to_f16_rows<<<(unsigned) ((pairs + 255) / 256), 256, 0, (cudaStream_t) stream>>>(x, (__half *) y, n);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_rope_kv_append_at(const float *kv, void *cache_row0, int64_t pos0, int T, int d_row, int d_rope,
+                                   float rope_base, void *stream) {
+    if (int e = check_rope(d_row, d_rope)) return e;
+    if (T <= 0) return 0;
+    if (pos0 < 0) return fail_invalid("append: pos0 < 0");
+    AppendParams P{};
+    P.kv = kv;
+    P.cache = (__half *) cache_row0;
+    P.pos0 = nullptr;
+    P.pos0_host = pos0;
+    P.page_rows = 1;
+    P.T = T;
+    P.d_row = d_row;
+    P.d_rope = d_rope;
+    fill_table(P.tab, d_rope, rope_base);
+    k_rope_append<<<dim3(T, 1), 128, 0, (cudaStream_t) stream>>>(P);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos0, const int32_t *seq_base,
+                                const int32_t *page_table, int page_table_stride, int page_rows, int n_seq, int T,
+                                int d_row, int d_rope, float rope_base, void *stream) {
+    if (int e = check_rope(d_row, d_rope)) return e;
+    if (n_seq <= 0 || T <= 0) return 0;
+    if (!pos0) return fail_invalid("append: pos0 (device) is required; use gs_rope_kv_append_at for a host position");
+    if (page_table && page_rows <= 0) return fail_invalid("append: page_rows must be positive");
+    if (n_seq > 65535) return fail_invalid("append: n_seq > 65535");
+    AppendParams P{};
+    P.kv = kv;
+    P.cache = (__half *) cache;
+    P.pos0 = pos0;
+    P.seq_base = seq_base;
+    P.page_table = page_table;
+    P.page_table_stride = page_table_stride;
+    P.page_rows = page_rows > 0 ? page_rows : 1;
+    P.T = T;
+    P.d_row = d_row;
+    P.d_rope = d_rope;
+    fill_table(P.tab, d_rope, rope_base);
+    k_rope_append<<<dim3(T, n_seq), 128, 0, (cudaStream_t) stream>>>(P);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_rope_f16_inplace(void *x, int S, int H, int d, int d_rope, int64_t pos0, float rope_base,
+                                  void *stream) {
+    if (d <= 0 || d_rope < 0 || d_rope % 2 != 0 || d_rope > d || d % 2 != 0 || d_rope / 2 > ROPE_MAX_PAIRS)
+        return fail_invalid("rope: need even d, even d_rope <= d, d_rope <= 128");
+    if (S <= 0 || H <= 0 || d_rope == 0) return 0;
+    RopeTable tab;
+    fill_table(tab, d_rope, rope_base);
+    const int64_t n_pairs = (int64_t) S * H * (d_rope / 2);
+    k_rope_f16<<<(unsigned) ((n_pairs + 255) / 256), 256, 0, (cudaStream_t) stream>>>((__half *) x, n_pairs, H, d, d_rope,
+                                                                                     pos0, tab);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}

@@ -1,0 +1,129 @@
+/*
+ * glmssd_attn.h - C ABI of the B200 (sm_100a) attention library for the GLM-SSD engine.
+ *
+ * Conventions (those of the reference's kernel crate, crates/cuda/kernels/common.cuh:6-14):
+ *   - every function is extern "C", returns a cudaError_t as int (0 = success), never throws;
+ *   - bad arguments return cudaErrorInvalidValue (1), like crates/cuda/kernels/ops.cu:581;
+ *   - calls only enqueue work on the caller's stream (`void *stream` is a cudaStream_t) and never
+ *     synchronise; results are valid in stream order;
+ *   - the caller owns all device memory, including workspaces; the library allocates nothing and
+ *     keeps no state between calls (safe across cudaDeviceReset, cf. ops.cu:583-587).
+ * All pointers are device pointers unless a comment says "host".
+ */
+#ifndef GLMSSD_ATTN_H
+#define GLMSSD_ATTN_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------
+ * Reference-compatible entry points (same names, argument order and meaning).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Replaces gs_mla_attn, crates/cuda/kernels/ops.cu:579-597 (Rust declaration crates/cuda/src/lib.rs:97-100;
+ * only caller crates/engine/src/forward.rs:902-906).
+ *   q    f32 [T][H][R]  absorbed queries           C    f16 [ctx][R] latent cache
+ *   sel  i32 [T][sel_stride] attended rows         cnt  i32 [T] rows attended by query t
+ *   o    f32 [T][H][R]                             part f32 workspace, T*H*splits*(R+2) floats
+ *                                                       when splits > 1 (same size as ops.cu:578)
+ * Returns cudaErrorInvalidValue for R != 512, H % 16 != 0, splits < 1 (as the reference) and for
+ * C_scales != NULL (the Q8 cache format is not implemented). */
+int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride, const int *cnt,
+                float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
+
+/* Replaces gs_f32_to_f16, crates/cuda/kernels/gemm.cu:159-163 (Rust declaration crates/cuda/src/lib.rs:123;
+ * caller crates/engine/src/forward.rs:857-860): y[i] = half_rn(x[i]) for i < n.  This is the reference's
+ * KV-append. */
+int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Absorbed-MLA decode over the f16 latent cache.  Generalises gs_mla_attn (ops.cu:420-597) to
+ * score width d_qk != value width d_v (V = the first d_v columns of the same cache row), f16
+ * queries, any head count, several sequences per call, and dense-range or paged addressing
+ * instead of a materialised position list (the dense list of ops.cu:728-731).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct gs_mla_decode_args {
+    const void *q;             /* f16 [n_seq][T][H][d_qk] */
+    const void *cache;         /* f16 [cache_rows][d_qk] row-major (the layout of forward.rs:388-404) */
+    int64_t cache_rows;        /* rows in the cache allocation (for paged: n_pages * page_rows) */
+    const int32_t *seq_lens;   /* [n_seq] rows attended by the LAST query token of each sequence */
+    const int32_t *seq_base;   /* dense: [n_seq] first cache row of each sequence; NULL = all 0 */
+    const int32_t *page_table; /* paged: [n_seq][page_table_stride] page ids; NULL = dense */
+    int32_t page_table_stride;
+    int32_t page_rows;         /* rows per page; 64 when paged */
+    float scale;               /* softmax scale, 1/sqrt(256) in the engine (forward.rs:904) */
+    int32_t tail_causal;       /* 1: query token t attends seq_lens[b] - (T-1-t) rows (the T new rows are
+                                  causal among themselves, ops.cu:728-731); 0: every token attends
+                                  seq_lens[b] rows (a shard that does not hold the end of the sequence) */
+    float *o;                  /* f32 [n_seq][T][H][d_v]; NULL when only part_out is wanted */
+    float *part_out;           /* optional: one merged (acc, m, l) record per query row instead of / besides
+                                  o, for a cross-GPU combine: floats [rows*d_v acc][rows*2 (m,l)],
+                                  rows = n_seq*T*H; the unnormalised form of ops.cu:539-549 */
+    void *workspace;           /* gs_mla_decode_workspace_bytes() bytes */
+    int64_t workspace_bytes;
+    int32_t n_seq, T, H, d_qk, d_v;
+    int32_t max_seq_len;       /* host-side upper bound of seq_lens[] (sizing only; 0 = cache_rows) */
+    int32_t impl;              /* 0 = automatic; 1 = force the CUDA-core gather kernel; 2 = force the
+                                  tcgen05 kernel (returns cudaErrorInvalidValue if the shape is outside it) */
+} gs_mla_decode_args;
+
+/* Bytes of workspace gs_mla_decode needs on the current device for these sizes (host function). */
+int64_t gs_mla_decode_workspace_bytes(int n_seq, int T, int H, int d_v);
+
+/* Enqueue the decode.  New entry point; the call it stands in for is forward.rs:902-906. */
+int gs_mla_decode(const gs_mla_decode_args *args /* host */, void *stream);
+
+/* Merge n_parts record blocks (each [rows*d_v acc][rows*2 (m,l)] floats, consecutive blocks
+ * part_stride floats apart) into o f32 [rows][d_v]:  M = max m, L = sum l e^(m-M),
+ * o = sum acc e^(m-M) / L, zeros when L == 0; the arithmetic of k_mla_combine, ops.cu:552-574,
+ * with "split" = shard/GPU. */
+int gs_mla_combine_parts(const float *parts, int n_parts, int64_t part_stride, int rows, int d_v, float *o,
+                         void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Causal prefill attention (non-absorbed).  The reference runs prefill through gs_mla_attn with
+ * T <= 256 and splits = 1 (forward.rs:61, :898-908), which equals per-head causal attention of
+ * width 256 (forward.rs:900, :907).
+ *   q f16 [S][H][d]   k f16 [p0+S][H][d]   v f16 [p0+S][H][d]   query i attends keys 0 .. p0+i
+ *   o: f32 [S][H][d] (o_f16 == 0) or f16 (o_f16 == 1)
+ * ---------------------------------------------------------------------------------------------- */
+int gs_prefill_attn(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d, int p0,
+                    float scale, int impl, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Fused RoPE + KV-append: replaces the gs_f32_to_f16 call of forward.rs:857-860 when the cache row
+ * carries a rotary part.  Row t of kv (f32 [n_seq][T][d_row]) is rounded to f16 (RNE, as
+ * gemm.cu:157) and stored at position pos0 + t of its sequence, after rotating its last d_rope
+ * columns (adjacent pairs, angle pos * base^(-2i/d_rope)).  d_rope = 0 gives the plain append.
+ * ---------------------------------------------------------------------------------------------- */
+/* Host-known position, one sequence, dense cache: `cache_row0` points at row pos0 (as the
+ * reference passes latent + p0*R*2, forward.rs:858). */
+int gs_rope_kv_append_at(const float *kv, void *cache_row0, int64_t pos0, int T, int d_row, int d_rope,
+                         float rope_base, void *stream);
+/* Batched, positions on the device: pos0[b] is the position of sequence b's first new row. */
+int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos0, const int32_t *seq_base,
+                      const int32_t *page_table, int page_table_stride, int page_rows, int n_seq, int T, int d_row,
+                      int d_rope, float rope_base, void *stream);
+/* RoPE in place on f16 rows x [S][H][d] (prefill Q and K): last d_rope columns of every head at
+ * position pos0 + s. */
+int gs_rope_f16_inplace(void *x, int S, int H, int d, int d_rope, int64_t pos0, float rope_base, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Diagnostics.
+ * ---------------------------------------------------------------------------------------------- */
+/* Text of the last error this thread's calls produced (host; like gs_error_string, lib.rs:169-175). */
+const char *gs_attn_last_error_string(void);
+/* Library build tag, e.g. "glmssd_attn sm_100a". */
+const char *gs_attn_version(void);
+/* Reads (synchronously, after synchronising `stream`) the device status word a decode left in its
+ * workspace: 0 = ok, non-zero = a bounded wait inside the kernel gave up (code identifies which).
+ * Returns cudaErrorLaunchTimeout when the word is non-zero. */
+int gs_mla_decode_status(const void *workspace, int32_t *status_out /* host, may be NULL */, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLMSSD_ATTN_H */

@@ -1,0 +1,479 @@
+/*
+ * CPU oracle for the GLM-SSD attention hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C fp32 restatement of the attention semantics of the reference engine's
+ * CUDA kernels, used by the test-suite as the checker and by the benchmark as the timed CPU
+ * baseline.  It is never linked into, imported by, or called from the product library.
+ *
+ * Parity status: the reference repository holds no golden vector, known-answer test or CPU
+ * implementation for its attention path, so this restatement is pinned in two other ways:
+ *   (1) the f16 conversion pair is checked against the reference's own pin, the exhaustive
+ *       65 536-value round trip of crates/quants/src/lib.rs:361-370;
+ *   (2) the attention functions are checked against outputs of the reference's own CUDA kernel
+ *       (crates/cuda/kernels/ops.cu gs_mla_attn, gemm.cu gs_f32_to_f16) compiled unmodified and
+ *       run on a B200; those outputs are committed as fixtures under tests/golden/.
+ * The 576-wide score / 512-wide value split, RoPE and the non-absorbed prefill are extensions the
+ * reference does not have; for them parity is unpinned by the reference and rests on (2)'s shared
+ * core plus an independent float64 numpy check in the tests.
+ *
+ * Each function cites the reference lines it follows (paths relative to the reference project).
+ */
+#define _GNU_SOURCE
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#include "oracle.h"
+
+/* ------------------------------------------------------------------------------------------
+ * f16 <-> f32, round-to-nearest-even.  Follows crates/quants/src/lib.rs:15-38 (f16_to_f32) and
+ * :41-74 (f32_to_f16); the CUDA side of the reference uses __float2half (gemm.cu:157), which is
+ * the same rounding.
+ * ------------------------------------------------------------------------------------------ */
+float oracle_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t) (h >> 15)) << 31;
+    uint32_t exp = (h >> 10) & 0x1f;
+    uint32_t man = h & 0x3ff;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            /* subnormal half: shift the mantissa up until its leading one reaches bit 10 */
+            uint32_t e = 113;
+            while ((man & 0x400) == 0) {
+                man <<= 1;
+                e -= 1;
+            }
+            bits = sign | (e << 23) | ((man & 0x3ff) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+uint16_t oracle_f32_to_f16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint16_t sign = (uint16_t) ((x >> 16) & 0x8000);
+    int32_t exp = (int32_t) ((x >> 23) & 0xff);
+    uint32_t man = x & 0x7fffff;
+    if (exp == 0xff) return (uint16_t) (sign | 0x7c00 | (man ? 0x200 : 0));
+    int32_t e = exp - 127 + 15;
+    if (e >= 31) return (uint16_t) (sign | 0x7c00);
+    if (e <= 0) {
+        if (e < -10) return sign;
+        uint32_t m = man | 0x800000;
+        uint32_t shift = (uint32_t) (14 - e);
+        uint32_t half = 1u << (shift - 1);
+        uint32_t rem = m & ((1u << shift) - 1);
+        uint32_t r = m >> shift;
+        if (rem > half || (rem == half && (r & 1))) r += 1;
+        return (uint16_t) (sign | r);
+    }
+    uint32_t rem = man & 0x1fff;
+    uint32_t r = ((uint32_t) e << 10) | (man >> 13);
+    if (rem > 0x1000 || (rem == 0x1000 && (r & 1))) r += 1;
+    return (uint16_t) (sign | r);
+}
+
+static float g_h2f[65536];
+static pthread_once_t g_h2f_once = PTHREAD_ONCE_INIT;
+static void h2f_init(void) {
+    for (uint32_t i = 0; i < 65536; i++) g_h2f[i] = oracle_f16_to_f32((uint16_t) i);
+}
+static inline const float *h2f_table(void) {
+    pthread_once(&g_h2f_once, h2f_init);
+    return g_h2f;
+}
+
+void oracle_f16_to_f32_array(const uint16_t *x, float *y, int64_t n) {
+    const float *lut = h2f_table();
+    for (int64_t i = 0; i < n; i++) y[i] = lut[x[i]];
+}
+
+/* KV-append of the reference: cache[i] = half_rn(x[i]) for i < n (gemm.cu:155-163). */
+void oracle_f32_to_f16_array(const float *x, uint16_t *y, int64_t n) {
+    for (int64_t i = 0; i < n; i++) y[i] = oracle_f32_to_f16(x[i]);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Thread pool helper: run fn(item) for item in [0, n_items) on up to `threads` pthreads.
+ * ------------------------------------------------------------------------------------------ */
+typedef void (*item_fn)(void *ctx, int64_t item);
+typedef struct {
+    item_fn fn;
+    void *ctx;
+    int64_t n_items;
+    volatile int64_t next;
+} pool_t;
+
+static void *pool_worker(void *arg) {
+    pool_t *p = (pool_t *) arg;
+    for (;;) {
+        int64_t i = __atomic_fetch_add(&p->next, 1, __ATOMIC_RELAXED);
+        if (i >= p->n_items) break;
+        p->fn(p->ctx, i);
+    }
+    return NULL;
+}
+
+int oracle_host_cores(void) {
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    return n > 0 ? (int) n : 1;
+}
+
+static int run_pool(item_fn fn, void *ctx, int64_t n_items, int threads) {
+    if (threads <= 0) threads = oracle_host_cores();
+    if (threads > 256) threads = 256;
+    if ((int64_t) threads > n_items) threads = n_items > 0 ? (int) n_items : 1;
+    pool_t p = {fn, ctx, n_items, 0};
+    if (threads == 1) {
+        pool_worker(&p);
+        return 1;
+    }
+    pthread_t th[256];
+    int started = 0;
+    for (int t = 0; t < threads - 1; t++) {
+        if (pthread_create(&th[started], NULL, pool_worker, &p) == 0) started++;
+    }
+    pool_worker(&p);
+    for (int t = 0; t < started; t++) pthread_join(th[t], NULL);
+    return started + 1;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * One attention row.  Semantics of k_mla_flash (crates/cuda/kernels/ops.cu:420-424, :487-538):
+ *   score_s = scale * q . K[row_s]          (fp32 accumulate over d_qk)
+ *   p_s     = exp(score_s - max_s score)     (softmax over the n attended rows)
+ *   o       = sum_s p_s * V[row_s] / sum_s p_s, over d_v columns; an empty set gives zeros
+ *             (ops.cu:535, :565).
+ * In the reference K and V are the same latent row (d_qk = d_v = 512); the absorbed-MLA extension
+ * scores over 576 columns and takes V = the first 512 of the same row; the non-absorbed prefill
+ * passes separate K and V rows.  `rows` (may be NULL = identity) is the position list sel[t]
+ * (ops.cu:455, :459).  Also returns the softmax statistics (m = max score, l = sum p) so that
+ * split partials in the layout of ops.cu:539-549 can be formed.
+ * ------------------------------------------------------------------------------------------ */
+#if defined(__F16C__) && defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+/* 8-wide helpers; the f16 -> f32 widening is exact, so these give the same products as the table. */
+static inline float dot_f32_f16(const float *q, const uint16_t *k, int d) {
+    __m256 a0 = _mm256_setzero_ps(), a1 = _mm256_setzero_ps();
+    int r = 0;
+    for (; r + 16 <= d; r += 16) {
+        a0 = _mm256_fmadd_ps(_mm256_loadu_ps(q + r), _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (k + r))), a0);
+        a1 = _mm256_fmadd_ps(_mm256_loadu_ps(q + r + 8), _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (k + r + 8))),
+                             a1);
+    }
+    float tmp[8];
+    _mm256_storeu_ps(tmp, _mm256_add_ps(a0, a1));
+    float acc = ((tmp[0] + tmp[1]) + (tmp[2] + tmp[3])) + ((tmp[4] + tmp[5]) + (tmp[6] + tmp[7]));
+    const float *lut = h2f_table();
+    for (; r < d; r++) acc += q[r] * lut[k[r]];
+    return acc;
+}
+static inline void axpy_f16(float *o, float p, const uint16_t *v, int d) {
+    const __m256 pp = _mm256_set1_ps(p);
+    int c = 0;
+    for (; c + 8 <= d; c += 8)
+        _mm256_storeu_ps(o + c, _mm256_fmadd_ps(pp, _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (v + c))),
+                                                _mm256_loadu_ps(o + c)));
+    const float *lut = h2f_table();
+    for (; c < d; c++) o[c] += p * lut[v[c]];
+}
+#else
+static inline float dot_f32_f16(const float *q, const uint16_t *k, int d) {
+    const float *lut = h2f_table();
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int r = 0;
+    for (; r + 4 <= d; r += 4) {
+        a0 += q[r] * lut[k[r]];
+        a1 += q[r + 1] * lut[k[r + 1]];
+        a2 += q[r + 2] * lut[k[r + 2]];
+        a3 += q[r + 3] * lut[k[r + 3]];
+    }
+    for (; r < d; r++) a0 += q[r] * lut[k[r]];
+    return (a0 + a1) + (a2 + a3);
+}
+static inline void axpy_f16(float *o, float p, const uint16_t *v, int d) {
+    const float *lut = h2f_table();
+    for (int c = 0; c < d; c++) o[c] += p * lut[v[c]];
+}
+#endif
+
+static void attend_row(const float *q, int d_qk, int d_v, const uint16_t *K, int64_t k_stride, const uint16_t *V,
+                       int64_t v_stride, const int32_t *rows, int64_t row0, int64_t n, float scale, int normalise,
+                       float *o, float *m_out, float *l_out, float *score_buf) {
+    float m = -INFINITY;
+    for (int64_t s = 0; s < n; s++) {
+        const int64_t row = rows ? (int64_t) rows[s] : row0 + s;
+        const float sc = dot_f32_f16(q, K + row * k_stride, d_qk) * scale;
+        score_buf[s] = sc;
+        if (sc > m) m = sc;
+    }
+    for (int c = 0; c < d_v; c++) o[c] = 0.f;
+    float l = 0.f;
+    for (int64_t s = 0; s < n; s++) {
+        const int64_t row = rows ? (int64_t) rows[s] : row0 + s;
+        const float p = expf(score_buf[s] - m);
+        l += p;
+        axpy_f16(o, p, V + row * v_stride, d_v);
+    }
+    if (normalise) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        for (int c = 0; c < d_v; c++) o[c] *= inv;
+    }
+    if (m_out) *m_out = m;
+    if (l_out) *l_out = l;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Reference-ABI attention: gs_mla_attn (ops.cu:579-597) with an f16 cache (C_scales == NULL).
+ *   q   f32 [T][H][R]     sel int32 [T][sel_stride]   cnt int32 [T]    o f32 [T][H][R]
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+    const float *q;
+    const uint16_t *C;
+    const int32_t *sel;
+    int sel_stride;
+    const int32_t *cnt;
+    float scale;
+    float *o;
+    int T, H, R;
+} ref_ctx_t;
+
+static void ref_item(void *vctx, int64_t item) {
+    ref_ctx_t *c = (ref_ctx_t *) vctx;
+    const int t = (int) (item / c->H), h = (int) (item % c->H);
+    const int64_t n = c->cnt[t];
+    float *buf = (float *) malloc(sizeof(float) * (size_t) (n > 0 ? n : 1));
+    attend_row(c->q + ((int64_t) t * c->H + h) * c->R, c->R, c->R, c->C, c->R, c->C, c->R,
+               c->sel + (int64_t) t * c->sel_stride, 0, n, c->scale, 1, c->o + ((int64_t) t * c->H + h) * c->R, NULL,
+               NULL, buf);
+    free(buf);
+}
+
+int oracle_mla_attn_ref(const float *q, const uint16_t *C, const int32_t *sel, int sel_stride, const int32_t *cnt,
+                        float scale, float *o, int T, int H, int R, int threads) {
+    ref_ctx_t c = {q, C, sel, sel_stride, cnt, scale, o, T, H, R};
+    return run_pool(ref_item, &c, (int64_t) T * H, threads);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Split partials and their combine, as the reference forms them:
+ *   key range of split s: per = ceil(n / splits), [s*per, min(n, s*per + per))  (ops.cu:447-449)
+ *   partial = (unnormalised acc[R], m, l)                                       (ops.cu:539-549)
+ *   combine: M = max m_s; L = sum l_s e^{m_s-M} (skipping m_s = -inf);
+ *            o = sum acc_s e^{m_s-M} / L, zeros when L == 0                      (ops.cu:558-573)
+ * The oracle keeps one record per (t, h, split): part[((t*H+h)*splits+s)*(R_v+2)] = acc.., m, l.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_combine(const float *part, int64_t n_rows, int n_parts, int d_v, float *o) {
+    const int64_t rec = d_v + 2;
+    for (int64_t r = 0; r < n_rows; r++) {
+        const float *base = part + r * n_parts * rec;
+        float M = -INFINITY;
+        for (int s = 0; s < n_parts; s++) M = fmaxf(M, base[s * rec + d_v]);
+        float L = 0.f;
+        for (int s = 0; s < n_parts; s++) {
+            const float m = base[s * rec + d_v];
+            if (m != -INFINITY) L += base[s * rec + d_v + 1] * expf(m - M);
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int c = 0; c < d_v; c++) {
+            float a = 0.f;
+            for (int s = 0; s < n_parts; s++) {
+                const float m = base[s * rec + d_v];
+                if (m != -INFINITY) a += base[s * rec + c] * expf(m - M);
+            }
+            o[r * d_v + c] = a * inv;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Absorbed-MLA decode over the latent cache (extension of gs_mla_attn to the benchmark shapes):
+ *   q      f16 [n_seq][T][H][d_qk]
+ *   cache  f16 rows of d_qk; dense: sequence b owns rows seq_base[b] .. ; paged: row i of sequence
+ *          b is row (i % page_rows) of page page_table[b][i / page_rows]
+ *   seq_lens[b] = rows attended by the LAST of the T query tokens; token t attends
+ *          seq_lens[b] - (T-1-t) rows, i.e. the T tokens are causal among themselves.  This is the
+ *          dense list of ops.cu:728-731 (query t sees 0..=pos0+t) with the new rows already
+ *          appended (crates/engine/src/forward.rs:849-860 precede :902).
+ *   V = first d_v columns of the same row; o f32 [n_seq][T][H][d_v].
+ * With parts != NULL the rows [part_lo, part_hi) of every sequence are attended only and the
+ * unnormalised (acc, m, l) record is written instead of o (the per-GPU shard partial).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+    const uint16_t *q;
+    const uint16_t *cache;
+    const int32_t *seq_lens, *seq_base, *page_table;
+    int page_table_stride, page_rows;
+    float scale;
+    float *o;
+    float *parts;
+    int64_t part_lo, part_hi;
+    int n_seq, T, H, d_qk, d_v;
+} dec_ctx_t;
+
+static void dec_item(void *vctx, int64_t item) {
+    dec_ctx_t *c = (dec_ctx_t *) vctx;
+    const int h = (int) (item % c->H);
+    const int t = (int) ((item / c->H) % c->T);
+    const int b = (int) (item / ((int64_t) c->H * c->T));
+    int64_t n = (int64_t) c->seq_lens[b] - (c->T - 1 - t);
+    if (n < 0) n = 0;
+    int64_t lo = 0, hi = n;
+    if (c->parts) {
+        lo = c->part_lo < n ? c->part_lo : n;
+        hi = c->part_hi < n ? c->part_hi : n;
+    }
+    const int64_t cnt = hi - lo;
+    float *qf = (float *) malloc(sizeof(float) * (size_t) c->d_qk);
+    oracle_f16_to_f32_array(c->q + (((int64_t) b * c->T + t) * c->H + h) * c->d_qk, qf, c->d_qk);
+    float *buf = (float *) malloc(sizeof(float) * (size_t) (cnt > 0 ? cnt : 1));
+    int32_t *rows = NULL;
+    int64_t row0 = 0;
+    if (c->page_table) {
+        rows = (int32_t *) malloc(sizeof(int32_t) * (size_t) (cnt > 0 ? cnt : 1));
+        const int32_t *pt = c->page_table + (int64_t) b * c->page_table_stride;
+        for (int64_t i = 0; i < cnt; i++) {
+            const int64_t pos = lo + i;
+            rows[i] = pt[pos / c->page_rows] * c->page_rows + (int32_t) (pos % c->page_rows);
+        }
+    } else {
+        row0 = (c->seq_base ? (int64_t) c->seq_base[b] : 0) + lo;
+    }
+    const int64_t orow = ((int64_t) b * c->T + t) * c->H + h;
+    if (c->parts) {
+        float *rec = c->parts + orow * (c->d_v + 2);
+        attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 0, rec,
+                   rec + c->d_v, rec + c->d_v + 1, buf);
+    } else {
+        attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 1,
+                   c->o + orow * c->d_v, NULL, NULL, buf);
+    }
+    free(rows);
+    free(buf);
+    free(qf);
+}
+
+int oracle_mla_decode(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens, const int32_t *seq_base,
+                      const int32_t *page_table, int page_table_stride, int page_rows, float scale, float *o,
+                      int n_seq, int T, int H, int d_qk, int d_v, int threads) {
+    dec_ctx_t c = {q, cache, seq_lens, seq_base, page_table, page_table_stride, page_rows, scale, o, NULL, 0, 0,
+                   n_seq, T, H, d_qk, d_v};
+    return run_pool(dec_item, &c, (int64_t) n_seq * T * H, threads);
+}
+
+int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens,
+                              const int32_t *seq_base, const int32_t *page_table, int page_table_stride,
+                              int page_rows, float scale, float *parts, int64_t part_lo, int64_t part_hi, int n_seq,
+                              int T, int H, int d_qk, int d_v, int threads) {
+    dec_ctx_t c = {q, cache, seq_lens, seq_base, page_table, page_table_stride, page_rows, scale, NULL, parts,
+                   part_lo, part_hi, n_seq, T, H, d_qk, d_v};
+    return run_pool(dec_item, &c, (int64_t) n_seq * T * H, threads);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Causal prefill attention, non-absorbed form.  The reference runs prefill through the same
+ * absorbed kernel with T <= 256 queries and splits = 1 (forward.rs:61, :898-908); with
+ * q.(k_b c) = (k_b^T q).c that equals per-head causal attention with head width 256
+ * (forward.rs:900, :907), which is what is restated here:
+ *   Q f16 [S][H][d], K f16 [p0+S][H][d], V f16 [p0+S][H][dv]; query i attends keys 0 .. p0+i.
+ * rows_subset (may be NULL) restricts the computed query rows (for spot checks at full size).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+    const uint16_t *Q, *K, *V;
+    float scale;
+    float *o;
+    int S, H, d, dv, p0;
+    const int32_t *rows_subset;
+    int n_subset;
+} pf_ctx_t;
+
+static void pf_item(void *vctx, int64_t item) {
+    pf_ctx_t *c = (pf_ctx_t *) vctx;
+    const int h = (int) (item % c->H);
+    const int64_t idx = item / c->H;
+    const int i = c->rows_subset ? c->rows_subset[idx] : (int) idx;
+    const int64_t n = (int64_t) c->p0 + i + 1;
+    float *qf = (float *) malloc(sizeof(float) * (size_t) c->d);
+    oracle_f16_to_f32_array(c->Q + ((int64_t) i * c->H + h) * c->d, qf, c->d);
+    float *buf = (float *) malloc(sizeof(float) * (size_t) n);
+    attend_row(qf, c->d, c->dv, c->K + (int64_t) h * c->d, (int64_t) c->H * c->d, c->V + (int64_t) h * c->dv,
+               (int64_t) c->H * c->dv, NULL, 0, n, c->scale, 1, c->o + (idx * c->H + h) * c->dv, NULL, NULL, buf);
+    free(buf);
+    free(qf);
+}
+
+int oracle_prefill(const uint16_t *Q, const uint16_t *K, const uint16_t *V, float scale, float *o, int S, int H, int d,
+                   int dv, int p0, const int32_t *rows_subset, int n_subset, int threads) {
+    pf_ctx_t c = {Q, K, V, scale, o, S, H, d, dv, p0, rows_subset, n_subset};
+    const int64_t n_rows = rows_subset ? n_subset : S;
+    return run_pool(pf_item, &c, n_rows * H, threads);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * RoPE.  The reference model has no rotary embedding; the benchmark configs add one: base 10000 on
+ * the last `d_rope` columns of a row at its absolute position.  Convention fixed here (and matched
+ * by the CUDA kernels): adjacent pairs (2i, 2i+1) rotate by angle pos * base^(-2i/d_rope);
+ * the inverse frequency is computed in double and rounded to f32, the angle is an f32 product,
+ * cos/sin are evaluated in f32.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_rope_inv_freq(float *inv_freq, int d_rope, double base) {
+    for (int i = 0; i < d_rope / 2; i++) inv_freq[i] = (float) pow(base, -2.0 * i / (double) d_rope);
+}
+
+static inline void rope_pair(float *x0, float *x1, float pos, float inv_freq) {
+    const float ang = pos * inv_freq;
+    const float c = cosf(ang), s = sinf(ang);
+    const float a = *x0, b = *x1;
+    *x0 = a * c - b * s;
+    *x1 = a * s + b * c;
+}
+
+/* Fused RoPE + KV-append: the reference appends half_rn(kv) to cache rows p0.. (gemm.cu:155-163,
+ * forward.rs:857-860); here the last d_rope columns are rotated at position pos0+t first.
+ * x f32 [T][d_row] -> y f16 [T][d_row]. */
+void oracle_rope_append(const float *x, uint16_t *y, int T, int d_row, int d_rope, int64_t pos0, double base) {
+    float inv[256];
+    oracle_rope_inv_freq(inv, d_rope, base);
+    for (int t = 0; t < T; t++) {
+        const float *xr = x + (int64_t) t * d_row;
+        uint16_t *yr = y + (int64_t) t * d_row;
+        const int d0 = d_row - d_rope;
+        for (int c = 0; c < d0; c++) yr[c] = oracle_f32_to_f16(xr[c]);
+        for (int i = 0; i < d_rope / 2; i++) {
+            float a = xr[d0 + 2 * i], b = xr[d0 + 2 * i + 1];
+            rope_pair(&a, &b, (float) (pos0 + t), inv[i]);
+            yr[d0 + 2 * i] = oracle_f32_to_f16(a);
+            yr[d0 + 2 * i + 1] = oracle_f32_to_f16(b);
+        }
+    }
+}
+
+/* RoPE in place on f16 rows [S][H][d] (prefill Q and K): last d_rope columns of every head at
+ * position pos0 + s; computed in f32 and rounded back to f16. */
+void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base) {
+    float inv[256];
+    oracle_rope_inv_freq(inv, d_rope, base);
+    const int d0 = d - d_rope;
+    for (int s = 0; s < S; s++)
+        for (int h = 0; h < H; h++) {
+            uint16_t *r = x + ((int64_t) s * H + h) * d + d0;
+            for (int i = 0; i < d_rope / 2; i++) {
+                float a = oracle_f16_to_f32(r[2 * i]), b = oracle_f16_to_f32(r[2 * i + 1]);
+                rope_pair(&a, &b, (float) (pos0 + s), inv[i]);
+                r[2 * i] = oracle_f32_to_f16(a);
+                r[2 * i + 1] = oracle_f32_to_f16(b);
+            }
+        }
+}

@@ -1,0 +1,36 @@
+/* CPU oracle for the attention hot path: test infrastructure, never part of the product library.
+ * See oracle.c for the reference lines each function follows. */
+#ifndef GLMSSD_ORACLE_H
+#define GLMSSD_ORACLE_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+float oracle_f16_to_f32(uint16_t h);
+uint16_t oracle_f32_to_f16(float f);
+void oracle_f16_to_f32_array(const uint16_t *x, float *y, int64_t n);
+void oracle_f32_to_f16_array(const float *x, uint16_t *y, int64_t n);
+int oracle_host_cores(void);
+
+/* Every threaded entry point returns the number of threads it used. threads <= 0: all host cores. */
+int oracle_mla_attn_ref(const float *q, const uint16_t *C, const int32_t *sel, int sel_stride, const int32_t *cnt,
+                        float scale, float *o, int T, int H, int R, int threads);
+void oracle_combine(const float *part, int64_t n_rows, int n_parts, int d_v, float *o);
+int oracle_mla_decode(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens, const int32_t *seq_base,
+                      const int32_t *page_table, int page_table_stride, int page_rows, float scale, float *o,
+                      int n_seq, int T, int H, int d_qk, int d_v, int threads);
+int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens,
+                              const int32_t *seq_base, const int32_t *page_table, int page_table_stride,
+                              int page_rows, float scale, float *parts, int64_t part_lo, int64_t part_hi, int n_seq,
+                              int T, int H, int d_qk, int d_v, int threads);
+int oracle_prefill(const uint16_t *Q, const uint16_t *K, const uint16_t *V, float scale, float *o, int S, int H, int d,
+                   int dv, int p0, const int32_t *rows_subset, int n_subset, int threads);
+void oracle_rope_inv_freq(float *inv_freq, int d_rope, double base);
+void oracle_rope_append(const float *x, uint16_t *y, int T, int d_row, int d_rope, int64_t pos0, double base);
+void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

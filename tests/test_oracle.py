@@ -1,0 +1,169 @@
+"""CPU tests of the oracle: the reference's own pin (f16 round trip), float64 numpy cross-checks,
+split/combine algebra, RoPE, and the committed golden vectors."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from conftest import check_close
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_f16_roundtrip_all_values(oracle):
+    # the reference's test: crates/quants/src/lib.rs:361-370
+    h = np.arange(65536, dtype=np.uint16)
+    f = oracle.f16_to_f32(h.view(np.float16))
+    keep = ~np.isnan(f)
+    back = oracle.f32_to_f16(f[keep]).view(np.uint16)
+    assert np.array_equal(back, h[keep])
+    ref = h.view(np.float16).astype(np.float32)
+    assert np.array_equal(f[keep], ref[keep])
+
+
+def test_f32_to_f16_rne_matches_numpy(oracle):
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.standard_normal(200000).astype(np.float32) * s for s in (1e-8, 1e-4, 1.0, 300.0, 7e4)])
+    x = np.concatenate([x, np.array([0.0, -0.0, np.inf, -np.inf, 65504.0, 65520.0, 5.96e-8, 2.98e-8], np.float32)])
+    assert np.array_equal(oracle.f32_to_f16(x).view(np.uint16), x.astype(np.float16).view(np.uint16))
+
+
+def _numpy_attend(q, K, V, scale):
+    s = (q.astype(np.float64) @ K.astype(np.float64).T) * scale
+    if s.shape[-1] == 0:
+        return np.zeros((q.shape[0], V.shape[1]))
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    return p @ V.astype(np.float64)
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 63, 64, 65, 1000])
+def test_ref_abi_attention_vs_numpy(oracle, n):
+    rng = np.random.default_rng(n)
+    T, H, R, ctx = 3, 16, 512, max(n, 1) + 40
+    q = rng.standard_normal((T, H, R)).astype(np.float32)
+    C = (rng.standard_normal((ctx, R)) * 0.5).astype(np.float16)
+    stride = n + 5
+    sel = np.zeros((T, stride), np.int32)
+    cnt = np.zeros(T, np.int32)
+    for t in range(T):
+        k = max(0, n - t)
+        cnt[t] = k
+        sel[t, :k] = rng.permutation(ctx)[:k]
+    o = oracle.mla_attn_ref(q, C, sel, cnt, 1 / 16)
+    for t in range(T):
+        want = _numpy_attend(q[t], C[sel[t, :cnt[t]]], C[sel[t, :cnt[t]]], 1 / 16)
+        check_close(o[t], want, f"t={t}", 1e-5, 1e-6)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3])
+def test_decode_dense_and_paged_agree(oracle, T):
+    rng = np.random.default_rng(11 + T)
+    H, n_seq = 5, 3
+    lens = np.array([130, 64, 7], np.int32)
+    q = rng.standard_normal((n_seq, T, H, 576)).astype(np.float16)
+    n_pages = int(sum(-(-l // 64) for l in lens)) + 2
+    pool = (rng.standard_normal((n_pages * 64, 576)) * 0.5).astype(np.float16)
+    perm = rng.permutation(n_pages)
+    pt = np.zeros((n_seq, 4), np.int32)
+    k = 0
+    dense = np.zeros((int(lens.sum()), 576), np.float16)
+    base = np.zeros(n_seq, np.int32)
+    off = 0
+    for b in range(n_seq):
+        base[b] = off
+        for j in range(-(-int(lens[b]) // 64)):
+            pt[b, j] = perm[k]
+            k += 1
+            rows = min(64, lens[b] - 64 * j)
+            dense[off + 64 * j: off + 64 * j + rows] = pool[pt[b, j] * 64: pt[b, j] * 64 + rows]
+        off += int(lens[b])
+    o_paged = oracle.mla_decode(q, pool, lens, 1 / 16, page_table=pt)
+    o_dense = oracle.mla_decode(q, dense, lens, 1 / 16, seq_base=base)
+    assert np.array_equal(o_paged, o_dense)
+    for b in range(n_seq):
+        for t in range(T):
+            n = max(0, lens[b] - (T - 1 - t))
+            rows = dense[base[b]: base[b] + n]
+            want = _numpy_attend(q[b, t], rows, rows[:, :512], 1 / 16)
+            check_close(o_dense[b, t], want, f"b={b} t={t}", 1e-5, 1e-6)
+
+
+def test_partials_combine_to_full(oracle):
+    # the split/combine algebra of crates/cuda/kernels/ops.cu:539-574, with shards as splits
+    rng = np.random.default_rng(5)
+    n, H, T = 1000, 4, 2
+    q = rng.standard_normal((1, T, H, 576)).astype(np.float16)
+    cache = (rng.standard_normal((n, 576)) * 0.5).astype(np.float16)
+    full = oracle.mla_decode(q, cache, [n], 1 / 16)
+    for G in (1, 2, 3, 8, 16):
+        per = -(-n // G)
+        recs = [oracle.mla_decode(q, cache, [n], 1 / 16, part_range=(g * per, min(n, (g + 1) * per))) for g in range(G)]
+        # an empty shard has m = -inf, l = 0 and must be ignored
+        recs.append(oracle.mla_decode(q, cache, [n], 1 / 16, part_range=(n, n)))
+        parts = np.stack([r.reshape(T * H, 514) for r in recs], axis=1)
+        assert np.isneginf(parts[:, -1, 512]).all() and (parts[:, -1, 513] == 0).all()
+        o = oracle.combine(parts).reshape(1, T, H, 512)
+        check_close(o, full, f"G={G}", 1e-5, 1e-6)
+
+
+def test_prefill_vs_numpy(oracle):
+    rng = np.random.default_rng(8)
+    S, H, d, p0 = 70, 3, 256, 9
+    Q = rng.standard_normal((S, H, d)).astype(np.float16)
+    K = rng.standard_normal((p0 + S, H, d)).astype(np.float16)
+    V = rng.standard_normal((p0 + S, H, d)).astype(np.float16)
+    o = oracle.prefill(Q, K, V, 1 / 16, p0=p0)
+    for h in range(H):
+        for i in (0, 1, 33, 69):
+            want = _numpy_attend(Q[i:i + 1, h], K[:p0 + i + 1, h], V[:p0 + i + 1, h], 1 / 16)
+            check_close(o[i, h][None], want, f"h={h} i={i}", 1e-5, 1e-6)
+    sub = oracle.prefill(Q, K, V, 1 / 16, p0=p0, rows=[5, 69])
+    assert np.array_equal(sub[0], o[5]) and np.array_equal(sub[1], o[69])
+
+
+def test_rope_append_matches_float64(oracle):
+    rng = np.random.default_rng(2)
+    T, d_row, d_rope = 5, 576, 64
+    x = rng.standard_normal((T, d_row)).astype(np.float32)
+    for pos0 in (0, 1, 4097, 131000):
+        y = oracle.rope_append(x, pos0).astype(np.float64)
+        want = x.astype(np.float64).copy()
+        i = np.arange(d_rope // 2)
+        inv = 10000.0 ** (-2.0 * i / d_rope)
+        for t in range(T):
+            ang = (pos0 + t) * inv
+            a, b = x[t, 512::2].astype(np.float64), x[t, 513::2].astype(np.float64)
+            want[t, 512::2] = a * np.cos(ang) - b * np.sin(ang)
+            want[t, 513::2] = a * np.sin(ang) + b * np.cos(ang)
+        assert np.array_equal(y[:, :512], x[:, :512].astype(np.float16).astype(np.float64))
+        # f32 angle at positions ~1e5 carries ~1e-2 * 2^-24 * 1e5 absolute angle error; allow f16-level slack
+        assert np.abs(y - want).max() < 2e-2
+    # position 0 is the identity rotation: bit-exact f16 rounding of the input
+    assert np.array_equal(oracle.rope_append(x, 0)[0], x[0].astype(np.float16))
+
+
+def test_rope_f16_norm_preserving(oracle):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((9, 2, 256)).astype(np.float16)
+    y = oracle.rope_f16(x, pos0=100)
+    assert np.array_equal(y[..., :192], x[..., :192])
+    n0 = (x[..., 192:].astype(np.float64) ** 2).reshape(9, 2, 32, 2).sum(-1)
+    n1 = (y[..., 192:].astype(np.float64) ** 2).reshape(9, 2, 32, 2).sum(-1)
+    assert np.abs(n0 - n1).max() < 2e-2
+
+
+def test_golden_vectors_from_reference_kernel(oracle):
+    """Outputs of the reference's own CUDA kernel (gs_mla_attn / gs_f32_to_f16 compiled unmodified and
+    run on a B200) pin the oracle.  The fixtures are made by tests/golden/make_golden_from_ref.py."""
+    files = sorted(glob.glob(os.path.join(HERE, "golden", "ref_*.npz")))
+    if not files:
+        pytest.skip("no golden fixtures committed yet")
+    for f in files:
+        z = np.load(f)
+        if "append_x" in z:
+            assert np.array_equal(oracle.f32_to_f16(z["append_x"]).view(np.uint16), z["append_y"])
+        o = oracle.mla_attn_ref(z["q"], z["C"].view(np.float16), z["sel"], z["cnt"], float(z["scale"]))
+        # the reference kernel is built with fast-math (__expf) and sums in tiles of 32
+        check_close(o, z["o"], os.path.basename(f), 2e-5, 2e-6)
