@@ -1,0 +1,463 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  The default workload is the MTP-verify decode the headline metric is quoted
+on (batch 1, 2 causal query tokens, 20 heads x 576 f16, 32768-row f16 latent cache, V = first 512
+columns, scale 1/16).  A step is one pass of the hot path over that input: the attention kernel
+plus the combine kernel, called through the C ABI.  Inputs are synthetic (device RNG, N(0,1)
+queries, N(0,0.5) cache).
+
+  value     algorithmic bytes per step / device time per step, inputs resident in HBM; between
+            steps the call rotates over distinct cache copies totalling more than twice L2.
+  e2e       the same metric through the call-site mirror (MlaDecodeLayer.step): pinned host q and
+            new latent rows are copied in, appended with RoPE, attended, and the output is copied
+            back to the host, every step.  The latent cache is persistent layer state and stays in
+            HBM, as in the engine.
+  roofline  the attention kernel alone (CUDA events around it, per step), against the measured
+            HBM copy bandwidth.
+  --impl reference   times the CPU restatement of the reference's attention semantics (the test
+            oracle) on the host cores; the reference has no CPU implementation of this path and
+            its CUDA kernel rejects these shapes, see DESIGN.md.
+
+With --gpus N > 1 (launched by torchrun) every rank runs its own independent copy of the workload
+(sequences are independent units: weak scaling, no collective on the data path); the "others"
+object carries the 128K-context decode sharded by sequence over the N GPUs, the paged 64-sequence
+batch and the 8192-token prefill.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, D_QK, D_V = 20, 576, 512
+SCALE = 1.0 / 16.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(n_rows: int, T: int, n_seq: int = 1) -> int:
+    """Cache rows read once + queries + f32 outputs (the per-call figure of the measurement plan)."""
+    return n_rows * D_QK * 2 + n_seq * T * H * D_QK * 2 + n_seq * T * H * D_V * 4
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _names(self, mask: int) -> list[str]:
+        nv = self.nv
+        table = {
+            "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap, "hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+            "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+            "hw_power_brake": nv.nvmlClocksEventReasonHwPowerBrakeSlowdown,
+            "applications_clocks": nv.nvmlClocksEventReasonApplicationsClocksSetting,
+        }
+        return [k for k, bit in table.items() if mask & bit]
+
+    def sample(self):
+        if self.nv is None:
+            return
+        try:
+            self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+            self.reasons.update(self._names(int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))))
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict | None:
+        if self.nv is None:
+            return None
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        self.sample()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement on the host cores
+# ---------------------------------------------------------------------------------------------------
+
+def cpu_decode_baseline(n_rows: int, T: int, budget_s: float, max_reps: int = 50) -> dict:
+    """Times the oracle (all host threads) on the decode workload; returns GB/s of algorithmic bytes."""
+    import numpy as np
+    from oracle import oracle_py as O
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, T, H, D_QK), dtype=np.float32).astype(np.float16)
+    cache = (rng.standard_normal((n_rows, D_QK), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True)  # warm-up, page in
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < max_reps and (time.perf_counter() - t0 < budget_s or reps == 0):
+        O.mla_decode(q, cache, [n_rows], SCALE)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": algorithmic_bytes(n_rows, T) / dt / 1e9, "unit": "GB/s", "cores": int(used), "kind": "port",
+            "sample": f"full workload ({n_rows} rows, T={T}, H={H}), {reps} passes, {dt * 1e3:.1f} ms each",
+            "seconds_per_pass": dt}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle_py as O
+    n_rows, T = 32768, 2
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, T, H, D_QK), dtype=np.float32).astype(np.float16)
+    cache = (rng.standard_normal((n_rows, D_QK), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True)
+    t0 = time.perf_counter()
+    O.mla_decode(q, cache, [n_rows], SCALE)
+    t_full = time.perf_counter() - t0
+    # bound the whole run to about two minutes: shorten each step to a prefix of the cache if needed
+    total = (args.steps + args.warmup) * t_full
+    rows = n_rows if total <= 120.0 else max(1024, int(n_rows * 120.0 / total) // 64 * 64)
+    for _ in range(args.warmup):
+        O.mla_decode(q, cache[:rows], [rows], SCALE)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.mla_decode(q, cache[:rows], [rows], SCALE)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = algorithmic_bytes(rows, T) / dt / 1e9
+    sample = f"{rows} of {n_rows} cache rows per step" if rows != n_rows else "full workload per step"
+    line = {
+        "impl": "reference", "metric": "MLA decode-attention HBM GB/s (MTP verify, 32K ctx)", "value": val,
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "mtp_verify_32k: batch 1, T=2 causal, H=20, d_qk=576, d_v=512, ctx=32768, scale=1/16"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": int(used), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU restatement (oracle port) of the reference's attention semantics on the host cores; the "
+                "reference has no CPU implementation of this path",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    pkg = importlib.import_module("glm-ssd_b200")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks, peak_kind = measured_peaks()
+    hbm_peak = float(peaks["hbm_gbs"])
+    tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+
+    def randn_f16(shape, sigma=1.0):
+        out = torch.empty(shape, dtype=torch.float16, device=dev)
+        # chunked so the f32 temporary stays small
+        flat = out.view(-1)
+        step = 1 << 26
+        for i in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - i)
+            flat[i:i + n] = (torch.randn(n, generator=gen, device=dev, dtype=torch.float32) * sigma).to(torch.float16)
+        return out
+
+    def time_loop(fn, steps, warmup):
+        """Device time of `steps` calls of fn(i) after `warmup` calls: barrier + sync on both sides,
+        CUDA events on the launching stream, max over ranks.  Returns seconds per step."""
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) * 1e-3) / max(1, steps)
+
+    sampler = ClockSampler(local_rank)
+
+    # ---- headline workload: MTP verify, T = 2, 32768 rows -------------------------------------------
+    n_rows, T = 32768, 2
+    bytes_step = algorithmic_bytes(n_rows, T)
+    n_copies = max(2, -(-2 * L2_BYTES // (n_rows * D_QK * 2)) + 1)  # total > 2 x L2
+    caches = [randn_f16((n_rows, D_QK), 0.5) for _ in range(n_copies)]
+    q = randn_f16((1, T, H, D_QK))
+    seq_len = torch.tensor([n_rows], dtype=torch.int32, device=dev)
+    out = torch.empty((1, T, H, D_V), dtype=torch.float32, device=dev)
+    ws = pkg.new_workspace(1, T, H, D_V, dev)
+
+    def step(i, ev=None):
+        pkg.mla_decode(q, caches[i % n_copies], seq_len, out=out, workspace=ws, max_seq_len=n_rows, ev_after_main=ev)
+
+    sampler.start()
+    sec = time_loop(step, args.steps, args.warmup)
+    value = world * bytes_step / sec / 1e9
+
+    # ---- roofline pass: the attention kernel alone, one event pair per step ------------------------
+    k_steps = min(args.steps, 200)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(k_steps)]
+    mids = [torch.cuda.Event(enable_timing=True) for _ in range(k_steps)]
+    for e in mids:
+        e.record()  # creates the underlying cudaEvent_t
+    torch.cuda.synchronize()
+    for i in range(k_steps):
+        starts[i].record()
+        step(args.warmup + i, ev=mids[i].cuda_event)
+    torch.cuda.synchronize()
+    kern_ms = [starts[i].elapsed_time(mids[i]) for i in range(k_steps)]
+    kern_sec = statistics.mean(kern_ms) * 1e-3
+    achieved = bytes_step / kern_sec / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        try:
+            with open(tpath) as f:
+                traffic = json.load(f).get("mtp_verify_32k_dram_bytes_per_launch")
+        except Exception:
+            traffic = None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": traffic, "peak_kind": peak_kind, "kernel": "decode attention kernel (combine excluded)",
+                "kernel_us": kern_sec * 1e6, "algorithmic_bytes_per_launch": bytes_step}
+
+    # ---- e2e: host buffers through the call-site mirror ---------------------------------------------
+    n_layers = n_copies
+    layers = []
+    for j in range(n_layers):
+        lay = pkg.MlaDecodeLayer(ctx=n_rows, H=H, T_max=T, device=dev)
+        lay.cache.copy_(caches[j])
+        layers.append(lay)
+    del caches
+    q_host = randn_f16((T, H, D_QK)).cpu().pin_memory()
+    kv_host = (torch.randn((T, D_QK), generator=gen, device=dev) * 0.5).cpu().pin_memory()
+    h2d = q_host.numel() * 2 + kv_host.numel() * 4 + 4
+    d2h = T * H * D_V * 4
+
+    def e2e_step(i):
+        lay = layers[i % n_layers]
+        lay.pos = n_rows - T  # the two new rows land at 32766, 32767; 32768 rows are attended
+        lay.step(q_host, kv_host)
+
+    e2e_steps = min(args.steps, 500)
+    for i in range(min(args.warmup, 20)):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_sec = max_over_ranks((time.perf_counter() - t0)) / e2e_steps
+    clocks = sampler.stop()
+    e2e = {"value": world * bytes_step / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "us_per_step": e2e_sec * 1e6, "steps": e2e_steps}
+    del layers
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations --------------------------------------------------------------------
+    others = {}
+    if not args.no_others:
+        try:
+            others = run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_peak, tf_peak, args)
+        except Exception as exc:  # keep the headline line even if an extra fails
+            others = {"error": f"{type(exc).__name__}: {exc}"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_decode_baseline(n_rows, T, budget_s=10.0)
+        cpu.pop("seconds_per_pass", None)
+
+    if rank == 0:
+        line = {
+            "metric": "MLA decode-attention HBM GB/s (MTP verify, 32K ctx)", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "mtp_verify_32k: batch 1, T=2 causal, H=20, d_qk=576, d_v=512, ctx=32768, "
+                                   "scale=1/16; one independent sequence per GPU",
+                       "l2": f"rotates over {n_copies} distinct cache copies ({n_copies * n_rows * D_QK * 2 >> 20} MiB "
+                             "> 2 x L2)"},
+            "e2e": e2e, "gpu_launches": 2 * args.steps, "launches_per_step": {"value": 2, "e2e": 3},
+            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "others": others,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_peak, tf_peak, args) -> dict:
+    res = {}
+    steps, warm = min(args.steps, 200), min(max(args.warmup, 3), 20)
+
+    # -- 128K context, T = 1: one GPU, or sharded by contiguous sequence ranges over all ranks --------
+    n_total = 131072
+    lo, hi = pkg.shard_rows(n_total, world, rank, 16)
+    rows_local = hi - lo
+    n_copies = max(2, -(-2 * L2_BYTES // max(1, rows_local * D_QK * 2)) + 1)
+    n_copies = min(n_copies, 24)
+    shards = [randn_f16((max(rows_local, 1), D_QK), 0.5) for _ in range(n_copies)]
+    q1 = randn_f16((1, 1, H, D_QK))
+    lens = torch.tensor([rows_local], dtype=torch.int32, device=dev)
+    ws = pkg.new_workspace(1, 1, H, D_V, dev)
+    rows_q = H
+    total_bytes = algorithmic_bytes(n_total, 1)
+    if world == 1:
+        o1 = torch.empty((1, 1, H, D_V), dtype=torch.float32, device=dev)
+        sec = time_loop(lambda i: pkg.mla_decode(q1, shards[i % n_copies], lens, out=o1, workspace=ws,
+                                                 max_seq_len=rows_local), steps, warm)
+        exchange = "none"
+    else:
+        block = torch.empty(pkg.part_floats(rows_q), dtype=torch.float32, device=dev)
+        gathered = torch.empty((world, block.numel()), dtype=torch.float32, device=dev)
+        o1 = torch.empty((rows_q, D_V), dtype=torch.float32, device=dev)
+
+        def sharded_step(i):
+            pkg.mla_decode(q1, shards[i % n_copies], lens, tail_causal=(rank == world - 1), want_out=False,
+                           part_out=block, workspace=ws, max_seq_len=rows_local)
+            dist.all_gather_into_tensor(gathered, block)
+            pkg.combine_parts(gathered, world, rows_q, D_V, out=o1)
+
+        sec = time_loop(sharded_step, steps, warm)
+        exchange = "nccl all_gather of (acc, m, l) records + local combine"
+    gbs = total_bytes / sec / 1e9
+    res["ctx128k_T1"] = {"metric": "aggregate GB/s", "value": gbs, "us_per_step": sec * 1e6, "scaling": "strong",
+                         "frac_of_hbm_per_gpu": gbs / world / hbm_peak, "exchange": exchange,
+                         "rows_per_gpu": rows_local, "bytes": total_bytes}
+    del shards
+    torch.cuda.empty_cache()
+
+    # -- 64 paged sequences, lengths U[1024, 65536], sharded across ranks longest-first ---------------
+    import numpy as np
+    rng = np.random.default_rng(5)
+    lens_all = rng.integers(1024, 65537, size=64)
+    owners, load = pkg.lpt_assign(lens_all.tolist(), world)
+    mine = owners[rank]
+    my_lens = lens_all[mine]
+    pages_per = -(-my_lens // 64)
+    n_pages = int(pages_per.sum()) + 4
+    pool = randn_f16((n_pages * 64, D_QK), 0.5)
+    perm = rng.permutation(n_pages)
+    pt = np.zeros((max(1, len(mine)), int(max(1, pages_per.max() if len(mine) else 1))), np.int32)
+    k = 0
+    for b in range(len(mine)):
+        pt[b, :pages_per[b]] = perm[k:k + pages_per[b]]
+        k += int(pages_per[b])
+    if len(mine):
+        ptd = torch.from_numpy(pt).to(dev)
+        ld = torch.from_numpy(my_lens.astype(np.int32)).to(dev)
+        qb = randn_f16((len(mine), 1, H, D_QK))
+        ob = torch.empty((len(mine), 1, H, D_V), dtype=torch.float32, device=dev)
+        wsb = pkg.new_workspace(len(mine), 1, H, D_V, dev)
+        fn = lambda i: pkg.mla_decode(qb, pool, ld, page_table=ptd, out=ob, workspace=wsb,
+                                      max_seq_len=int(my_lens.max()))
+    else:
+        fn = lambda i: None
+    sec = time_loop(fn, min(steps, 50), min(warm, 5))
+    tot = int(lens_all.sum()) * D_QK * 2 + 64 * H * (D_QK * 2 + D_V * 4)
+    res["paged64"] = {"metric": "aggregate GB/s", "value": tot / sec / 1e9, "us_per_step": sec * 1e6,
+                      "frac_of_hbm_per_gpu": tot / sec / 1e9 / world / hbm_peak, "scaling": "strong",
+                      "load_imbalance_max_over_mean": max(load) / (sum(load) / world), "bytes": tot,
+                      "l2": "pool per GPU exceeds L2 at 1-8 GPUs" if n_pages * 64 * D_QK * 2 > 2 * L2_BYTES
+                      else "pool smaller than 2 x L2"}
+    del pool
+    torch.cuda.empty_cache()
+
+    # -- causal prefill, 8192 tokens, 20 heads, d = 256 (replicas only; measured on every rank) -------
+    S, d = 8192, 256
+    Q, K, V = randn_f16((S, H, d)), randn_f16((S, H, d)), randn_f16((S, H, d))
+    pkg.rope_f16_inplace(Q)
+    pkg.rope_f16_inplace(K)
+    O = torch.empty((S, H, d), dtype=torch.float32, device=dev)
+    sec = time_loop(lambda i: pkg.prefill_attn(Q, K, V, out=O), min(steps, 20), 3)
+    flops = H * S * (S + 1) / 2 * (2 * d + 2 * d)
+    res["prefill8k"] = {"metric": "TFLOP/s (causal FLOPs)", "value": flops / sec / 1e12, "ms_per_step": sec * 1e3,
+                        "frac_of_tensor_peak": flops / sec / 1e12 / tf_peak, "flops": flops, "scaling": "replicas"}
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the 128K / paged / prefill extras")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

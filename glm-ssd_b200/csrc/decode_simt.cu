@@ -327,6 +327,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
         k_decode_gather<__half><<<grid, NT, smem, st>>>(P);
     }
     GS_TRY(cudaGetLastError());
+    if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     CombinePlan c;
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;

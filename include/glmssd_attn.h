@@ -68,6 +68,8 @@ typedef struct gs_mla_decode_args {
     int32_t max_seq_len;       /* host-side upper bound of seq_lens[] (sizing only; 0 = cache_rows) */
     int32_t impl;              /* 0 = automatic; 1 = force the CUDA-core gather kernel; 2 = force the
                                   tcgen05 kernel (returns cudaErrorInvalidValue if the shape is outside it) */
+    void *ev_after_main;       /* optional cudaEvent_t recorded on the stream between the attention kernel and
+                                  the combine kernel, so a caller can time the two apart; NULL = none */
 } gs_mla_decode_args;
 
 /* Bytes of workspace gs_mla_decode needs on the current device for these sizes (host function). */

@@ -1,0 +1,67 @@
+"""Generate the golden fixtures that pin the CPU oracle: outputs of the reference engine's own CUDA
+kernels (gs_mla_attn, gs_f32_to_f16), compiled unmodified into oracle/_ref/libglmssd_ref.so by
+oracle/build.py and run on a GPU.
+
+    python tests/golden/make_golden_from_ref.py <out_dir>
+
+writes ref_*.npz into <out_dir>; the committed copies live beside this script.  Inputs are seeded
+(numpy default_rng) so the run is reproducible.  Needs a CUDA device; not used at test time.
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libglmssd_ref.so")
+
+CASES = [  # name, seed, T, H, n, ctx, splits, dense
+    ("decode_dense", 101, 1, 16, 200, 256, 16, True),
+    ("mtp_verify", 102, 2, 32, 129, 160, 4, True),
+    ("sparse_list", 103, 3, 16, 100, 300, 4, False),
+    ("prefill_block", 104, 12, 16, 40, 64, 1, True),
+    ("empty_and_one", 105, 2, 16, 1, 32, 16, True),
+]
+
+
+def main(out_dir: str) -> None:
+    os.makedirs(out_dir, exist_ok=True)
+    ref = C.CDLL(REF_SO)
+    vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+    ref.gs_mla_attn.restype = i32
+    ref.gs_mla_attn.argtypes = [vp, vp, vp, vp, i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]
+    ref.gs_f32_to_f16.restype = i32
+    ref.gs_f32_to_f16.argtypes = [vp, vp, C.c_int64, vp]
+    for name, seed, T, H, n, ctx, splits, dense in CASES:
+        rng = np.random.default_rng(seed)
+        q = rng.standard_normal((T, H, 512), dtype=np.float32)
+        Cc = (rng.standard_normal((ctx, 512), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+        stride = n + 4
+        sel = np.zeros((T, stride), np.int32)
+        cnt = np.zeros(T, np.int32)
+        for t in range(T):
+            k = max(0, n - (T - 1 - t))
+            cnt[t] = k
+            sel[t, :k] = np.arange(k) if dense else rng.permutation(ctx)[:k]
+        qd, cd = torch.from_numpy(q).cuda(), torch.from_numpy(Cc).cuda()
+        sd, nd = torch.from_numpy(sel).cuda(), torch.from_numpy(cnt).cuda()
+        o = torch.zeros((T, H, 512), dtype=torch.float32, device="cuda")
+        part = torch.zeros(T * (H // 16) * splits * (16 * 512 + 32), dtype=torch.float32, device="cuda")
+        rc = ref.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), stride, nd.data_ptr(), 1 / 16,
+                             o.data_ptr(), part.data_ptr(), T, H, 512, splits, None)
+        assert rc == 0, rc
+        x = rng.standard_normal(2048, dtype=np.float32) * np.float32(10.0 ** rng.integers(-6, 4))
+        xd = torch.from_numpy(x).cuda()
+        yd = torch.zeros(2048, dtype=torch.float16, device="cuda")
+        assert ref.gs_f32_to_f16(xd.data_ptr(), yd.data_ptr(), 2048, None) == 0
+        torch.cuda.synchronize()
+        np.savez_compressed(os.path.join(out_dir, f"ref_{name}.npz"), q=q, C=Cc.view(np.uint16), sel=sel, cnt=cnt,
+                            scale=np.float32(1 / 16), o=o.cpu().numpy(), splits=np.int32(splits), append_x=x,
+                            append_y=yd.cpu().numpy().view(np.uint16))
+        print("wrote", name)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden"))
