@@ -1,6 +1,588 @@
-// placeholder until the tcgen05 decode kernel lands
+// Absorbed-MLA decode on the Blackwell tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// What it computes is the contract of the reference kernel (crates/cuda/kernels/ops.cu:420-424):
+// scores of every query row against the attended cache rows, softmax, and the probability-weighted
+// sum of the same rows' first d_v columns, emitted as split partials (unnormalised acc, m, l) that
+// the combine kernel merges (ops.cu:539-574).  How it computes it is specific to sm_100a:
+//
+//  * One persistent CTA per SM.  The 16-row units (64-row pages when paged) of all sequences are
+//    cut into equal contiguous chunks, one per CTA; the part of a sequence inside a chunk is a
+//    "segment" and yields one partial record.  The cache is read from HBM exactly once.
+//  * A producer warp streams 64-row cache tiles into a two-stage shared-memory ring with TMA
+//    (128-byte swizzle, one 64x64 box per 64-column block); the ragged last tile of a segment is
+//    fetched in 16-row boxes so no row outside the segment is read.
+//  * The contraction is small on the query side (T*H = 20..48 rows), so the cache rows fill the
+//    128-lane datapath and the packed query rows (all heads of all query tokens) ride on the MMA's
+//    N side:  S^T[64 x NQ] = C_tile[64 x d_qk] . Q^T   (M = 64 cache rows, K-major operands),
+//             O^T[128 x NQ] += V^T[128 x 64] . P^T     (M = 128 value columns; the SAME shared-memory
+//    tile, now read MN-major), with both accumulators in tensor memory.  Padding 20 query rows to
+//    the 64/128 rows of an M tile instead would spend 3-6x the tensor time on zeros and push the
+//    kernel from the HBM roofline to the tensor roofline.
+//  * A 4-warp group reads S^T from TMEM (one cache row per thread), does the online softmax with
+//    warp-shuffle column maxima and a lazily updated reference maximum (the O accumulators are
+//    rescaled only when a maximum grows by more than 2^6), writes P^T as f16 into shared memory in
+//    the canonical K-major layout, and at the end of a segment drains O^T from TMEM.
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the status word and leaves
+// through the common exit, which frees tensor memory.
+#include <string.h>
+
 #include "internal.cuh"
+#include "sm100_prims.cuh"
+
 namespace gs {
-bool decode_umma_supported(const DecodeProblem &, const char **why) { *why = "not built"; return false; }
-int launch_decode_umma(const DecodeProblem &, cudaStream_t) { return fail_invalid("tcgen05 decode not built"); }
+
+int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                       uint32_t box_rows, uint32_t box_cols, int swizzle) {
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    // looked up on every call: a cached pointer could go stale across a device reset
+    GS_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return (int) cudaErrorNotSupported;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = ((encode_fn) fn)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides,
+                                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, (CUtensorMapSwizzle) swizzle,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows %llu cols %llu box %ux%u)", (int) r,
+                  (unsigned long long) rows, (unsigned long long) cols, box_rows, box_cols);
+        return (int) cudaErrorInvalidValue;
+    }
+    return 0;
 }
+
+namespace {
+using namespace sm100;
+
+constexpr int TILE = 64;                 // cache rows per tile
+constexpr int BLK_BYTES = TILE * 128;    // one 64-column block of a tile: 64 rows x 128 B
+constexpr int NBLK_MAX = 9;              // 576 / 64
+constexpr int STAGE_BYTES = NBLK_MAX * BLK_BYTES;
+constexpr int STAGES = 2;
+constexpr int NTHREADS = 192;            // warp 0 producer, warp 1 MMA, warps 2-5 softmax group
+constexpr int TMEM_COLS = 512;
+constexpr int SLOT = 64;                 // TMEM column slot: S0, S1, then O tiles
+constexpr int O_COL0 = 2 * SLOT;
+constexpr int MAX_SEQ = 1024;
+constexpr float RESCALE_LOG2 = 6.0f;     // lazy rescale threshold, in log2 units
+constexpr float LN2 = 0.6931471805599453f;
+
+// status codes (bit flags) left in the workspace when a bounded wait gives up
+enum { ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 4 };
+
+struct UmmaParams {
+    CUtensorMap tm_kv64, tm_kv16, tm_q;
+    const int32_t *seq_lens, *seq_base, *page_table;
+    int page_table_stride, paged;
+    float scale_log2;
+    int tail_causal;
+    float *ws_acc, *ws_ml;
+    int2 *ws_desc;
+    int32_t *status;
+    int n_seq, T, H, rows_q, nblk, n_vtiles, d_v;
+};
+
+struct Barriers {
+    uint64_t kv_full[STAGES], kv_empty[STAGES];
+    uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t q_full, q_empty, o_full, o_empty;
+};
+
+template <int NQ>
+struct Smem {
+    static constexpr int Q_BYTES = NBLK_MAX * NQ * 128;
+    static constexpr int P_BYTES = NQ * TILE * 2;
+    static constexpr int OFF_Q = STAGES * STAGE_BYTES;
+    static constexpr int OFF_P = OFF_Q + Q_BYTES;
+    static constexpr int OFF_MISC = OFF_P + 2 * P_BYTES;
+    struct Misc {
+        Barriers bar;
+        uint32_t tmem_base;
+        int abort_flag;
+        int flag[2];
+        int cum[MAX_SEQ + 1];
+        float smax[4][NQ];
+        float sl[4][NQ];
+        float mref[NQ];
+        float f[NQ];
+        int lim[NQ];
+    };
+    static constexpr int TOTAL = OFF_MISC + (int) sizeof(Misc) + 1024;  // + slack for the 1024-byte alignment
+};
+
+struct Segment {
+    int b, r0, r1, len, n_tiles, seg_id;
+};
+
+// Walks the segments of this CTA's unit range [pos, end); `b` is a cursor over sequences.
+__device__ __forceinline__ bool next_segment(int &pos, int &b, int end, const int *cum, int unit_rows,
+                                             const int32_t *seq_lens, Segment &sg) {
+    if (pos >= end) return false;
+    while (cum[b + 1] <= pos) b++;
+    const int u_lo = pos - cum[b];
+    const int u_hi = min(end, cum[b + 1]) - cum[b];
+    sg.b = b;
+    sg.len = seq_lens[b];
+    sg.r0 = u_lo * unit_rows;
+    sg.r1 = min(sg.len, u_hi * unit_rows);
+    sg.n_tiles = (sg.r1 - sg.r0 + TILE - 1) / TILE;
+    sg.seg_id = blockIdx.x + b;
+    pos = cum[b] + u_hi;
+    return true;
+}
+
+template <int NQ>
+__global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
+    using SM = Smem<NQ>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    uint8_t *kv_smem = smem;
+    uint8_t *q_smem = smem + SM::OFF_Q;
+    uint8_t *p_smem = smem + SM::OFF_P;
+    typename SM::Misc &M = *reinterpret_cast<typename SM::Misc *>(smem + SM::OFF_MISC);
+    Barriers &B = M.bar;
+    volatile int *abort_flag = &M.abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int unit_rows = P.paged ? TILE : 16;
+    const int nblk = P.nblk;
+
+    // ---- set-up: barriers, tensor memory, the unit schedule -------------------------------------------
+    if (tid == 0) {
+        tma_prefetch_desc(&P.tm_kv64);
+        tma_prefetch_desc(&P.tm_kv16);
+        tma_prefetch_desc(&P.tm_q);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&B.kv_full[s], 1);
+            mbar_init(&B.kv_empty[s], 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&B.s_full[s], 1);
+            mbar_init(&B.s_empty[s], 4);
+            mbar_init(&B.p_full[s], 4);
+            mbar_init(&B.p_empty[s], 1);
+        }
+        mbar_init(&B.q_full, 1);
+        mbar_init(&B.q_empty, 1);
+        mbar_init(&B.o_full, 1);
+        mbar_init(&B.o_empty, 4);
+        M.abort_flag = 0;
+        M.flag[0] = M.flag[1] = 0;
+        M.cum[0] = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&M.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    for (int b = tid; b < P.n_seq; b += NTHREADS) {
+        const int len = max(P.seq_lens[b], 0);
+        M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {  // inclusive scan of cum[1..n_seq], 32 entries per step
+        int carry = 0;
+        for (int base = 1; base <= P.n_seq; base += 32) {
+            const int i = base + lane;
+            int v = i <= P.n_seq ? M.cum[i] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
+            }
+            v += carry;
+            if (i <= P.n_seq) M.cum[i] = v;
+            carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = M.tmem_base;
+    const int total = M.cum[P.n_seq];
+    const int chunk = (total + (int) gridDim.x - 1) / (int) gridDim.x;
+    const int start = min(total, (int) blockIdx.x * chunk);
+    const int end = min(total, start + chunk);
+    if (blockIdx.x == 0) {  // where the combine kernel finds each sequence's segments
+        for (int b = tid; b < P.n_seq; b += NTHREADS) {
+            const int u0 = M.cum[b], u1 = M.cum[b + 1];
+            int2 d = make_int2(0, 0);
+            if (u1 > u0) {
+                const int c_first = u0 / chunk, c_last = (u1 - 1) / chunk;
+                d = make_int2(c_first + b, c_last - c_first + 1);
+            }
+            P.ws_desc[b] = d;
+        }
+    }
+    // first sequence of this CTA's range (binary search: largest b with cum[b] <= start)
+    int b_cur = 0;
+    {
+        int lo = 0, hi = P.n_seq - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (M.cum[mid] <= start) lo = mid; else hi = mid - 1;
+        }
+        b_cur = lo;
+    }
+    int pos = start;
+    uint32_t it = 0, sgc = 0;  // running tile and segment counters (identical in every role)
+    Segment sg;
+
+    if (warp == 0) {
+        // =================================== TMA producer ==================================================
+        if (lane == 0) {
+            bool ok = true;
+            while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
+                ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&B.q_full, (uint32_t) (nblk * NQ * 128));
+                for (int k = 0; k < nblk; k++)
+                    tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
+                const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
+                for (int j = 0; j < sg.n_tiles; j++, it++) {
+                    const int s = it & 1;
+                    ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+                    if (!ok) break;
+                    const int row = sg.r0 + j * TILE;
+                    const int valid = min(TILE, sg.r1 - row);
+                    uint8_t *dst = kv_smem + s * STAGE_BYTES;
+                    if (P.paged) {
+                        const int page = P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE];
+                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (nblk * BLK_BYTES));
+                        for (int k = 0; k < nblk; k++)
+                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, page * TILE);
+                    } else if (valid == TILE) {
+                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (nblk * BLK_BYTES));
+                        for (int k = 0; k < nblk; k++)
+                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, (int) (base_row + row));
+                    } else {
+                        const int ng = (valid + 15) >> 4;
+                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (ng * nblk * 2048));
+                        for (int g = 0; g < ng; g++)
+                            for (int k = 0; k < nblk; k++)
+                                tma_load_2d(dst + k * BLK_BYTES + g * 2048, &P.tm_kv16, &B.kv_full[s], k * 64,
+                                            (int) (base_row + row + g * 16));
+                    }
+                }
+                sgc++;
+            }
+        }
+    } else if (warp == 1) {
+        // =================================== MMA issuer ======================================================
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 0);
+            const uint32_t q_addr = smem_u32(q_smem), p_addr0 = smem_u32(p_smem), kv_addr0 = smem_u32(kv_smem);
+            bool ok = true;
+            while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
+                ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
+                for (int j = 0; ok && j < sg.n_tiles; j++, it++) {
+                    const int s = it & 1;
+                    const uint32_t ph = (it >> 1) & 1;
+                    const uint32_t kv_addr = kv_addr0 + s * STAGE_BYTES;
+                    // S^T = C_tile . Q^T
+                    ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
+                         mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
+                    if (!ok) break;
+                    tc_fence_after();
+                    for (int k = 0; k < nblk; k++) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ks++) {
+                            const uint64_t a = make_smem_desc(kv_addr + k * BLK_BYTES + ks * 32, 16, 1024, kSwizzle128B);
+                            const uint64_t bq = make_smem_desc(q_addr + k * NQ * 128 + ks * 32, 16, 1024, kSwizzle128B);
+                            umma_ss(tmem + s * SLOT, a, bq, idesc_s, (k | ks) != 0);
+                        }
+                    }
+                    umma_commit(&B.s_full[s]);
+                    // O^T += V^T . P^T
+                    ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
+                    if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
+                    const int nk = (valid + 15) >> 4;
+                    const uint32_t p_addr = p_addr0 + s * SM::P_BYTES;
+                    for (int mt = 0; mt < P.n_vtiles; mt++) {
+                        for (int ks = 0; ks < nk; ks++) {
+                            const uint64_t a = make_smem_desc(kv_addr + 2 * mt * BLK_BYTES + ks * 2048, BLK_BYTES, 1024,
+                                                              kSwizzle128B);
+                            const uint64_t bp = make_smem_desc(p_addr + ks * 256, 128, 1024, kSwizzleNone);
+                            umma_ss(tmem + O_COL0 + mt * SLOT, a, bp, idesc_pv, j > 0 || ks > 0);
+                        }
+                    }
+                    umma_commit(&B.kv_empty[s]);
+                    umma_commit(&B.p_empty[s]);
+                    if (j == sg.n_tiles - 1) {
+                        umma_commit(&B.o_full);
+                        umma_commit(&B.q_empty);
+                    }
+                }
+                sgc++;
+            }
+        }
+    } else {
+        // =================================== softmax / epilogue group ==========================================
+        const int wg_tid = tid - 64;
+        const int qt = warp & 3;                      // TMEM lane quarter this warp may touch
+        const uint32_t lane_base = (uint32_t) (qt * 32) << 16;
+        const int row_in_tile = qt * 16 + lane;       // S^T row of this thread (lanes 0..15 only)
+        const bool has_row = lane < 16;
+        float l_part[NQ];
+        bool ok = true;
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
+            if (wg_tid < NQ) {
+                const int q = wg_tid, t = q / P.H;
+                int lim = 0;
+                if (q < P.rows_q) lim = P.tail_causal ? min(sg.r1, sg.len - (P.T - 1 - t)) : sg.r1;
+                M.lim[q] = lim;
+                M.mref[q] = -INFINITY;
+            }
+#pragma unroll
+            for (int q = 0; q < NQ; q++) l_part[q] = 0.f;
+            named_bar_sync(1, 128);
+            for (int j = 0; j < sg.n_tiles; j++, it++) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                (void) mbar_wait(&B.s_full[s], ph, abort_flag, P.status, ST_SOFTMAX);
+                // uniform exit: every thread of the group takes the same branch after this barrier
+                named_bar_sync(2, 128);
+                if (*abort_flag) { ok = false; break; }
+                tc_fence_after();
+                float sv[NQ];
+#pragma unroll
+                for (int c = 0; c < NQ / 16; c++) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + lane_base + s * SLOT + c * 16, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) sv[c * 16 + i] = __uint_as_float(r[i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&B.s_empty[s]);
+                const int rpos = sg.r0 + j * TILE + row_in_tile;
+                // masked, scaled scores and the column maxima over this warp's 16 rows
+#pragma unroll
+                for (int q = 0; q < NQ; q++) {
+                    const float v = (has_row && rpos < M.lim[q]) ? sv[q] * P.scale_log2 : -INFINITY;
+                    sv[q] = v;
+                    float mx = v;
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    if (lane == 0) M.smax[qt][q] = mx;
+                }
+                named_bar_sync(1, 128);
+                if (wg_tid < NQ) {
+                    const int q = wg_tid;
+                    const float mt = fmaxf(fmaxf(M.smax[0][q], M.smax[1][q]), fmaxf(M.smax[2][q], M.smax[3][q]));
+                    const float mr = M.mref[q];
+                    float f = 1.f;
+                    if (mt > mr + RESCALE_LOG2 || (mr == -INFINITY && mt > -INFINITY)) {
+                        if (mr == -INFINITY) {
+                            f = 0.f;
+                        } else {
+                            f = exp2f(mr - mt);
+                            if (j > 0) M.flag[it & 1] = 1;  // accumulators hold data scaled by the old reference
+                        }
+                        M.mref[q] = mt;
+                    }
+                    M.f[q] = f;
+                }
+                if (wg_tid == 0) M.flag[(it + 1) & 1] = 0;
+                named_bar_sync(2, 128);
+                const bool rescale = M.flag[it & 1] != 0;
+                // (a failed wait raises the shared abort flag; the group leaves together after the next barrier)
+                (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, P.status, ST_SOFTMAX);
+                // probabilities: row sums in registers, P^T (f16) into the K-major operand layout
+                __half *pbuf = reinterpret_cast<__half *>(p_smem + s * SM::P_BYTES);
+                const int p_off = (row_in_tile >> 3) * 64 + (row_in_tile & 7);  // in halves; + (q/8)*512 + (q%8)*8
+#pragma unroll
+                for (int q = 0; q < NQ; q++) {
+                    const float p = sv[q] == -INFINITY ? 0.f : exp2f(sv[q] - M.mref[q]);
+                    l_part[q] = l_part[q] * M.f[q] + p;
+                    if (has_row) pbuf[(q >> 3) * 512 + (q & 7) * 8 + p_off] = __float2half_rn(p);
+                }
+                if (rescale) {
+                    // S(it) has completed, so every earlier MMA, PV(it-1) included, has completed too
+                    for (int mt = 0; mt < P.n_vtiles; mt++) {
+#pragma unroll
+                        for (int c = 0; c < NQ / 16; c++) {
+                            uint32_t r[16];
+                            const uint32_t addr = tmem + lane_base + O_COL0 + mt * SLOT + c * 16;
+                            tmem_ld16(addr, r);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 16; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * M.f[c * 16 + i]);
+                            tmem_st16(addr, r);
+                        }
+                    }
+                    tmem_wait_st();
+                }
+                // rows of the last 16-row group past the segment's end must not feed NaNs into P.V
+                const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
+                if (valid & 15) {
+                    const int r_lo = valid, r_hi = (valid + 15) & ~15;
+                    const int n_vec = (r_hi - r_lo) * nblk * 8;  // 16-byte vectors
+                    uint8_t *stage = kv_smem + s * STAGE_BYTES;
+                    for (int i = wg_tid; i < n_vec; i += 128) {
+                        const int v = i & 7, rk = i >> 3;
+                        const int k = rk % nblk, r = r_lo + rk / nblk;
+                        *reinterpret_cast<uint4 *>(stage + k * BLK_BYTES + r * 128 + v * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                fence_proxy_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&B.p_full[s]);
+            }
+            if (!ok) break;
+            // ---- end of segment: drain the accumulators into this segment's partial record ----------------
+            (void) mbar_wait(&B.o_full, sgc & 1, abort_flag, P.status, ST_SOFTMAX);
+            named_bar_sync(2, 128);
+            if (*abort_flag) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int q = 0; q < NQ; q++) {
+                float v = has_row ? l_part[q] : 0.f;
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                if (lane == 0) M.sl[qt][q] = v;
+            }
+            named_bar_sync(1, 128);
+            if (wg_tid < P.rows_q) {
+                const int q = wg_tid;
+                const float m = M.mref[q];
+                float *ml = P.ws_ml + ((int64_t) sg.seg_id * P.rows_q + q) * 2;
+                ml[0] = m == -INFINITY ? -INFINITY : m * LN2;
+                ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
+            }
+            float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
+            for (int mt = 0; mt < P.n_vtiles; mt++) {
+#pragma unroll
+                for (int c = 0; c < NQ / 16; c++) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + lane_base + O_COL0 + mt * SLOT + c * 16, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int q = c * 16 + i;
+                        if (q < P.rows_q) acc[(int64_t) q * P.d_v + mt * 128] = __uint_as_float(r[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&B.o_empty);
+            sgc++;
+        }
+    }
+
+    // ---- common exit -----------------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) {
+        // loads that were issued but never consumed may still be landing in this CTA's shared memory
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int NQ>
+int launch_nq(const UmmaParams &P, int grid, cudaStream_t st) {
+    const int smem = Smem<NQ>::TOTAL;
+    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    k_decode_umma<NQ><<<grid, NTHREADS, smem, st>>>(P);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+bool decode_umma_supported(const DecodeProblem &p, const char **why) {
+    if (p.q_is_f32) { *why = "f32 queries"; return false; }
+    if (p.sel) { *why = "explicit position lists"; return false; }
+    if (p.d_qk % 64 != 0 || p.d_qk < 64 || p.d_qk > 576) { *why = "d_qk must be a multiple of 64 up to 576"; return false; }
+    if (p.d_v % 128 != 0 || p.d_v > 512 || p.d_v > p.d_qk) { *why = "d_v must be a multiple of 128 up to min(512, d_qk)"; return false; }
+    if (p.T * p.H > 48) { *why = "more than 48 query rows per sequence"; return false; }
+    if (p.n_seq > MAX_SEQ) { *why = "more than 1024 sequences"; return false; }
+    if (p.page_table && p.page_rows != TILE) { *why = "page size other than 64"; return false; }
+    if ((reinterpret_cast<uintptr_t>(p.q) & 15) || (reinterpret_cast<uintptr_t>(p.cache) & 15)) { *why = "q and cache must be 16-byte aligned"; return false; }
+    if ((int64_t) p.n_seq * p.T * p.H >= (1ll << 31) || p.cache_rows >= (1ll << 31)) { *why = "row counts beyond 2^31"; return false; }
+    return true;
+}
+
+int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
+    const int rows_q = p.T * p.H;
+    const int NQ = rows_q <= 32 ? 32 : 48;
+    UmmaParams P;
+    memset(&P, 0, sizeof(P));
+    const int kSw128 = (int) CU_TENSOR_MAP_SWIZZLE_128B;
+    if (int e = encode_tmap_2d_f16(&P.tm_kv64, p.cache, (uint64_t) p.cache_rows, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
+                                   TILE, 64, kSw128)) return e;
+    if (int e = encode_tmap_2d_f16(&P.tm_kv16, p.cache, (uint64_t) p.cache_rows, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
+                                   16, 64, kSw128)) return e;
+    if (int e = encode_tmap_2d_f16(&P.tm_q, p.q, (uint64_t) p.n_seq * rows_q, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
+                                   (uint32_t) NQ, 64, kSw128)) return e;
+    P.seq_lens = p.seq_lens;
+    P.seq_base = p.seq_base;
+    P.page_table = p.page_table;
+    P.page_table_stride = p.page_table_stride;
+    P.paged = p.page_table != nullptr;
+    P.scale_log2 = p.scale * 1.4426950408889634f;
+    P.tail_causal = p.tail_causal;
+    P.ws_acc = p.ws_acc;
+    P.ws_ml = p.ws_ml;
+    P.ws_desc = p.ws_desc;
+    P.status = p.status;
+    P.n_seq = p.n_seq;
+    P.T = p.T;
+    P.H = p.H;
+    P.rows_q = rows_q;
+    P.nblk = p.d_qk / 64;
+    P.n_vtiles = p.d_v / 128;
+    P.d_v = p.d_v;
+    int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
+    if (grid < 1) grid = 1;
+    if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
+    if (NQ == 32) {
+        if (int e = launch_nq<32>(P, grid, st)) return e;
+    } else {
+        if (int e = launch_nq<48>(P, grid, st)) return e;
+    }
+    if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
+    CombinePlan c;
+    c.acc = p.ws_acc;
+    c.ml = p.ws_ml;
+    c.desc = p.ws_desc;
+    c.regular_segments = 0;
+    c.seg_stride_acc = (int64_t) rows_q * p.d_v;
+    c.seg_stride_ml = (int64_t) rows_q * 2;
+    c.n_seq = p.n_seq;
+    c.T = p.T;
+    c.H = p.H;
+    c.d_v = p.d_v;
+    c.o = p.o;
+    c.part_out = p.part_out;
+    return launch_combine(c, st);
+}
+
+}  // namespace gs

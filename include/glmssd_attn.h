@@ -62,7 +62,8 @@ typedef struct gs_mla_decode_args {
     float *part_out;           /* optional: one merged (acc, m, l) record per query row instead of / besides
                                   o, for a cross-GPU combine: floats [rows*d_v acc][rows*2 (m,l)],
                                   rows = n_seq*T*H; the unnormalised form of ops.cu:539-549 */
-    void *workspace;           /* gs_mla_decode_workspace_bytes() bytes */
+    void *workspace;           /* gs_mla_decode_workspace_bytes() bytes, 256-byte aligned; zero it once after
+                                  allocating (its first word is a sticky status the kernels only OR into) */
     int64_t workspace_bytes;
     int32_t n_seq, T, H, d_qk, d_v;
     int32_t max_seq_len;       /* host-side upper bound of seq_lens[] (sizing only; 0 = cache_rows) */
