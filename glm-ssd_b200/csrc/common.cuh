@@ -29,12 +29,18 @@ inline int fail_invalid(const char *what) {
     } while (0)
 
 // ---- decode workspace layout -------------------------------------------------------------------
-// [0, 256)                 status block: int32 status word, then spare
-// [256, ...)               partial accumulators f32 [n_segments][rows_q][d_v]
+// [0, 4096)                status block: int32 status word (sticky, kernels only OR into it);
+//                           int32 at byte 4: when non-zero, CTA 0 of the tcgen05 kernel writes clock64
+//                           stamps of its first tiles as int64 from byte 256 on (a tuning aid, off by default)
+// [4096, ...)              per-sequence segment descriptors, then
+//                           partial accumulators f32 [n_segments][rows_q][d_v]
 // then                     partial (m, l)       f32 [n_segments][rows_q][2]
 // A "segment" is the share of one sequence handled by one CTA (tcgen05 kernel: at most
 // n_ctas + n_seq of them) or one (sequence, token, split) triple (CUDA-core kernel).
-constexpr int kStatusBytes = 256;
+constexpr int kStatusBytes = 4096;
+constexpr int kProfOffsetBytes = 256;
+constexpr int kProfSlots = 16;   // stamps per tile
+constexpr int kProfTiles = 24;   // tiles recorded
 constexpr int kMaxCtas = 160;       // persistent grid never exceeds this (B200 has 148 SMs)
 constexpr int kSimtMaxSplits = 64;  // CUDA-core kernel: splits per (sequence, token)
 

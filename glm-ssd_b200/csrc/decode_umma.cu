@@ -72,12 +72,16 @@ constexpr int NTHREADS = 192;            // warp 0 producer, warp 1 MMA, warps 2
 constexpr int TMEM_COLS = 512;
 constexpr int SLOT = 64;                 // TMEM column slot: S0, S1, then O tiles
 constexpr int O_COL0 = 2 * SLOT;
+constexpr int NVT = 4;                   // 128-column value tiles (d_v = 512)
 constexpr int MAX_SEQ = 1024;
 constexpr float RESCALE_LOG2 = 6.0f;     // lazy rescale threshold, in log2 units
 constexpr float LN2 = 0.6931471805599453f;
 
 // status codes (bit flags) left in the workspace when a bounded wait gives up
 enum { ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 4 };
+// clock-stamp slots (tuning aid)
+enum { PF_LOAD_ISSUE = 0, PF_KV_FULL = 1, PF_S_ISSUED = 2, PF_S_FULL = 3, PF_S_LOADED = 4, PF_VOTED = 5,
+       PF_P_WRITTEN = 6, PF_P_FULL_SEEN = 7, PF_PV_ISSUED = 8, PF_SLOW_PATH = 9 };
 
 struct UmmaParams {
     CUtensorMap tm_kv64, tm_kv16, tm_q;
@@ -88,7 +92,7 @@ struct UmmaParams {
     float *ws_acc, *ws_ml;
     int2 *ws_desc;
     int32_t *status;
-    int n_seq, T, H, rows_q, nblk, n_vtiles, d_v;
+    int n_seq, T, H, rows_q, d_v;
 };
 
 struct Barriers {
@@ -140,7 +144,23 @@ __device__ __forceinline__ bool next_segment(int &pos, int &b, int end, const in
     return true;
 }
 
-template <int NQ>
+// barrier among the softmax group that also ORs a predicate over its threads
+__device__ __forceinline__ bool group_any(int id, int n_threads, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, r;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.or.pred r, %2, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, r;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"((uint32_t) pred), "r"(id), "r"(n_threads)
+        : "memory");
+    return out != 0;
+}
+
+template <int NQ, int NBLK>
 __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
     using SM = Smem<NQ>;
     extern __shared__ uint8_t smem_raw[];
@@ -154,7 +174,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit_rows = P.paged ? TILE : 16;
-    const int nblk = P.nblk;
+
+    // optional clock stamps of CTA 0's first tiles
+    long long *prof = nullptr;
+    if (blockIdx.x == 0 && P.status[1] != 0)
+        prof = reinterpret_cast<long long *>(reinterpret_cast<char *>(P.status) + kProfOffsetBytes);
+#define GS_STAMP(tile, slot)                                                                     \
+    do {                                                                                         \
+        if (prof && (tile) < (uint32_t) kProfTiles) prof[(tile) * kProfSlots + (slot)] = clock64(); \
+    } while (0)
 
     // ---- set-up: barriers, tensor memory, the unit schedule -------------------------------------------
     if (tid == 0) {
@@ -190,7 +218,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {  // inclusive scan of cum[1..n_seq], 32 entries per step
+    if (warp == 0 && P.n_seq > 1) {  // inclusive scan of cum[1..n_seq], 32 entries per step
         int carry = 0;
         for (int base = 1; base <= P.n_seq; base += 32) {
             const int i = base + lane;
@@ -205,11 +233,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             carry = __shfl_sync(0xffffffffu, v, 31);
         }
     }
-    __syncthreads();
+    if (P.n_seq > 1) __syncthreads();
     tc_fence_after();
     const uint32_t tmem = M.tmem_base;
     const int total = M.cum[P.n_seq];
-    const int chunk = (total + (int) gridDim.x - 1) / (int) gridDim.x;
+    const int chunk = max(1, (total + (int) gridDim.x - 1) / (int) gridDim.x);
     const int start = min(total, (int) blockIdx.x * chunk);
     const int end = min(total, start + chunk);
     if (blockIdx.x == 0) {  // where the combine kernel finds each sequence's segments
@@ -244,33 +272,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
                 ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&B.q_full, (uint32_t) (nblk * NQ * 128));
-                for (int k = 0; k < nblk; k++)
+                mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * NQ * 128));
+#pragma unroll
+                for (int k = 0; k < NBLK; k++)
                     tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
                 const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
                 for (int j = 0; j < sg.n_tiles; j++, it++) {
                     const int s = it & 1;
                     ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
                     if (!ok) break;
+                    GS_STAMP(it, PF_LOAD_ISSUE);
                     const int row = sg.r0 + j * TILE;
                     const int valid = min(TILE, sg.r1 - row);
                     uint8_t *dst = kv_smem + s * STAGE_BYTES;
-                    if (P.paged) {
-                        const int page = P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE];
-                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (nblk * BLK_BYTES));
-                        for (int k = 0; k < nblk; k++)
-                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, page * TILE);
-                    } else if (valid == TILE) {
-                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (nblk * BLK_BYTES));
-                        for (int k = 0; k < nblk; k++)
-                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, (int) (base_row + row));
+                    if (P.paged || valid == TILE) {
+                        const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE] * TILE
+                                                 : (int) (base_row + row);
+                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (NBLK * BLK_BYTES));
+#pragma unroll
+                        for (int k = 0; k < NBLK; k++)
+                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, grow);
                     } else {
                         const int ng = (valid + 15) >> 4;
-                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (ng * nblk * 2048));
-                        for (int g = 0; g < ng; g++)
-                            for (int k = 0; k < nblk; k++)
+                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (ng * NBLK * 2048));
+                        for (int g = 0; g < ng; g++) {
+#pragma unroll
+                            for (int k = 0; k < NBLK; k++)
                                 tma_load_2d(dst + k * BLK_BYTES + g * 2048, &P.tm_kv16, &B.kv_full[s], k * 64,
                                             (int) (base_row + row + g * 16));
+                        }
                     }
                 }
                 sgc++;
@@ -279,44 +309,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     } else if (warp == 1) {
         // =================================== MMA issuer ======================================================
         if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);
-            constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 0);
-            const uint32_t q_addr = smem_u32(q_smem), p_addr0 = smem_u32(p_smem), kv_addr0 = smem_u32(kv_smem);
+            constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);    // A, B K-major
+            constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 1);  // A (V^T) and B (P^T) MN-major
+            // descriptors with a zero start address; the start address (>> 4) is added per instruction
+            const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);         // cache tile / Q, K-major
+            const uint64_t d_vt = make_smem_desc(0, BLK_BYTES, 1024, kSwizzle128B);    // cache tile, MN-major
+            const uint64_t d_pt = make_smem_desc(0, 128, 1024, kSwizzleNone);          // P^T, MN-major
+            const uint32_t q_lo = smem_u32(q_smem) >> 4, p_lo0 = smem_u32(p_smem) >> 4, kv_lo0 = smem_u32(kv_smem) >> 4;
             bool ok = true;
             while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
                 ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
                 for (int j = 0; ok && j < sg.n_tiles; j++, it++) {
                     const int s = it & 1;
                     const uint32_t ph = (it >> 1) & 1;
-                    const uint32_t kv_addr = kv_addr0 + s * STAGE_BYTES;
+                    const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
                     // S^T = C_tile . Q^T
                     ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
                          mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
                     if (!ok) break;
+                    GS_STAMP(it, PF_KV_FULL);
                     tc_fence_after();
-                    for (int k = 0; k < nblk; k++) {
+#pragma unroll
+                    for (int k = 0; k < NBLK; k++) {
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++) {
-                            const uint64_t a = make_smem_desc(kv_addr + k * BLK_BYTES + ks * 32, 16, 1024, kSwizzle128B);
-                            const uint64_t bq = make_smem_desc(q_addr + k * NQ * 128 + ks * 32, 16, 1024, kSwizzle128B);
-                            umma_ss(tmem + s * SLOT, a, bq, idesc_s, (k | ks) != 0);
+                            umma_ss(tmem + s * SLOT, d_kmaj + (kv_lo + k * (BLK_BYTES >> 4) + ks * 2),
+                                    d_kmaj + (q_lo + k * (NQ * 128 >> 4) + ks * 2), idesc_s, (k | ks) != 0);
                         }
                     }
                     umma_commit(&B.s_full[s]);
+                    GS_STAMP(it, PF_S_ISSUED);
                     // O^T += V^T . P^T
                     ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
                     if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
                     if (!ok) break;
+                    GS_STAMP(it, PF_P_FULL_SEEN);
                     tc_fence_after();
                     const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
                     const int nk = (valid + 15) >> 4;
-                    const uint32_t p_addr = p_addr0 + s * SM::P_BYTES;
-                    for (int mt = 0; mt < P.n_vtiles; mt++) {
-                        for (int ks = 0; ks < nk; ks++) {
-                            const uint64_t a = make_smem_desc(kv_addr + 2 * mt * BLK_BYTES + ks * 2048, BLK_BYTES, 1024,
-                                                              kSwizzle128B);
-                            const uint64_t bp = make_smem_desc(p_addr + ks * 256, 128, 1024, kSwizzleNone);
-                            umma_ss(tmem + O_COL0 + mt * SLOT, a, bp, idesc_pv, j > 0 || ks > 0);
+                    const uint32_t p_lo = p_lo0 + s * (SM::P_BYTES >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        if (ks < nk) {
+#pragma unroll
+                            for (int mt = 0; mt < NVT; mt++) {
+                                umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128),
+                                        d_pt + (p_lo + ks * 16), idesc_pv, j > 0 || ks > 0);
+                            }
                         }
                     }
                     umma_commit(&B.kv_empty[s]);
@@ -325,6 +364,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         umma_commit(&B.o_full);
                         umma_commit(&B.q_empty);
                     }
+                    GS_STAMP(it, PF_PV_ISSUED);
                 }
                 sgc++;
             }
@@ -346,6 +386,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 M.lim[q] = lim;
                 M.mref[q] = -INFINITY;
             }
+            // rows below lim_min are attended by every query row of the sequence
+            const int lim_min = P.tail_causal ? min(sg.r1, sg.len - (P.T - 1)) : sg.r1;
 #pragma unroll
             for (int q = 0; q < NQ; q++) l_part[q] = 0.f;
             named_bar_sync(1, 128);
@@ -353,9 +395,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
                 (void) mbar_wait(&B.s_full[s], ph, abort_flag, P.status, ST_SOFTMAX);
-                // uniform exit: every thread of the group takes the same branch after this barrier
-                named_bar_sync(2, 128);
-                if (*abort_flag) { ok = false; break; }
+                GS_STAMP(it, PF_S_FULL);
                 tc_fence_after();
                 float sv[NQ];
 #pragma unroll
@@ -369,53 +409,95 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B.s_empty[s]);
-                const int rpos = sg.r0 + j * TILE + row_in_tile;
-                // masked, scaled scores and the column maxima over this warp's 16 rows
+                GS_STAMP(it, PF_S_LOADED);
+                const int row0 = sg.r0 + j * TILE;
+                const int rpos = row0 + row_in_tile;
+                // scaled (and, on boundary tiles, masked) scores; does any exceed its reference by the threshold?
+                bool exceed = false;
+                if (row0 + TILE <= lim_min) {
 #pragma unroll
-                for (int q = 0; q < NQ; q++) {
-                    const float v = (has_row && rpos < M.lim[q]) ? sv[q] * P.scale_log2 : -INFINITY;
-                    sv[q] = v;
-                    float mx = v;
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    if (lane == 0) M.smax[qt][q] = mx;
-                }
-                named_bar_sync(1, 128);
-                if (wg_tid < NQ) {
-                    const int q = wg_tid;
-                    const float mt = fmaxf(fmaxf(M.smax[0][q], M.smax[1][q]), fmaxf(M.smax[2][q], M.smax[3][q]));
-                    const float mr = M.mref[q];
-                    float f = 1.f;
-                    if (mt > mr + RESCALE_LOG2 || (mr == -INFINITY && mt > -INFINITY)) {
-                        if (mr == -INFINITY) {
-                            f = 0.f;
-                        } else {
-                            f = exp2f(mr - mt);
-                            if (j > 0) M.flag[it & 1] = 1;  // accumulators hold data scaled by the old reference
-                        }
-                        M.mref[q] = mt;
+                    for (int q = 0; q < NQ; q++) {
+                        const float v = has_row ? sv[q] * P.scale_log2 : -INFINITY;
+                        sv[q] = v;
+                        exceed |= v > M.mref[q] + RESCALE_LOG2;
                     }
-                    M.f[q] = f;
-                }
-                if (wg_tid == 0) M.flag[(it + 1) & 1] = 0;
-                named_bar_sync(2, 128);
-                const bool rescale = M.flag[it & 1] != 0;
-                // (a failed wait raises the shared abort flag; the group leaves together after the next barrier)
-                (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, P.status, ST_SOFTMAX);
-                // probabilities: row sums in registers, P^T (f16) into the K-major operand layout
-                __half *pbuf = reinterpret_cast<__half *>(p_smem + s * SM::P_BYTES);
-                const int p_off = (row_in_tile >> 3) * 64 + (row_in_tile & 7);  // in halves; + (q/8)*512 + (q%8)*8
+                } else {
 #pragma unroll
-                for (int q = 0; q < NQ; q++) {
-                    const float p = sv[q] == -INFINITY ? 0.f : exp2f(sv[q] - M.mref[q]);
-                    l_part[q] = l_part[q] * M.f[q] + p;
-                    if (has_row) pbuf[(q >> 3) * 512 + (q & 7) * 8 + p_off] = __float2half_rn(p);
+                    for (int q = 0; q < NQ; q++) {
+                        const float v = (has_row && rpos < M.lim[q]) ? sv[q] * P.scale_log2 : -INFINITY;
+                        sv[q] = v;
+                        exceed |= v > M.mref[q] + RESCALE_LOG2;
+                    }
+                }
+                // one barrier per tile: combines the vote and orders the group; every thread leaves together on abort
+                const bool slow = group_any(2, 128, exceed);
+                if (*abort_flag) { ok = false; break; }
+                GS_STAMP(it, PF_VOTED);
+                bool rescale = false;
+                if (slow) {
+                    // some column's maximum moved: exact column maxima, new references, rescale factors
+                    GS_STAMP(it, PF_SLOW_PATH);
+#pragma unroll
+                    for (int q = 0; q < NQ; q++) {
+                        float mx = sv[q];
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                        if (lane == 0) M.smax[qt][q] = mx;
+                    }
+                    named_bar_sync(1, 128);
+                    if (wg_tid < NQ) {
+                        const int q = wg_tid;
+                        const float mt = fmaxf(fmaxf(M.smax[0][q], M.smax[1][q]), fmaxf(M.smax[2][q], M.smax[3][q]));
+                        const float mr = M.mref[q];
+                        float f = 1.f;
+                        if (mt > mr + RESCALE_LOG2) {  // also true for mr = -inf and any finite mt
+                            if (mr == -INFINITY) {
+                                f = 0.f;
+                            } else {
+                                f = exp2f(mr - mt);
+                                if (j > 0) M.flag[it & 1] = 1;  // accumulators hold data scaled by the old reference
+                            }
+                            M.mref[q] = mt;
+                        }
+                        M.f[q] = f;
+                    }
+                    if (wg_tid == 0) M.flag[(it + 1) & 1] = 0;
+                    named_bar_sync(1, 128);
+                    rescale = M.flag[it & 1] != 0;
+#pragma unroll
+                    for (int q = 0; q < NQ; q++) l_part[q] *= M.f[q];
+                }
+                (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, P.status, ST_SOFTMAX);
+                // probabilities: row sums in registers; P^T as f16, 8 query rows per 16-byte store, in the
+                // MN-major operand layout [q/8][row/8][row%8][q%8]
+                uint8_t *pbuf = p_smem + s * SM::P_BYTES + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
+#pragma unroll
+                for (int g = 0; g < NQ / 8; g++) {
+                    float p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int q = g * 8 + i;
+                        // masked entries are -inf and give 0; the clamp keeps (-inf) - (-inf) out of a column
+                        // that has seen no attended row yet
+                        p[i] = exp2f(sv[q] - fmaxf(M.mref[q], -1e30f));
+                        l_part[q] += p[i];
+                    }
+                    if (has_row) {
+                        uint4 v;
+                        __half2 h;
+                        h = __floats2half2_rn(p[0], p[1]); v.x = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(p[2], p[3]); v.y = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(p[4], p[5]); v.z = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(p[6], p[7]); v.w = *reinterpret_cast<uint32_t *>(&h);
+                        *reinterpret_cast<uint4 *>(pbuf + g * 1024) = v;
+                    }
                 }
                 if (rescale) {
                     // S(it) has completed, so every earlier MMA, PV(it-1) included, has completed too
-                    for (int mt = 0; mt < P.n_vtiles; mt++) {
+#pragma unroll
+                    for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                         for (int c = 0; c < NQ / 16; c++) {
                             uint32_t r[16];
@@ -430,14 +512,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     tmem_wait_st();
                 }
                 // rows of the last 16-row group past the segment's end must not feed NaNs into P.V
-                const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
+                const int valid = min(TILE, sg.r1 - row0);
                 if (valid & 15) {
                     const int r_lo = valid, r_hi = (valid + 15) & ~15;
-                    const int n_vec = (r_hi - r_lo) * nblk * 8;  // 16-byte vectors
+                    const int n_vec = (r_hi - r_lo) * NBLK * 8;  // 16-byte vectors
                     uint8_t *stage = kv_smem + s * STAGE_BYTES;
                     for (int i = wg_tid; i < n_vec; i += 128) {
                         const int v = i & 7, rk = i >> 3;
-                        const int k = rk % nblk, r = r_lo + rk / nblk;
+                        const int k = rk % NBLK, r = r_lo + rk / NBLK;
                         *reinterpret_cast<uint4 *>(stage + k * BLK_BYTES + r * 128 + v * 16) = make_uint4(0, 0, 0, 0);
                     }
                 }
@@ -445,6 +527,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B.p_full[s]);
+                GS_STAMP(it, PF_P_WRITTEN);
             }
             if (!ok) break;
             // ---- end of segment: drain the accumulators into this segment's partial record ----------------
@@ -470,7 +553,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
             float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
-            for (int mt = 0; mt < P.n_vtiles; mt++) {
+#pragma unroll
+            for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
                     uint32_t r[16];
@@ -489,6 +573,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             sgc++;
         }
     }
+#undef GS_STAMP
 
     // ---- common exit -----------------------------------------------------------------------------------------
     tc_fence_before();
@@ -506,11 +591,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     }
 }
 
-template <int NQ>
-int launch_nq(const UmmaParams &P, int grid, cudaStream_t st) {
+template <int NQ, int NBLK>
+int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
     const int smem = Smem<NQ>::TOTAL;
-    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k_decode_umma<NQ><<<grid, NTHREADS, smem, st>>>(P);
+    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    k_decode_umma<NQ, NBLK><<<grid, NTHREADS, smem, st>>>(P);
     GS_TRY(cudaGetLastError());
     return 0;
 }
@@ -520,8 +605,7 @@ int launch_nq(const UmmaParams &P, int grid, cudaStream_t st) {
 bool decode_umma_supported(const DecodeProblem &p, const char **why) {
     if (p.q_is_f32) { *why = "f32 queries"; return false; }
     if (p.sel) { *why = "explicit position lists"; return false; }
-    if (p.d_qk % 64 != 0 || p.d_qk < 64 || p.d_qk > 576) { *why = "d_qk must be a multiple of 64 up to 576"; return false; }
-    if (p.d_v % 128 != 0 || p.d_v > 512 || p.d_v > p.d_qk) { *why = "d_v must be a multiple of 128 up to min(512, d_qk)"; return false; }
+    if (!((p.d_qk == 576 || p.d_qk == 512) && p.d_v == 512)) { *why = "row widths other than 576/512 or 512/512"; return false; }
     if (p.T * p.H > 48) { *why = "more than 48 query rows per sequence"; return false; }
     if (p.n_seq > MAX_SEQ) { *why = "more than 1024 sequences"; return false; }
     if (p.page_table && p.page_rows != TILE) { *why = "page size other than 64"; return false; }
@@ -557,17 +641,14 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.T = p.T;
     P.H = p.H;
     P.rows_q = rows_q;
-    P.nblk = p.d_qk / 64;
-    P.n_vtiles = p.d_v / 128;
     P.d_v = p.d_v;
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
-    if (NQ == 32) {
-        if (int e = launch_nq<32>(P, grid, st)) return e;
-    } else {
-        if (int e = launch_nq<48>(P, grid, st)) return e;
-    }
+    int e;
+    if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
+    else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
+    if (e) return e;
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     CombinePlan c;
     c.acc = p.ws_acc;
