@@ -20,7 +20,7 @@ class DecodeArgs(C.Structure):
         ("page_table_stride", C.c_int32), ("page_rows", C.c_int32), ("scale", f32), ("tail_causal", C.c_int32),
         ("o", vp), ("part_out", vp), ("workspace", vp), ("workspace_bytes", i64),
         ("n_seq", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("d_qk", C.c_int32), ("d_v", C.c_int32),
-        ("max_seq_len", C.c_int32), ("impl", C.c_int32), ("ev_after_main", vp),
+        ("max_seq_len", C.c_int32), ("impl", C.c_int32), ("ev_after_main", vp), ("flags", C.c_int32),
     ]
 
 

@@ -63,7 +63,7 @@ def new_workspace(n_seq: int, T: int, H: int, d_v: int = 512, device=None) -> to
 
 def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, page_table=None, page_rows=64,
                tail_causal=True, out=None, part_out=None, want_out=True, workspace=None, max_seq_len=0, impl=0,
-               ev_after_main=None):
+               ev_after_main=None, no_combine=False):
     """Absorbed-MLA decode.  q f16 [n_seq,T,H,d_qk]; cache f16 [rows,d_qk]; seq_lens i32 [n_seq] (device).
     Returns ``out`` (f32 [n_seq,T,H,d_v]) or, with ``want_out=False``, ``part_out``."""
     L = _lib.load()
@@ -92,6 +92,7 @@ def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, p
     a.max_seq_len = max_seq_len
     a.impl = impl
     a.ev_after_main = ev_after_main  # raw cudaEvent_t handle (int) or None
+    a.flags = 1 if no_combine else 0
     _lib.check(L.gs_mla_decode(C.byref(a), _stream()), "gs_mla_decode")
     return out if want_out else part_out
 

@@ -102,6 +102,7 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
     p.max_seq_len = a->max_seq_len;
     p.splits = 0;
     p.ev_after_main = (cudaEvent_t) a->ev_after_main;
+    p.no_combine = (a->flags & GS_DECODE_NO_COMBINE) != 0;
     if (int e = device_sm_count(&p.sm_count)) return e;
     const char *why = "";
     const bool umma_ok = decode_umma_supported(p, &why);

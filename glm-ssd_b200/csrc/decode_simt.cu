@@ -8,6 +8,7 @@
 // Arithmetic follows the reference kernel's contract (crates/cuda/kernels/ops.cu:420-424):
 //   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
 // with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
+#include "combine.cuh"
 #include "internal.cuh"
 
 namespace gs {
@@ -163,109 +164,14 @@ __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
 }
 
 // ---- combine --------------------------------------------------------------------------------------
-// One CTA per (output row, 128-column chunk); 32 column quads x 8 segment lanes.
-constexpr int CB_COLS = 128;
-constexpr int CB_LANES = 8;
-constexpr int CB_NT = (CB_COLS / 4) * CB_LANES;  // 256
-constexpr int CB_MAX_SEG = 1024;
-
+// Stand-alone combine: one CTA per item.  Launched with programmatic dependent launch: the launch
+// overlaps the tail of the kernel that writes the partials.
 __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
-    const int row = blockIdx.x;  // (b, t, h)
-    const int col0 = blockIdx.y * CB_COLS;
-    const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
-    int first, nseg, row_in_seg;
-    if (C.desc) {
-        const int2 d = C.desc[b];
-        first = d.x;
-        nseg = d.y;
-        row_in_seg = t * C.H + h;
-    } else {
-        first = (b * C.T + t) * C.regular_segments;
-        nseg = C.regular_segments;
-        row_in_seg = h;
-    }
-    nseg = min(nseg, CB_MAX_SEG);
-    __shared__ float s_w[CB_MAX_SEG];
-    __shared__ float s_red[CB_NT / 32];
-    __shared__ float s_M, s_L;
-    __shared__ float4 s_part[CB_LANES][CB_COLS / 4];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    // pass 1: M = max m_s
-    float mx = -INFINITY;
-    for (int s = tid; s < nseg; s += CB_NT) mx = fmaxf(mx, C.ml[(int64_t) (first + s) * C.seg_stride_ml + row_in_seg * 2]);
-    mx = warp_max(mx);
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    if (tid == 0) {
-        float m = -INFINITY;
-        for (int w = 0; w < CB_NT / 32; w++) m = fmaxf(m, s_red[w]);
-        s_M = m;
-    }
-    __syncthreads();
-    const float M = s_M;
-    // pass 2: weights and L
-    float lsum = 0.f;
-    for (int s = tid; s < nseg; s += CB_NT) {
-        const float *ml = C.ml + (int64_t) (first + s) * C.seg_stride_ml + row_in_seg * 2;
-        const float m = ml[0];
-        const float w = m == -INFINITY ? 0.f : expf(m - M);
-        s_w[s] = w;
-        lsum += ml[1] * w;
-    }
-    lsum = warp_sum(lsum);
-    __syncthreads();
-    if (lane == 0) s_red[warp] = lsum;
-    __syncthreads();
-    if (tid == 0) {
-        float l = 0.f;
-        for (int w = 0; w < CB_NT / 32; w++) l += s_red[w];
-        s_L = l;
-    }
-    __syncthreads();
-    const float L = s_L;
-    // pass 3: weighted sum of the accumulators
-    const int quad = tid % (CB_COLS / 4), sl = tid / (CB_COLS / 4);
-    const int col = col0 + quad * 4;
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (col < C.d_v) {
-        for (int s = sl; s < nseg; s += CB_LANES) {
-            const float w = s_w[s];
-            if (w != 0.f) {
-                const float4 v = *reinterpret_cast<const float4 *>(
-                    C.acc + (int64_t) (first + s) * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col);
-                a.x = fmaf(v.x, w, a.x);
-                a.y = fmaf(v.y, w, a.y);
-                a.z = fmaf(v.z, w, a.z);
-                a.w = fmaf(v.w, w, a.w);
-            }
-        }
-    }
-    s_part[sl][quad] = a;
-    __syncthreads();
-    if (sl == 0 && col < C.d_v) {
-#pragma unroll
-        for (int j = 1; j < CB_LANES; j++) {
-            const float4 v = s_part[j][quad];
-            a.x += v.x;
-            a.y += v.y;
-            a.z += v.z;
-            a.w += v.w;
-        }
-        if (C.part_out) {
-            const int64_t rows_total = (int64_t) C.n_seq * C.T * C.H;
-            *reinterpret_cast<float4 *>(C.part_out + (int64_t) row * C.d_v + col) = a;
-            if (blockIdx.y == 0 && quad == 0) {
-                C.part_out[rows_total * C.d_v + (int64_t) row * 2] = M;
-                C.part_out[rows_total * C.d_v + (int64_t) row * 2 + 1] = L;
-            }
-        }
-        if (C.o) {
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            *reinterpret_cast<float4 *>(C.o + (int64_t) row * C.d_v + col) =
-                make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
-        }
-    }
+    __shared__ CombineSmem S;
+#if __CUDA_ARCH__ >= 900
+    cudaGridDependencySynchronize();  // the partials (and desc) are written by the preceding kernel
+#endif
+    combine_item(C, blockIdx.x, blockIdx.y * CB_COLS, S);
 }
 
 }  // namespace
@@ -274,9 +180,17 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     const int rows = c.n_seq * c.T * c.H;
     if (rows <= 0) return 0;
     if (c.d_v % 4 != 0) return fail_invalid("combine: d_v must be a multiple of 4");
-    dim3 grid(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
-    k_combine<<<grid, CB_NT, 0, st>>>(c);
-    GS_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
+    cfg.blockDim = dim3(CB_NT);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GS_TRY(cudaLaunchKernelEx(&cfg, k_combine, c));
     return 0;
 }
 
@@ -328,6 +242,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     }
     GS_TRY(cudaGetLastError());
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
+    if (p.no_combine) return 0;
     CombinePlan c;
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;

@@ -20,8 +20,11 @@
 //    kernel from the HBM roofline to the tensor roofline.
 //  * A 4-warp group reads S^T from TMEM (one cache row per thread), does the online softmax with
 //    warp-shuffle column maxima and a lazily updated reference maximum (the O accumulators are
-//    rescaled only when a maximum grows by more than 2^6), writes P^T as f16 into shared memory in
-//    the canonical K-major layout, and at the end of a segment drains O^T from TMEM.
+//    rescaled only when a maximum grows by more than 2^6; in the common case one vote barrier per tile
+//    replaces the reduction), writes P^T as f16 into shared memory in the canonical MN-major operand
+//    layout, and at the end of a segment drains O^T from TMEM.
+//  * Three warps issue the MMAs concurrently, each into its own accumulators (a single issuing thread
+//    cannot keep the tensor pipe busy with MMAs this small); the softmax group adds the S^T partials.
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status word and leaves
 // through the common exit, which frees tensor memory.
@@ -68,10 +71,11 @@ constexpr int BLK_BYTES = TILE * 128;    // one 64-column block of a tile: 64 ro
 constexpr int NBLK_MAX = 9;              // 576 / 64
 constexpr int STAGE_BYTES = NBLK_MAX * BLK_BYTES;
 constexpr int STAGES = 2;
-constexpr int NTHREADS = 192;            // warp 0 producer, warp 1 MMA, warps 2-5 softmax group
+constexpr int N_MMA_WARPS = 3;           // concurrently issuing MMA warps
+constexpr int NTHREADS = 32 * (1 + N_MMA_WARPS + 4);  // warp 0 producer, warps 1-3 MMA, warps 4-7 softmax group
 constexpr int TMEM_COLS = 512;
-constexpr int SLOT = 64;                 // TMEM column slot: S0, S1, then O tiles
-constexpr int O_COL0 = 2 * SLOT;
+constexpr int SLOT = 64;                 // TMEM column slot: one S^T partial per issuer, then the O tiles
+constexpr int O_COL0 = N_MMA_WARPS * SLOT;
 constexpr int NVT = 4;                   // 128-column value tiles (d_v = 512)
 constexpr int MAX_SEQ = 1024;
 constexpr float RESCALE_LOG2 = 6.0f;     // lazy rescale threshold, in log2 units
@@ -97,7 +101,7 @@ struct UmmaParams {
 
 struct Barriers {
     uint64_t kv_full[STAGES], kv_empty[STAGES];
-    uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint64_t s_full, s_empty, p_full[2], p_empty[2];
     uint64_t q_full, q_empty, o_full, o_empty;
 };
 
@@ -114,6 +118,7 @@ struct Smem {
         int abort_flag;
         int flag[2];
         int cum[MAX_SEQ + 1];
+        int len[MAX_SEQ];
         float smax[4][NQ];
         float sl[4][NQ];
         float mref[NQ];
@@ -129,7 +134,7 @@ struct Segment {
 
 // Walks the segments of this CTA's unit range [pos, end); `b` is a cursor over sequences.
 __device__ __forceinline__ bool next_segment(int &pos, int &b, int end, const int *cum, int unit_rows,
-                                             const int32_t *seq_lens, Segment &sg) {
+                                             const int *seq_lens, Segment &sg) {
     if (pos >= end) return false;
     while (cum[b + 1] <= pos) b++;
     const int u_lo = pos - cum[b];
@@ -160,6 +165,29 @@ __device__ __forceinline__ bool group_any(int id, int n_threads, bool pred) {
     return out != 0;
 }
 
+// P.V for the O^T tiles [MT_LO, MT_HI): nk 16-row k-steps, fully unrolled
+template <int NQ, int MT_LO, int MT_HI>
+__device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t d_pt, uint32_t kv_lo, uint32_t p_lo,
+                                         uint32_t idesc, int nk, bool acc0) {
+    if (nk == 4) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+            for (int mt = MT_LO; mt < MT_HI; mt++)
+                umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128), d_pt + (p_lo + ks * 16),
+                        idesc, acc0 || ks > 0);
+    } else {
+#pragma unroll
+        for (int ks = 0; ks < 3; ks++)
+            if (ks < nk) {
+#pragma unroll
+                for (int mt = MT_LO; mt < MT_HI; mt++)
+                    umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128),
+                            d_pt + (p_lo + ks * 16), idesc, acc0 || ks > 0);
+            }
+    }
+}
+
 template <int NQ, int NBLK>
 __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
     using SM = Smem<NQ>;
@@ -184,6 +212,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         if (prof && (tile) < (uint32_t) kProfTiles) prof[(tile) * kProfSlots + (slot)] = clock64(); \
     } while (0)
 
+    if (tid == 0) GS_STAMP(kProfTiles - 1, 0);  // kernel-level stamps live in the last row
     // ---- set-up: barriers, tensor memory, the unit schedule -------------------------------------------
     if (tid == 0) {
         tma_prefetch_desc(&P.tm_kv64);
@@ -191,17 +220,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tma_prefetch_desc(&P.tm_q);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&B.kv_full[s], 1);
-            mbar_init(&B.kv_empty[s], 1);
+            mbar_init(&B.kv_empty[s], N_MMA_WARPS);
         }
+        mbar_init(&B.s_full, N_MMA_WARPS);
+        mbar_init(&B.s_empty, 4);
         for (int s = 0; s < 2; s++) {
-            mbar_init(&B.s_full[s], 1);
-            mbar_init(&B.s_empty[s], 4);
             mbar_init(&B.p_full[s], 4);
-            mbar_init(&B.p_empty[s], 1);
+            mbar_init(&B.p_empty[s], N_MMA_WARPS);
         }
         mbar_init(&B.q_full, 1);
-        mbar_init(&B.q_empty, 1);
-        mbar_init(&B.o_full, 1);
+        mbar_init(&B.q_empty, N_MMA_WARPS);
+        mbar_init(&B.o_full, N_MMA_WARPS);
         mbar_init(&B.o_empty, 4);
         M.abort_flag = 0;
         M.flag[0] = M.flag[1] = 0;
@@ -212,8 +241,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tmem_alloc(&M.tmem_base, TMEM_COLS);
         tmem_relinquish();
     }
+    // everything above touched only this CTA's own resources; inputs written by earlier kernels come next
+    griddep_wait();
     for (int b = tid; b < P.n_seq; b += NTHREADS) {
         const int len = max(P.seq_lens[b], 0);
+        M.len[b] = len;
         M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
     }
     tc_fence_before();
@@ -261,39 +293,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         }
         b_cur = lo;
     }
+    griddep_launch_dependents();
+    if (tid == 0) GS_STAMP(kProfTiles - 1, 1);
     int pos = start;
     uint32_t it = 0, sgc = 0;  // running tile and segment counters (identical in every role)
     Segment sg;
 
     if (warp == 0) {
         // =================================== TMA producer ==================================================
-        if (lane == 0) {
-            bool ok = true;
-            while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
-                ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+        // The whole warp runs the loop (uniform control flow); one elected lane issues each copy.
+        bool ok = true;
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
+            const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
+            for (int j = 0; j < sg.n_tiles; j++, it++) {
+                const int s = it & 1;
+                ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * NQ * 128));
-#pragma unroll
-                for (int k = 0; k < NBLK; k++)
-                    tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
-                const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
-                for (int j = 0; j < sg.n_tiles; j++, it++) {
-                    const int s = it & 1;
-                    ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
-                    if (!ok) break;
-                    GS_STAMP(it, PF_LOAD_ISSUE);
-                    const int row = sg.r0 + j * TILE;
-                    const int valid = min(TILE, sg.r1 - row);
-                    uint8_t *dst = kv_smem + s * STAGE_BYTES;
-                    if (P.paged || valid == TILE) {
-                        const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE] * TILE
-                                                 : (int) (base_row + row);
+                if (lane == 0) GS_STAMP(it, PF_LOAD_ISSUE);
+                const int row = sg.r0 + j * TILE;
+                const int valid = min(TILE, sg.r1 - row);
+                uint8_t *dst = kv_smem + s * STAGE_BYTES;
+                if (P.paged || valid == TILE) {
+                    const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE] * TILE
+                                             : (int) (base_row + row);
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (NBLK * BLK_BYTES));
 #pragma unroll
                         for (int k = 0; k < NBLK; k++)
                             tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, grow);
-                    } else {
-                        const int ng = (valid + 15) >> 4;
+                    }
+                } else {
+                    const int ng = (valid + 15) >> 4;
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (ng * NBLK * 2048));
                         for (int g = 0; g < ng; g++) {
 #pragma unroll
@@ -303,82 +334,105 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         }
                     }
                 }
-                sgc++;
+                if (j == 0) {  // the query rows of this sequence, after the first (larger, farther) cache tile
+                    ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+                    if (!ok) break;
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * NQ * 128));
+#pragma unroll
+                        for (int k = 0; k < NBLK; k++)
+                            tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
+                    }
+                }
+                __syncwarp();
             }
+            sgc++;
         }
-    } else if (warp == 1) {
-        // =================================== MMA issuer ======================================================
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);    // A, B K-major
-            constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 1);  // A (V^T) and B (P^T) MN-major
-            // descriptors with a zero start address; the start address (>> 4) is added per instruction
-            const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);         // cache tile / Q, K-major
-            const uint64_t d_vt = make_smem_desc(0, BLK_BYTES, 1024, kSwizzle128B);    // cache tile, MN-major
-            const uint64_t d_pt = make_smem_desc(0, 128, 1024, kSwizzleNone);          // P^T, MN-major
-            const uint32_t q_lo = smem_u32(q_smem) >> 4, p_lo0 = smem_u32(p_smem) >> 4, kv_lo0 = smem_u32(kv_smem) >> 4;
-            bool ok = true;
-            while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
-                ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
-                for (int j = 0; ok && j < sg.n_tiles; j++, it++) {
-                    const int s = it & 1;
-                    const uint32_t ph = (it >> 1) & 1;
-                    const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
-                    // S^T = C_tile . Q^T
-                    ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
-                         mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
-                    if (!ok) break;
-                    GS_STAMP(it, PF_KV_FULL);
-                    tc_fence_after();
+    } else if (warp <= N_MMA_WARPS) {
+        // =================================== MMA issuers ====================================================
+        // Three warps issue concurrently: one issuer cannot keep the tensor pipe busy with MMAs this
+        // small.  Each warp owns its accumulators: a third of the 16-column k-steps of S^T (partial sums,
+        // added by the softmax group) and one or two of the four 128-column O^T tiles.  The whole warp runs
+        // the loop; one elected lane (the same one every time) issues the MMAs and their commits.
+        const int mw = warp - 1;
+        constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);    // A, B K-major
+        constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 1);  // A (V^T) and B (P^T) MN-major
+        constexpr int KSTEPS = NBLK * 4;
+        constexpr int K_PER = (KSTEPS + N_MMA_WARPS - 1) / N_MMA_WARPS;
+        const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);         // cache tile / Q, K-major
+        const uint64_t d_vt = make_smem_desc(0, BLK_BYTES, 1024, kSwizzle128B);    // cache tile, MN-major
+        const uint64_t d_pt = make_smem_desc(0, 128, 1024, kSwizzleNone);          // P^T, MN-major
+        const uint32_t q_lo = smem_u32(q_smem) >> 4, p_lo0 = smem_u32(p_smem) >> 4, kv_lo0 = smem_u32(kv_smem) >> 4;
+        bool ok = true;
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
+            ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
+            for (int j = 0; ok && j < sg.n_tiles; j++, it++) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
+                // ---- S^T(partial) = C_tile[:, my k-steps] . Q^T[my k-steps] ----
+                ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
+                     mbar_wait(&B.s_empty, (it & 1) ^ 1, abort_flag, P.status, ST_MMA);
+                if (!ok) break;
+                if (mw == 0 && lane == 0) GS_STAMP(it, PF_KV_FULL);
+                tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < NBLK; k++) {
-#pragma unroll
-                        for (int ks = 0; ks < 4; ks++) {
-                            umma_ss(tmem + s * SLOT, d_kmaj + (kv_lo + k * (BLK_BYTES >> 4) + ks * 2),
-                                    d_kmaj + (q_lo + k * (NQ * 128 >> 4) + ks * 2), idesc_s, (k | ks) != 0);
+                    for (int i = 0; i < K_PER; i++) {
+                        const int kidx = mw * K_PER + i;
+                        if (kidx < KSTEPS) {
+                            const int kb = kidx >> 2, ks = kidx & 3;
+                            umma_ss(tmem + mw * SLOT, d_kmaj + (kv_lo + kb * (BLK_BYTES >> 4) + ks * 2),
+                                    d_kmaj + (q_lo + kb * (NQ * 128 >> 4) + ks * 2), idesc_s, i != 0);
                         }
                     }
-                    umma_commit(&B.s_full[s]);
-                    GS_STAMP(it, PF_S_ISSUED);
-                    // O^T += V^T . P^T
-                    ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
-                    if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
-                    if (!ok) break;
-                    GS_STAMP(it, PF_P_FULL_SEEN);
-                    tc_fence_after();
-                    const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
-                    const int nk = (valid + 15) >> 4;
-                    const uint32_t p_lo = p_lo0 + s * (SM::P_BYTES >> 4);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        if (ks < nk) {
-#pragma unroll
-                            for (int mt = 0; mt < NVT; mt++) {
-                                umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128),
-                                        d_pt + (p_lo + ks * 16), idesc_pv, j > 0 || ks > 0);
-                            }
-                        }
-                    }
+                    umma_commit(&B.s_full);
+                }
+                __syncwarp();
+                if (mw == 0 && lane == 0) GS_STAMP(it, PF_S_ISSUED);
+                // ---- O^T[my tiles] += V^T . P^T ----
+                ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
+                if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
+                if (!ok) break;
+                if (mw == 0 && lane == 0) GS_STAMP(it, PF_P_FULL_SEEN);
+                tc_fence_after();
+                const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
+                const int nk = (valid + 15) >> 4;
+                const uint32_t p_lo = p_lo0 + s * (SM::P_BYTES >> 4);
+                const bool acc0 = j > 0;
+                const bool last = j == sg.n_tiles - 1;
+                if (elect_one()) {
+                    if (mw == 0) issue_pv<NQ, 0, 2>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    else if (mw == 1) issue_pv<NQ, 2, 3>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    else issue_pv<NQ, 3, 4>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
                     umma_commit(&B.kv_empty[s]);
                     umma_commit(&B.p_empty[s]);
-                    if (j == sg.n_tiles - 1) {
+                    if (last) {
                         umma_commit(&B.o_full);
                         umma_commit(&B.q_empty);
                     }
-                    GS_STAMP(it, PF_PV_ISSUED);
                 }
-                sgc++;
+                __syncwarp();
+                if (mw == 0 && lane == 0) GS_STAMP(it, PF_PV_ISSUED);
             }
+            sgc++;
         }
     } else {
         // =================================== softmax / epilogue group ==========================================
-        const int wg_tid = tid - 64;
+        const int wg_tid = tid - 32 * (1 + N_MMA_WARPS);
         const int qt = warp & 3;                      // TMEM lane quarter this warp may touch
         const uint32_t lane_base = (uint32_t) (qt * 32) << 16;
-        const int row_in_tile = qt * 16 + lane;       // S^T row of this thread (lanes 0..15 only)
-        const bool has_row = lane < 16;
-        float l_part[NQ];
+        const int my_row = qt * 16 + (lane & 15);     // cache row (within the tile) this lane works on
+        constexpr float UNSET = 1e30f;                // "-reference" of a column that has seen no attended row
+        // After the scores are read (one cache row per thread, lanes 0..15), the upper half of the query
+        // rows is handed to lanes 16..31, so every lane works on HQ = NQ/2 query rows of one cache row.
+        constexpr int HQ = NQ / 2;
+        const int hi = lane >> 4;                     // which half of the query rows this lane handles
+        const int col0 = hi * HQ;
+        float l_part[HQ];                             // row sums of this thread's cache row, per query row
+        float nm[HQ];                                 // minus the reference maximum (log2 units) per query row
         bool ok = true;
-        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, P.seq_lens, sg)) {
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
             if (wg_tid < NQ) {
                 const int q = wg_tid, t = q / P.H;
                 int lim = 0;
@@ -389,47 +443,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             // rows below lim_min are attended by every query row of the sequence
             const int lim_min = P.tail_causal ? min(sg.r1, sg.len - (P.T - 1)) : sg.r1;
 #pragma unroll
-            for (int q = 0; q < NQ; q++) l_part[q] = 0.f;
+            for (int i = 0; i < HQ; i++) {
+                l_part[i] = 0.f;
+                nm[i] = UNSET;
+            }
             named_bar_sync(1, 128);
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                (void) mbar_wait(&B.s_full[s], ph, abort_flag, P.status, ST_SOFTMAX);
+                (void) mbar_wait(&B.s_full, it & 1, abort_flag, P.status, ST_SOFTMAX);
                 GS_STAMP(it, PF_S_FULL);
                 tc_fence_after();
-                float sv[NQ];
+                const int row0 = sg.r0 + j * TILE;
+                const int rpos = row0 + my_row;
+                const bool boundary = row0 + TILE > lim_min;  // some query row must not see some row of this tile
+                // S^T row = sum of the issuers' partial accumulators; then split the query rows over the lane halves
+                float sv[HQ];
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
-                    uint32_t r[16];
-                    tmem_ld16(tmem + lane_base + s * SLOT + c * 16, r);
+                    uint32_t r0[16], r1[16], r2[16];
+                    tmem_ld16(tmem + lane_base + 0 * SLOT + c * 16, r0);
+                    tmem_ld16(tmem + lane_base + 1 * SLOT + c * 16, r1);
+                    tmem_ld16(tmem + lane_base + 2 * SLOT + c * 16, r2);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; i++) sv[c * 16 + i] = __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; i++) {
+                        const int q = c * 16 + i;
+                        const float v = (__uint_as_float(r0[i]) + __uint_as_float(r1[i])) + __uint_as_float(r2[i]);
+                        // lanes 0..15 keep query rows [0, HQ), lanes 16..31 fetch [HQ, NQ) from lane - 16
+                        if (q < HQ) {
+                            if (!hi) sv[q] = v;
+                        } else {
+                            const float u = __shfl_sync(0xffffffffu, v, lane & 15);
+                            if (hi) sv[q - HQ] = u;
+                        }
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&B.s_empty[s]);
+                if (lane == 0) mbar_arrive(&B.s_empty);
                 GS_STAMP(it, PF_S_LOADED);
-                const int row0 = sg.r0 + j * TILE;
-                const int rpos = row0 + row_in_tile;
-                // scaled (and, on boundary tiles, masked) scores; does any exceed its reference by the threshold?
-                bool exceed = false;
-                if (row0 + TILE <= lim_min) {
+                if (boundary) {
 #pragma unroll
-                    for (int q = 0; q < NQ; q++) {
-                        const float v = has_row ? sv[q] * P.scale_log2 : -INFINITY;
-                        sv[q] = v;
-                        exceed |= v > M.mref[q] + RESCALE_LOG2;
-                    }
-                } else {
-#pragma unroll
-                    for (int q = 0; q < NQ; q++) {
-                        const float v = (has_row && rpos < M.lim[q]) ? sv[q] * P.scale_log2 : -INFINITY;
-                        sv[q] = v;
-                        exceed |= v > M.mref[q] + RESCALE_LOG2;
-                    }
+                    for (int i = 0; i < HQ; i++)
+                        if (rpos >= M.lim[col0 + i]) sv[i] = -INFINITY;
                 }
-                // one barrier per tile: combines the vote and orders the group; every thread leaves together on abort
+                // does any score exceed its column's reference by the threshold (or meet an unset column)?
+                bool exceed = false;
+#pragma unroll
+                for (int i = 0; i < HQ; i++) exceed |= fmaf(sv[i], P.scale_log2, nm[i]) > RESCALE_LOG2;
+                // one barrier per tile: combines the vote and orders the group; on abort every thread leaves together
                 const bool slow = group_any(2, 128, exceed);
                 if (*abort_flag) { ok = false; break; }
                 GS_STAMP(it, PF_VOTED);
@@ -438,13 +501,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     // some column's maximum moved: exact column maxima, new references, rescale factors
                     GS_STAMP(it, PF_SLOW_PATH);
 #pragma unroll
-                    for (int q = 0; q < NQ; q++) {
-                        float mx = sv[q];
+                    for (int i = 0; i < HQ; i++) {
+                        float mx = sv[i] * P.scale_log2;
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                        if (lane == 0) M.smax[qt][q] = mx;
+                        if ((lane & 15) == 0) M.smax[qt][col0 + i] = mx;
                     }
                     named_bar_sync(1, 128);
                     if (wg_tid < NQ) {
@@ -467,36 +530,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     named_bar_sync(1, 128);
                     rescale = M.flag[it & 1] != 0;
 #pragma unroll
-                    for (int q = 0; q < NQ; q++) l_part[q] *= M.f[q];
+                    for (int i = 0; i < HQ; i++) {
+                        l_part[i] *= M.f[col0 + i];
+                        const float mr = M.mref[col0 + i];
+                        nm[i] = mr == -INFINITY ? UNSET : -mr;
+                    }
                 }
                 (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, P.status, ST_SOFTMAX);
                 // probabilities: row sums in registers; P^T as f16, 8 query rows per 16-byte store, in the
-                // MN-major operand layout [q/8][row/8][row%8][q%8]
-                uint8_t *pbuf = p_smem + s * SM::P_BYTES + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
+                // MN-major operand layout [q/8][row/8][row%8][q%8].  A masked score is -inf and gives 0; an
+                // unset column holds only masked scores.
+                uint8_t *pbuf = p_smem + s * SM::P_BYTES + (my_row >> 3) * 128 + (my_row & 7) * 16 + (col0 >> 3) * 1024;
 #pragma unroll
-                for (int g = 0; g < NQ / 8; g++) {
+                for (int g = 0; g < HQ / 8; g++) {
                     float p[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        const int q = g * 8 + i;
-                        // masked entries are -inf and give 0; the clamp keeps (-inf) - (-inf) out of a column
-                        // that has seen no attended row yet
-                        p[i] = exp2f(sv[q] - fmaxf(M.mref[q], -1e30f));
-                        l_part[q] += p[i];
+                        p[i] = ex2_approx(fmaf(sv[g * 8 + i], P.scale_log2, nm[g * 8 + i]));
+                        l_part[g * 8 + i] += p[i];
                     }
-                    if (has_row) {
-                        uint4 v;
-                        __half2 h;
-                        h = __floats2half2_rn(p[0], p[1]); v.x = *reinterpret_cast<uint32_t *>(&h);
-                        h = __floats2half2_rn(p[2], p[3]); v.y = *reinterpret_cast<uint32_t *>(&h);
-                        h = __floats2half2_rn(p[4], p[5]); v.z = *reinterpret_cast<uint32_t *>(&h);
-                        h = __floats2half2_rn(p[6], p[7]); v.w = *reinterpret_cast<uint32_t *>(&h);
-                        *reinterpret_cast<uint4 *>(pbuf + g * 1024) = v;
-                    }
+                    uint4 v;
+                    __half2 h;
+                    h = __floats2half2_rn(p[0], p[1]); v.x = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2half2_rn(p[2], p[3]); v.y = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2half2_rn(p[4], p[5]); v.z = *reinterpret_cast<uint32_t *>(&h);
+                    h = __floats2half2_rn(p[6], p[7]); v.w = *reinterpret_cast<uint32_t *>(&h);
+                    *reinterpret_cast<uint4 *>(pbuf + g * 1024) = v;
                 }
                 if (rescale) {
-                    // S(it) has completed, so every earlier MMA, PV(it-1) included, has completed too
-#pragma unroll
+                    // every MMA issued before this tile's S has completed, P.V of the previous tile included
+#pragma unroll 1
                     for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                         for (int c = 0; c < NQ / 16; c++) {
@@ -535,14 +598,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             named_bar_sync(2, 128);
             if (*abort_flag) { ok = false; break; }
             tc_fence_after();
+            if (wg_tid == 0) GS_STAMP(kProfTiles - 1, 2);
 #pragma unroll
-            for (int q = 0; q < NQ; q++) {
-                float v = has_row ? l_part[q] : 0.f;
+            for (int i = 0; i < HQ; i++) {
+                float v = l_part[i];
                 v += __shfl_xor_sync(0xffffffffu, v, 8);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
-                if (lane == 0) M.sl[qt][q] = v;
+                if ((lane & 15) == 0) M.sl[qt][col0 + i] = v;
             }
             named_bar_sync(1, 128);
             if (wg_tid < P.rows_q) {
@@ -553,7 +617,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
             float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
-#pragma unroll
+#pragma unroll 1
             for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
@@ -570,10 +634,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&B.o_empty);
+            if (wg_tid == 0) GS_STAMP(kProfTiles - 1, 3);
             sgc++;
         }
     }
-#undef GS_STAMP
 
     // ---- common exit -----------------------------------------------------------------------------------------
     tc_fence_before();
@@ -589,14 +653,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
+    if (tid == 32) GS_STAMP(kProfTiles - 1, 4);
+#undef GS_STAMP
 }
 
 template <int NQ, int NBLK>
 int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
     const int smem = Smem<NQ>::TOTAL;
+    // attributes are set on every call: a cached flag would go stale across a device reset
     GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k_decode_umma<NQ, NBLK><<<grid, NTHREADS, smem, st>>>(P);
-    GS_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    // programmatic dependent launch: the CTA-local set-up may overlap the tail of the preceding kernel
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GS_TRY(cudaLaunchKernelEx(&cfg, k_decode_umma<NQ, NBLK>, P));
     return 0;
 }
 
@@ -607,6 +684,7 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
     if (p.sel) { *why = "explicit position lists"; return false; }
     if (!((p.d_qk == 576 || p.d_qk == 512) && p.d_v == 512)) { *why = "row widths other than 576/512 or 512/512"; return false; }
     if (p.T * p.H > 48) { *why = "more than 48 query rows per sequence"; return false; }
+    if (!(p.scale > 0.f)) { *why = "non-positive softmax scale"; return false; }
     if (p.n_seq > MAX_SEQ) { *why = "more than 1024 sequences"; return false; }
     if (p.page_table && p.page_rows != TILE) { *why = "page size other than 64"; return false; }
     if ((reinterpret_cast<uintptr_t>(p.q) & 15) || (reinterpret_cast<uintptr_t>(p.cache) & 15)) { *why = "q and cache must be 16-byte aligned"; return false; }
@@ -645,11 +723,6 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
-    int e;
-    if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
-    else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
-    if (e) return e;
-    if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     CombinePlan c;
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;
@@ -663,6 +736,12 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     c.d_v = p.d_v;
     c.o = p.o;
     c.part_out = p.part_out;
+    int e;
+    if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
+    else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
+    if (e) return e;
+    if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
+    if (p.no_combine) return 0;
     return launch_combine(c, st);
 }
 

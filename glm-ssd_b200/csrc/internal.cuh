@@ -30,6 +30,7 @@ struct DecodeProblem {
     int max_seq_len;
     int splits;           // CUDA-core kernel: splits per (sequence, token); 0 = choose
     int sm_count;
+    bool no_combine;      // stop after the attention kernel (timing aid)
     cudaEvent_t ev_after_main;  // recorded between the attention kernel and the combine, or nullptr
 };
 

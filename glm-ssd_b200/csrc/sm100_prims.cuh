@@ -11,6 +11,21 @@ namespace sm100 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
+// One lane of a converged warp: the form the compiler recognises, so that the operands of the
+// single-thread instructions that follow (TMA, tcgen05.mma, commit) stay in uniform registers.  A
+// plain `if (lane == 0)` around them makes every such instruction several times more expensive.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -44,9 +59,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // releases tensor memory.  A healthy run never comes near the limit (about a second).
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
-                                          int32_t code) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The slow path is kept out of line: the kernels are latency-sensitive to their code size.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
+                                           int32_t code) {
     const long long t0 = clock64();
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -60,6 +75,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
+                                          int32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------------
@@ -152,6 +172,17 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
+}
+
+// Programmatic dependent launch: wait for the kernels this one depends on (and their memory) /
+// allow the next kernel in the stream to begin its own set-up.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int n_threads) {

@@ -71,7 +71,11 @@ typedef struct gs_mla_decode_args {
                                   tcgen05 kernel (returns cudaErrorInvalidValue if the shape is outside it) */
     void *ev_after_main;       /* optional cudaEvent_t recorded on the stream between the attention kernel and
                                   the combine kernel, so a caller can time the two apart; NULL = none */
+    int32_t flags;             /* bit 0 (GS_DECODE_NO_COMBINE): run the attention kernel only and leave the split
+                                  partials in the workspace (o / part_out are not written); for timing that
+                                  kernel alone */
 } gs_mla_decode_args;
+#define GS_DECODE_NO_COMBINE 1
 
 /* Bytes of workspace gs_mla_decode needs on the current device for these sizes (host function). */
 int64_t gs_mla_decode_workspace_bytes(int n_seq, int T, int H, int d_v);
