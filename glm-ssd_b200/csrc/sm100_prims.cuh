@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
 // The slow path is kept out of line: the kernels are latency-sensitive to their code size.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
                                            int32_t code) {
     const long long t0 = clock64();
     int spins = 0;
