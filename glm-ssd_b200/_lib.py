@@ -30,6 +30,7 @@ SIGNATURES = {
     "gs_f32_to_f16": (i32, [vp, vp, i64, vp]),
     "gs_mla_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
     "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
+    "gs_mla_decode_static": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_combine_parts": (i32, [vp, i32, i64, i32, i32, vp, vp]),
     "gs_prefill_attn": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]),
     "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),

@@ -63,7 +63,7 @@ def new_workspace(n_seq: int, T: int, H: int, d_v: int = 512, device=None) -> to
 
 def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, page_table=None, page_rows=64,
                tail_causal=True, out=None, part_out=None, want_out=True, workspace=None, max_seq_len=0, impl=0,
-               ev_after_main=None, no_combine=False):
+               ev_after_main=None, no_combine=False, static_scratch=False):
     """Absorbed-MLA decode.  q f16 [n_seq,T,H,d_qk]; cache f16 [rows,d_qk]; seq_lens i32 [n_seq] (device).
     Returns ``out`` (f32 [n_seq,T,H,d_v]) or, with ``want_out=False``, ``part_out``."""
     L = _lib.load()
@@ -73,7 +73,7 @@ def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, p
     n_seq, T, H, d_qk = q.shape
     if cache.dim() != 2 or cache.shape[1] != d_qk:
         raise ValueError("cache must be [rows, d_qk]")
-    if workspace is None:
+    if workspace is None and not static_scratch:
         workspace = new_workspace(n_seq, T, H, d_v, q.device)
     if want_out and out is None:
         out = torch.empty((n_seq, T, H, d_v), dtype=torch.float32, device=q.device)
@@ -87,13 +87,18 @@ def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, p
     a.tail_causal = 1 if tail_causal else 0
     a.o = _ptr(out) if want_out else None
     a.part_out = _ptr(part_out)
-    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    if not static_scratch:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     a.n_seq, a.T, a.H, a.d_qk, a.d_v = n_seq, T, H, d_qk, d_v
     a.max_seq_len = max_seq_len
     a.impl = impl
     a.ev_after_main = ev_after_main  # raw cudaEvent_t handle (int) or None
     a.flags = 1 if no_combine else 0
-    _lib.check(L.gs_mla_decode(C.byref(a), _stream()), "gs_mla_decode")
+    if static_scratch:
+        # the library's built-in scratch array instead of a workspace: nothing is allocated for the call
+        _lib.check(L.gs_mla_decode_static(C.byref(a), _stream()), "gs_mla_decode_static")
+    else:
+        _lib.check(L.gs_mla_decode(C.byref(a), _stream()), "gs_mla_decode")
     return out if want_out else part_out
 
 

@@ -207,3 +207,38 @@ GS_EXPORT int gs_mla_decode_status(const void *workspace, int32_t *status_out, v
     }
     return 0;
 }
+
+// ---- decode without caller-provided scratch -------------------------------------------------------
+// The scratch array is part of the library image: every GPU that loads the library holds it until
+// the process exits.  In host code `g_static_scratch` is only a handle for the symbol, not a device
+// address; the address comes from cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[GS_MLA_DECODE_STATIC_SCRATCH_BYTES];
+static void *g_static_scratch_ptr[64] = {nullptr};
+
+GS_EXPORT int gs_mla_decode_static(const gs_mla_decode_args *a, void *stream) {
+    if (!a) return fail_invalid("gs_mla_decode_static: args == NULL");
+    if (a->n_seq < 0 || a->T < 0 || a->H < 0) return fail_invalid("gs_mla_decode_static: negative size");
+    if (a->n_seq == 0 || a->T == 0 || a->H == 0) return 0;
+    const int64_t need = gs_mla_decode_workspace_bytes(a->n_seq, a->T, a->H, a->d_v);
+    if (need > (int64_t) GS_MLA_DECODE_STATIC_SCRATCH_BYTES) {
+        set_error("gs_mla_decode_static: these sizes need %lld bytes of scratch, the built-in array holds %lld "
+                  "(use gs_mla_decode with a caller-allocated workspace)",
+                  (long long) need, (long long) GS_MLA_DECODE_STATIC_SCRATCH_BYTES);
+        return (int) cudaErrorInvalidValue;
+    }
+    int dev = 0;
+    GS_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail_invalid("gs_mla_decode_static: device index beyond 63");
+    void *scratch = g_static_scratch_ptr[dev];
+    if (!scratch) {
+        // first call on this device (it is the current one): resolve the symbol to its device address
+        GS_TRY(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        g_static_scratch_ptr[dev] = scratch;
+    }
+    // the status block must start at zero; the partial records are fully rewritten before they are read
+    GS_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes, (cudaStream_t) stream));
+    gs_mla_decode_args b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = GS_MLA_DECODE_STATIC_SCRATCH_BYTES;
+    return gs_mla_decode(&b, stream);
+}

@@ -83,6 +83,27 @@ int64_t gs_mla_decode_workspace_bytes(int n_seq, int T, int H, int d_v);
 /* Enqueue the decode.  New entry point; the call it stands in for is forward.rs:902-906. */
 int gs_mla_decode(const gs_mla_decode_args *args /* host */, void *stream);
 
+/* gs_mla_decode for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference, whose engine owns and passes every buffer (forward.rs:496-500).  Some hosts of this
+ * library cannot: a plugin running inside another runtime's memory pool, a call issued while that
+ * runtime forbids cudaMalloc (for instance between the capture and the replay set-up of its own
+ * graphs), or a caller with no place to keep a workspace between calls.  For them the split-KV
+ * partials and the status block live in a fixed scratch array inside the library image
+ * (GS_MLA_DECODE_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process
+ * exits); args->workspace and args->workspace_bytes are ignored, everything else is as for
+ * gs_mla_decode.
+ *   - Sizes whose workspace (gs_mla_decode_workspace_bytes) exceeds the scratch array are rejected
+ *     with cudaErrorInvalidValue and a message; one sequence with T <= 2 and H <= 24 fits.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current) and keeps it; make that first call outside any stream capture.  A cudaDeviceReset
+ *     invalidates the kept address: this entry point is not for processes that reset the device.
+ *   - All calls share the one array.  Each call clears the status block on `stream` first; the
+ *     partial records are overwritten before they are read.  Two calls whose kernels overlap on
+ *     the GPU (different streams, or different host threads) race on it: serialise them.
+ *   - Calls neither cudaMalloc nor cudaFree nor any allocating library routine. */
+#define GS_MLA_DECODE_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int gs_mla_decode_static(const gs_mla_decode_args *args /* host */, void *stream);
+
 /* Merge n_parts record blocks (each [rows*d_v acc][rows*2 (m,l)] floats, consecutive blocks
  * part_stride floats apart) into o f32 [rows][d_v]:  M = max m, L = sum l e^(m-M),
  * o = sum acc e^(m-M) / L, zeros when L == 0; the arithmetic of k_mla_combine, ops.cu:552-574,

@@ -1,0 +1,68 @@
+"""The allocation-free decode entry point (gs_mla_decode_static).
+
+Some callers of this library cannot allocate device memory at the time they need attention: a
+plugin that lives inside another runtime's memory pool, or code running while that runtime has
+forbidden cudaMalloc.  For them the library carries a fixed scratch array in its own image.  This
+test calls the entry point through the C ABI twice in a row (the second call meets the scratch
+contents the first one left) and checks both results against the regular entry point, which uses a
+caller-allocated workspace, and against the CPU oracle.  It is collected last so that a failure
+here cannot hide any other test's result.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import check_close, make_decode_inputs
+from gpu_util import to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _args(pkg, torch, q, cache, lens, out, workspace=None):
+    a = pkg._lib.DecodeArgs()
+    n_seq, T, H, d_qk = q.shape
+    a.q, a.cache, a.cache_rows = q.data_ptr(), cache.data_ptr(), cache.shape[0]
+    a.seq_lens = lens.data_ptr()
+    a.page_rows = 64
+    a.scale = 1 / 16
+    a.tail_causal = 1
+    a.o = out.data_ptr()
+    a.n_seq, a.T, a.H, a.d_qk, a.d_v = n_seq, T, H, d_qk, 512
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    return a
+
+
+def test_static_scratch_matches_workspace_entry_point_twice(pkg, cuda, oracle):
+    L = pkg._lib.load()
+    for call, (seed, n, T) in enumerate([(41, 5000, 2), (42, 9001, 1)]):
+        q, cache = make_decode_inputs(seed, 1, T, 20, n)
+        qd, cd = to_dev(cuda, q), to_dev(cuda, cache)
+        lens = to_dev(cuda, np.array([n], np.int32))
+        o_static = cuda.zeros((1, T, 20, 512), dtype=cuda.float32, device="cuda")
+        o_ws = cuda.zeros_like(o_static)
+        ws = pkg.new_workspace(1, T, 20)
+        before = cuda.cuda.memory_allocated()
+        rc = L.gs_mla_decode_static(C.byref(_args(pkg, cuda, qd, cd, lens, o_static)), None)
+        assert rc == 0, L.gs_attn_last_error_string()
+        assert cuda.cuda.memory_allocated() == before  # nothing went through torch's allocator either
+        rc = L.gs_mla_decode(C.byref(_args(pkg, cuda, qd, cd, lens, o_ws, ws)), None)
+        assert rc == 0, L.gs_attn_last_error_string()
+        cuda.cuda.synchronize()
+        a, b = o_static.cpu().numpy(), o_ws.cpu().numpy()
+        check_close(a, b, f"call {call}: static scratch vs caller workspace")
+        check_close(a, oracle.mla_decode(q, cache, [n], 1 / 16), f"call {call}: static scratch vs oracle")
+
+
+def test_static_scratch_rejects_sizes_beyond_its_array(pkg, cuda):
+    L = pkg._lib.load()
+    q, cache = make_decode_inputs(43, 64, 1, 20, 64 * 10)
+    qd, cd = to_dev(cuda, q), to_dev(cuda, cache)
+    lens = to_dev(cuda, np.full(64, 10, np.int32))
+    out = cuda.zeros((64, 1, 20, 512), dtype=cuda.float32, device="cuda")
+    assert pkg.decode_workspace_bytes(64, 1, 20) > 16 * 1024 * 1024
+    rc = L.gs_mla_decode_static(C.byref(_args(pkg, cuda, qd, cd, lens, out)), None)
+    assert rc == 1  # cudaErrorInvalidValue
+    msg = L.gs_attn_last_error_string()
+    assert b"scratch" in msg and b"gs_mla_decode_static" in msg
