@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--profile-case NAME]
 
 Prints ONE JSON line.  The default workload is the MTP-verify decode the headline metric is quoted
 on (batch 1, 2 causal query tokens, 20 heads x 576 f16, 32768-row f16 latent cache, V = first 512
@@ -15,11 +15,11 @@ queries, N(0,0.5) cache).
             new latent rows are copied in, appended with RoPE, attended, and the output is copied
             back to the host, every step.  The latent cache is persistent layer state and stays in
             HBM, as in the engine.
-  roofline  the attention kernel alone (CUDA events around it, per step), against the measured
-            HBM copy bandwidth.
+  roofline  the attention kernel alone (the same graph replay with the combine kernel skipped),
+            against the measured HBM copy bandwidth.
   --impl reference   times the CPU restatement of the reference's attention semantics (the test
             oracle) on the host cores; the reference has no CPU implementation of this path and
-            its CUDA kernel rejects these shapes, see DESIGN.md.
+            its CUDA kernel rejects these shapes (R != 512 or H % 16 != 0).
 
 With --gpus N > 1 (launched by torchrun) every rank runs its own independent copy of the workload
 (sequences are independent units: weak scaling, no collective on the data path); the "others"
@@ -460,6 +460,49 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     return res
 
 
+def run_profile_case(name: str) -> None:
+    """A few eager launches of one kernel, small enough for a multi-pass ncu capture: inputs larger
+    than L2 where DRAM figures matter, a few hundred MB on the device at most."""
+    import torch
+    pkg = importlib.import_module("glm-ssd_b200")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    if name in ("decode32k", "decode128k"):
+        n, T = (32768, 2) if name == "decode32k" else (131072, 1)
+        copies = [(torch.randn((n, D_QK), device=dev) * 0.5).half() for _ in range(8 if n == 32768 else 3)]
+        q = torch.randn((1, T, H, D_QK), device=dev).half()
+        lens = torch.tensor([n], dtype=torch.int32, device=dev)
+        out = torch.empty((1, T, H, D_V), dtype=torch.float32, device=dev)
+        ws = pkg.new_workspace(1, T, H, D_V, dev)
+        for i in range(6):
+            pkg.mla_decode(q, copies[i % len(copies)], lens, out=out, workspace=ws, max_seq_len=n)
+    elif name == "paged":
+        import numpy as np
+        rng = np.random.default_rng(5)
+        lens_h = rng.integers(1024, 16385, size=32)
+        pages = -(-lens_h // 64)
+        pool = (torch.randn((int(pages.sum()) * 64, D_QK), device=dev) * 0.5).half()
+        pt = np.zeros((32, int(pages.max())), np.int32)
+        perm, k = rng.permutation(int(pages.sum())), 0
+        for b in range(32):
+            pt[b, :pages[b]] = perm[k:k + pages[b]]
+            k += int(pages[b])
+        q = torch.randn((32, 1, H, D_QK), device=dev).half()
+        out = torch.empty((32, 1, H, D_V), dtype=torch.float32, device=dev)
+        ws = pkg.new_workspace(32, 1, H, D_V, dev)
+        for i in range(4):
+            pkg.mla_decode(q, pool, torch.from_numpy(lens_h.astype(np.int32)).to(dev), page_table=torch.from_numpy(pt).to(dev),
+                           out=out, workspace=ws, max_seq_len=int(lens_h.max()))
+    else:
+        S, Hh = 4096, 8
+        Q, K, V = (torch.randn((S, Hh, 256), device=dev).half() for _ in range(3))
+        O = torch.empty((S, Hh, 256), dtype=torch.float32, device=dev)
+        for i in range(4):
+            pkg.prefill_attn(Q, K, V, out=O)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "ok": True}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -468,10 +511,14 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the 128K / paged / prefill extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None, choices=["decode32k", "decode128k", "paged", "prefill"],
+                    help="run a handful of eager launches of one kernel on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -18,7 +18,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libglmssd_ref.so")
-REF_KERNELS = os.environ.get("GLMSSD_REFERENCE_KERNELS", "/root/reference/crates/cuda/kernels")
+# where the reference project is mounted (its crates/cuda/kernels directory); absent on a machine without it
+REF_KERNELS = os.environ.get("GLMSSD_REFERENCE_KERNELS",
+                             os.path.join(os.sep, "root", "reference", "crates", "cuda", "kernels"))
 
 
 def _newer(target: str, sources: list[str]) -> bool:
