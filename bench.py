@@ -177,7 +177,61 @@ def run_reference(args) -> None:
         "note": "CPU restatement (oracle port) of the reference's attention semantics on the host cores; the "
                 "reference has no CPU implementation of this path",
     }
+    twin = reference_cuda_twin()
+    if twin is not None:
+        line["reference_cuda_twin"] = twin
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_twin():
+    """The reference's own CUDA kernel (gs_mla_attn, compiled unmodified for sm_100a) on the twin
+    shapes it accepts: R = 512 (V = all 512 columns), H = 32, f32 queries, identity position list,
+    the engine's split policy (16 for T = 1, 4 for T = 2).  Returns None without a GPU or the library."""
+    so = os.path.join(ROOT, "oracle", "_ref", "libglmssd_ref.so")
+    try:
+        import ctypes as C
+        import torch
+        if not (os.path.exists(so) and torch.cuda.is_available()):
+            return None
+        ref = C.CDLL(so)
+        vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+        ref.gs_mla_attn.restype = i32
+        ref.gs_mla_attn.argtypes = [vp, vp, vp, vp, i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        out = {}
+        for name, n, T, Hh, splits in (("ctx32k_T2_H32", 32768, 2, 32, 4), ("ctx32k_T1_H32", 32768, 1, 32, 16),
+                                       ("ctx128k_T1_H32", 131072, 1, 32, 16)):
+            n_copies = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
+            caches = [(torch.randn((n, 512), device=dev) * 0.5).half() for _ in range(n_copies)]
+            q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
+            sel = torch.arange(n, dtype=torch.int32, device=dev).repeat(T, 1).contiguous()
+            cnt = torch.tensor([n - (T - 1 - t) for t in range(T)], dtype=torch.int32, device=dev)
+            o = torch.empty((T, Hh, 512), dtype=torch.float32, device=dev)
+            part = torch.empty(T * (Hh // 16) * splits * (16 * 512 + 32), dtype=torch.float32, device=dev)
+            st = torch.cuda.current_stream().cuda_stream
+
+            def call(i):
+                rc = ref.gs_mla_attn(q.data_ptr(), caches[i % n_copies].data_ptr(), None, sel.data_ptr(), n, cnt.data_ptr(),
+                                     SCALE, o.data_ptr(), part.data_ptr(), T, Hh, 512, splits, st)
+                assert rc == 0, rc
+
+            for i in range(3):
+                call(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 4 * n_copies
+            e0.record()
+            for i in range(reps):
+                call(i)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            out[name] = {"us_per_call": us, "GB/s": n * 1024 / us / 1e3, "splits": splits}
+            del caches
+        return out
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -447,6 +501,24 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
                       else "pool smaller than 2 x L2"}
     del pool
     torch.cuda.empty_cache()
+
+    # -- twin shapes of the reference kernel (R = 512, H = 32), for a like-for-like ratio --------------
+    twin = {}
+    for name, n, T in (("ctx32k_T2_H32", 32768, 2), ("ctx32k_T1_H32", 32768, 1), ("ctx128k_T1_H32", 131072, 1)):
+        if T * 32 > 48:
+            continue  # 64 packed query rows: outside the tcgen05 kernel's 48-row limit
+        nc = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
+        cs = [randn_f16((n, 512), 0.5) for _ in range(nc)]
+        qt = randn_f16((1, T, 32, 512))
+        lt = torch.tensor([n], dtype=torch.int32, device=dev)
+        ot = torch.empty((1, T, 32, 512), dtype=torch.float32, device=dev)
+        wt = pkg.new_workspace(1, T, 32, 512, dev)
+        sec = time_loop(lambda i: pkg.mla_decode(qt, cs[i % nc], lt, out=ot, workspace=wt, max_seq_len=n), steps, warm,
+                        period=nc)
+        twin[name] = {"us_per_call": sec * 1e6, "GB/s": n * 1024 / sec / 1e9}
+        del cs
+        torch.cuda.empty_cache()
+    res["twin_R512"] = twin
 
     # -- causal prefill, 8192 tokens, 20 heads, d = 256 (replicas only; measured on every rank) -------
     S, d = 8192, 256
