@@ -13,6 +13,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 i32, i64, f32, vp = C.c_int, C.c_int64, C.c_float, C.c_void_p
 
 
+class ShardExchange(C.Structure):
+    """Mirror of ``struct gs_shard_exchange``."""
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("epoch", C.c_uint32), ("peer_bufs", C.POINTER(vp)),
+                ("buf_bytes", i64), ("wait_limit_cycles", i64)]
+
+
 class DecodeArgs(C.Structure):
     """Mirror of ``struct gs_mla_decode_args``."""
     _fields_ = [
@@ -20,7 +26,7 @@ class DecodeArgs(C.Structure):
         ("page_table_stride", C.c_int32), ("page_rows", C.c_int32), ("scale", f32), ("tail_causal", C.c_int32),
         ("o", vp), ("part_out", vp), ("workspace", vp), ("workspace_bytes", i64),
         ("n_seq", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("d_qk", C.c_int32), ("d_v", C.c_int32),
-        ("max_seq_len", C.c_int32), ("impl", C.c_int32), ("ev_after_main", vp), ("flags", C.c_int32),
+        ("max_seq_len", C.c_int32), ("impl", C.c_int32), ("ev_after_main", vp), ("flags", C.c_int32), ("exchange", C.POINTER(ShardExchange)),
     ]
 
 
@@ -32,6 +38,12 @@ SIGNATURES = {
     "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_decode_static": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_combine_parts": (i32, [vp, i32, i64, i32, i32, vp, vp]),
+    "gs_shard_exchange_bytes": (i64, [i32, i32, i32]),
+    "gs_peer_alloc": (i32, [C.POINTER(vp), i64]),
+    "gs_peer_free": (i32, [vp]),
+    "gs_peer_export": (i32, [vp, vp]),
+    "gs_peer_open": (i32, [vp, C.POINTER(vp)]),
+    "gs_peer_close": (i32, [vp]),
     "gs_prefill_attn": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]),
     "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),
     "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),

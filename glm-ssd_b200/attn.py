@@ -63,7 +63,7 @@ def new_workspace(n_seq: int, T: int, H: int, d_v: int = 512, device=None) -> to
 
 def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, page_table=None, page_rows=64,
                tail_causal=True, out=None, part_out=None, want_out=True, workspace=None, max_seq_len=0, impl=0,
-               ev_after_main=None, no_combine=False, static_scratch=False):
+               ev_after_main=None, no_combine=False, static_scratch=False, exchange=None):
     """Absorbed-MLA decode.  q f16 [n_seq,T,H,d_qk]; cache f16 [rows,d_qk]; seq_lens i32 [n_seq] (device).
     Returns ``out`` (f32 [n_seq,T,H,d_v]) or, with ``want_out=False``, ``part_out``."""
     L = _lib.load()
@@ -94,6 +94,8 @@ def mla_decode(q, cache, seq_lens, *, scale=SCALE_256, d_v=512, seq_base=None, p
     a.impl = impl
     a.ev_after_main = ev_after_main  # raw cudaEvent_t handle (int) or None
     a.flags = 1 if no_combine else 0
+    if exchange is not None:  # a _lib.ShardExchange kept alive by the caller (see sharded.PeerExchange)
+        a.exchange = C.pointer(exchange)
     if static_scratch:
         # the library's built-in scratch array instead of a workspace: nothing is allocated for the call
         _lib.check(L.gs_mla_decode_static(C.byref(a), _stream()), "gs_mla_decode_static")

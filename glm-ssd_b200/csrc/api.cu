@@ -102,6 +102,8 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
     p.max_seq_len = a->max_seq_len;
     p.splits = 0;
     p.ev_after_main = (cudaEvent_t) a->ev_after_main;
+    p.exchange = a->exchange;
+    if (p.exchange && !a->o) return fail_invalid("gs_mla_decode: the cross-GPU merge writes o; o is required");
     p.no_combine = (a->flags & GS_DECODE_NO_COMBINE) != 0;
     if (int e = device_sm_count(&p.sm_count)) return e;
     const char *why = "";
@@ -160,7 +162,7 @@ GS_EXPORT int gs_mla_combine_parts(const float *parts, int n_parts, int64_t part
     if (reinterpret_cast<uintptr_t>(parts) & 15 || reinterpret_cast<uintptr_t>(o) & 15)
         return fail_invalid("gs_mla_combine_parts: parts and o must be 16-byte aligned");
     // every block is one segment that holds all `rows` rows: a single group with H := rows
-    CombinePlan c;
+    CombinePlan c{};
     c.acc = parts;
     c.ml = parts + (int64_t) rows * d_v;
     c.desc = nullptr;

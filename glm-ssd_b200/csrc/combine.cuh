@@ -23,8 +23,10 @@ struct CombineSmem {
     float4 part[CB_LANES][CB_COLS / 4];
 };
 
-// All CB_NT threads of the CTA call this with the same (row, col0).
-__device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int col0, CombineSmem &S) {
+// All CB_NT threads of the CTA call this with the same (row, col0).  Returns true in the threads that hold a
+// result: `a` = 4 merged (unnormalised) accumulator columns starting at `col`, with the row's M and L.
+__device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, int row, int col0, CombineSmem &S, float4 &a_out,
+                                                     float &M_out, float &L_out, int &col_out) {
     const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int quad = tid % (CB_COLS / 4), sl = tid / (CB_COLS / 4);
@@ -115,6 +117,7 @@ __device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int 
     S.part[sl][quad] = a;
     __syncthreads();
     const float L = S.L;
+    bool holds = false;
     if (sl == 0 && col < C.d_v) {
 #pragma unroll
         for (int j = 1; j < CB_LANES; j++) {
@@ -124,10 +127,26 @@ __device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int 
             a.z += u.z;
             a.w += u.w;
         }
+        holds = true;
+    }
+    a_out = a;
+    M_out = M;
+    L_out = L;
+    col_out = col;
+    __syncthreads();  // shared memory is reused by the next item
+    return holds;
+}
+
+// Merge one item and write it: normalised output and/or the merged record.
+__device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int col0, CombineSmem &S) {
+    float4 a;
+    float M, L;
+    int col;
+    if (combine_item_compute(C, row, col0, S, a, M, L, col)) {
         if (C.part_out) {
             const int64_t rows_total = (int64_t) C.n_seq * C.T * C.H;
             *reinterpret_cast<float4 *>(C.part_out + (int64_t) row * C.d_v + col) = a;
-            if (col0 == 0 && quad == 0) {
+            if (col == 0) {
                 C.part_out[rows_total * C.d_v + (int64_t) row * 2] = M;
                 C.part_out[rows_total * C.d_v + (int64_t) row * 2 + 1] = L;
             }
@@ -138,7 +157,6 @@ __device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int 
                 make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         }
     }
-    __syncthreads();  // shared memory is reused by the next item
 }
 
 }  // namespace gs

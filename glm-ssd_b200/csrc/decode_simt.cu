@@ -243,7 +243,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     GS_TRY(cudaGetLastError());
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     if (p.no_combine) return 0;
-    CombinePlan c;
+    CombinePlan c{};
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;
     c.desc = nullptr;
@@ -256,6 +256,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     c.d_v = p.d_v;
     c.o = p.o;
     c.part_out = p.part_out;
+    if (p.exchange) return launch_exchange_combine(c, *p.exchange, p.o, p.status, p.sm_count, st);
     return launch_combine(c, st);
 }
 

@@ -723,7 +723,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
-    CombinePlan c;
+    CombinePlan c{};
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;
     c.desc = p.ws_desc;
@@ -742,6 +742,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     if (e) return e;
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     if (p.no_combine) return 0;
+    if (p.exchange) return launch_exchange_combine(c, *p.exchange, p.o, p.status, p.sm_count, st);
     return launch_combine(c, st);
 }
 

@@ -31,6 +31,7 @@ struct DecodeProblem {
     int splits;           // CUDA-core kernel: splits per (sequence, token); 0 = choose
     int sm_count;
     bool no_combine;      // stop after the attention kernel (timing aid)
+    const gs_shard_exchange *exchange;  // cross-GPU merge of the records instead of a local output, or nullptr
     cudaEvent_t ev_after_main;  // recorded between the attention kernel and the combine, or nullptr
 };
 
@@ -49,6 +50,9 @@ struct CombinePlan {
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
 int launch_combine(const CombinePlan &c, cudaStream_t st);
+// local merge + peer-to-peer exchange of the merged records + final merge (exchange.cu)
+int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o, int32_t *status, int sm_count,
+                            cudaStream_t st);
 bool decode_umma_supported(const DecodeProblem &p, const char **why);
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st);
 

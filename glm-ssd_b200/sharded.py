@@ -58,3 +58,62 @@ def sharded_decode(local_partial: Callable[[], torch.Tensor], combine: Callable[
     part = local_partial()
     blocks = exchange_parts(part, group)
     return combine(blocks, dist.get_world_size(group))
+
+
+class PeerExchange:
+    """Exchange buffers for the peer-to-peer merge of a sequence-sharded decode (one per rank, mapped
+    into every rank's process).  ``next()`` returns the ``gs_shard_exchange`` argument of the next call;
+    every rank must call it in step.  Allocation and mapping happen here, once; the decode calls
+    themselves allocate nothing."""
+
+    def __init__(self, rows: int, d_v: int = 512, group=None, wait_limit_cycles: int = 0, world=None, rank=None,
+                 handles=None):
+        import ctypes as C
+
+        from . import _lib
+        self._C, self._lib = C, _lib
+        L = _lib.load()
+        self.world = dist.get_world_size(group) if world is None else world
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.bytes = int(L.gs_shard_exchange_bytes(self.world, rows, d_v))
+        self.wait_limit_cycles = wait_limit_cycles
+        self.epoch = 0
+        self._opened = []
+        local = C.c_void_p()
+        _lib.check(L.gs_peer_alloc(C.byref(local), self.bytes), "gs_peer_alloc")
+        self.local = local.value
+        handle = (C.c_ubyte * 64)()
+        _lib.check(L.gs_peer_export(self.local, handle), "gs_peer_export")
+        self.handle = bytes(handle)
+        if handles is None:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self.handle, group=group)
+        self.ptrs = (C.c_void_p * self.world)()
+        for r in range(self.world):
+            if r == self.rank:
+                self.ptrs[r] = self.local
+            else:
+                p = C.c_void_p()
+                buf = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+                _lib.check(L.gs_peer_open(buf, C.byref(p)), "gs_peer_open")
+                self.ptrs[r] = p.value
+                self._opened.append(p.value)
+
+    def next(self, device_epoch: bool = False):
+        """``device_epoch=True`` (on every call of every rank) keeps the epoch in the buffers: graph-capturable."""
+        self.epoch += 1
+        x = self._lib.ShardExchange()
+        x.world, x.rank, x.epoch = self.world, self.rank, 0 if device_epoch else self.epoch
+        x.peer_bufs = self._C.cast(self.ptrs, self._C.POINTER(self._C.c_void_p))
+        x.buf_bytes = self.bytes
+        x.wait_limit_cycles = self.wait_limit_cycles
+        return x
+
+    def close(self):
+        L = self._lib.load()
+        for p in self._opened:
+            L.gs_peer_close(p)
+        self._opened = []
+        if self.local:
+            L.gs_peer_free(self.local)
+            self.local = None

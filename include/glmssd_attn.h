@@ -45,6 +45,25 @@ int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream);
  * queries, any head count, several sequences per call, and dense-range or paged addressing
  * instead of a materialised position list (the dense list of ops.cu:728-731).
  * ---------------------------------------------------------------------------------------------- */
+/* Cross-GPU merge for a context sharded by sequence ranges over `world` GPUs of one node (one
+ * process per GPU).  Every rank attends its own rows; instead of a local output each rank's merged
+ * (acc, m, l) record is stored straight into every rank's exchange buffer over NVLink (plain peer
+ * stores), a per-item flag is released, and each rank merges the `world` records it received - the
+ * reference's split/combine algebra (ops.cu:539-574) with "split" = GPU.  No counterpart in the
+ * reference, which is single-GPU.  All ranks must make the same call with the same epoch. */
+typedef struct gs_shard_exchange {
+    int32_t world, rank;       /* 2..8 ranks */
+    uint32_t epoch;            /* 1, 2, 3, ... : strictly increasing from call to call, equal on all ranks; or 0
+                                  on every call of every rank: the epoch is then kept in the exchange buffers
+                                  themselves, which lets the call be captured in a CUDA graph and replayed */
+    void *const *peer_bufs;    /* host array [world]: every rank's exchange buffer as mapped in THIS process
+                                  (gs_peer_alloc / gs_peer_export / gs_peer_open); peer_bufs[rank] is local */
+    int64_t buf_bytes;         /* size of each buffer, >= gs_shard_exchange_bytes() */
+    int64_t wait_limit_cycles; /* bound of the wait for the other ranks' flags; 0 = about one second.  When
+                                  it runs out the kernel sets bit 16 of the workspace status word and
+                                  returns without writing o */
+} gs_shard_exchange;
+
 typedef struct gs_mla_decode_args {
     const void *q;             /* f16 [n_seq][T][H][d_qk] */
     const void *cache;         /* f16 [cache_rows][d_qk] row-major (the layout of forward.rs:388-404) */
@@ -74,6 +93,8 @@ typedef struct gs_mla_decode_args {
     int32_t flags;             /* bit 0 (GS_DECODE_NO_COMBINE): run the attention kernel only and leave the split
                                   partials in the workspace (o / part_out are not written); for timing that
                                   kernel alone */
+    const gs_shard_exchange *exchange; /* host; NULL = single GPU.  When set, o receives the result merged
+                                  over all ranks (on every rank) and part_out is ignored */
 } gs_mla_decode_args;
 #define GS_DECODE_NO_COMBINE 1
 
@@ -103,6 +124,17 @@ int gs_mla_decode(const gs_mla_decode_args *args /* host */, void *stream);
  *   - Calls neither cudaMalloc nor cudaFree nor any allocating library routine. */
 #define GS_MLA_DECODE_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
 int gs_mla_decode_static(const gs_mla_decode_args *args /* host */, void *stream);
+
+/* Bytes of one rank's exchange buffer for `rows` = n_seq*T*H query rows (host function). */
+int64_t gs_shard_exchange_bytes(int world, int rows, int d_v);
+/* Exchange-buffer plumbing (host functions; the only entry points that allocate): a zeroed device
+ * buffer that other processes on the node can map, its 64-byte handle, mapping a peer's handle
+ * (enables peer access on first use), and the matching releases. */
+int gs_peer_alloc(void **ptr, int64_t bytes);
+int gs_peer_free(void *ptr);
+int gs_peer_export(const void *ptr, void *handle64);
+int gs_peer_open(const void *handle64, void **ptr);
+int gs_peer_close(void *ptr);
 
 /* Merge n_parts record blocks (each [rows*d_v acc][rows*2 (m,l)] floats, consecutive blocks
  * part_stride floats apart) into o f32 [rows][d_v]:  M = max m, L = sum l e^(m-M),
