@@ -19,6 +19,14 @@ class ShardExchange(C.Structure):
                 ("buf_bytes", i64), ("wait_limit_cycles", i64)]
 
 
+class LayerStep(C.Structure):
+    """Mirror of ``struct gs_mla_layer_step``."""
+    _fields_ = [("q_host", vp), ("kv_host", vp), ("o_host", vp), ("q_dev", vp), ("kv_dev", vp), ("o_dev", vp),
+                ("cache", vp), ("cache_rows", i64), ("seq_len_dev", vp), ("workspace", vp), ("workspace_bytes", i64),
+                ("pos0", i64), ("T", C.c_int32), ("H", C.c_int32), ("d_qk", C.c_int32), ("d_v", C.c_int32),
+                ("d_rope", C.c_int32), ("rope_base", f32), ("scale", f32)]
+
+
 class DecodeArgs(C.Structure):
     """Mirror of ``struct gs_mla_decode_args``."""
     _fields_ = [
@@ -48,6 +56,7 @@ SIGNATURES = {
     "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),
     "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "gs_rope_f16_inplace": (i32, [vp, i32, i32, i32, i32, i64, f32, vp]),
+    "gs_mla_layer_step_host": (i32, [C.POINTER(LayerStep), vp]),
     "gs_attn_last_error_string": (C.c_char_p, []),
     "gs_attn_version": (C.c_char_p, []),
     "gs_mla_decode_status": (i32, [vp, C.POINTER(C.c_int32), vp]),

@@ -198,6 +198,15 @@ class MlaDecodeLayer:
         self._o_dev = torch.empty((1, T_max, H, d_v), dtype=torch.float32, device=self.device)
         self._o_host = torch.empty((1, T_max, H, d_v), dtype=torch.float32).pin_memory()
         self._len_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        st = _lib.LayerStep()
+        st.o_host = self._o_host.data_ptr()
+        st.q_dev, st.kv_dev, st.o_dev = self._q_dev.data_ptr(), self._kv_dev.data_ptr(), self._o_dev.data_ptr()
+        st.cache, st.cache_rows = self.cache.data_ptr(), ctx
+        st.seq_len_dev = self._seq_len.data_ptr()
+        st.workspace, st.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        st.H, st.d_qk, st.d_v, st.d_rope = H, d_qk, d_v, d_rope
+        st.rope_base, st.scale = 10000.0, SCALE_256
+        self._step = st
 
     def rollback(self, n: int = 1) -> None:
         """Drop the last n positions (rejected MTP draft): the rows are simply overwritten by the next
@@ -205,24 +214,17 @@ class MlaDecodeLayer:
         self.pos = max(0, self.pos - n)
 
     def step(self, q_host: torch.Tensor, kv_host: torch.Tensor) -> torch.Tensor:
-        """q_host f16 [T,H,d_qk], kv_host f32 [T,d_qk] in pinned host memory -> f32 [T,H,d_v] (host)."""
+        """q_host f16 [T,H,d_qk], kv_host f32 [T,d_qk] in pinned host memory -> f32 [T,H,d_v] (host).
+        One C call enqueues copy-in, append, attention and copy-out; then the stream is drained."""
         T = q_host.shape[0]
         if T > self.T_max:
             raise ValueError("T exceeds T_max")
         if self.pos + T > self.ctx:
             raise RuntimeError(f"context full ({self.ctx} tokens)")
-        q = self._q_dev[:, :T]
-        kv = self._kv_dev[:T]
-        q.copy_(q_host.view(1, T, self.H, self.d_qk), non_blocking=True)
-        kv.copy_(kv_host, non_blocking=True)
-        rope_kv_append_at(kv, self.cache, self.pos, d_rope=self.d_rope)
+        s = self._step
+        s.q_host, s.kv_host = q_host.data_ptr(), kv_host.data_ptr()
+        s.pos0, s.T = self.pos, T
+        _lib.check(_lib.load().gs_mla_layer_step_host(C.byref(s), _stream()), "gs_mla_layer_step_host")
         self.pos += T
-        self._len_host[0] = self.pos
-        self._seq_len.copy_(self._len_host, non_blocking=True)
-        out = self._o_dev[:, :T]
-        mla_decode(q, self.cache, self._seq_len, d_v=self.d_v, out=out,
-                   workspace=self.workspace, max_seq_len=self.pos)
-        oh = self._o_host[:, :T]
-        oh.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return oh[0]
+        return self._o_host[0, :T]

@@ -51,12 +51,15 @@ struct AppendParams {
     int64_t pos0_host;
     int page_table_stride, page_rows;
     int T, d_row, d_rope;
+    int32_t *len_out;  // optional: receives len_val (the sequence length after the append), for the decode that follows
+    int32_t len_val;
     RopeTable tab;
 };
 
 // grid (T, n_seq); thread j handles column pair (2j, 2j+1)
 __global__ void k_rope_append(const AppendParams P) {
     const int t = blockIdx.x, b = blockIdx.y;
+    if (P.len_out && t == 0 && b == 0 && threadIdx.x == 0) *P.len_out = P.len_val;
     const int64_t pos = (P.pos0 ? (int64_t) P.pos0[b] : P.pos0_host) + t;
     int64_t row;
     if (P.page_table) {
@@ -182,5 +185,57 @@ GS_EXPORT int gs_rope_f16_inplace(void *x, int S, int H, int d, int d_rope, int6
     k_rope_f16<<<(unsigned) ((n_pairs + 255) / 256), 256, 0, (cudaStream_t) stream>>>((__half *) x, n_pairs, H, d, d_rope,
                                                                                      pos0, tab);
     GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+// ---- one decode step of a layer with host buffers ---------------------------------------------------
+GS_EXPORT int gs_mla_layer_step_host(const gs_mla_layer_step *s, void *stream) {
+    if (!s) return fail_invalid("gs_mla_layer_step_host: args == NULL");
+    if (s->T <= 0 || s->H <= 0) return 0;
+    if (!s->q_host || !s->kv_host || !s->o_host || !s->q_dev || !s->kv_dev || !s->o_dev || !s->cache || !s->seq_len_dev ||
+        !s->workspace)
+        return fail_invalid("gs_mla_layer_step_host: null pointer");
+    if (int e = check_rope(s->d_qk, s->d_rope)) return e;
+    if (s->pos0 < 0 || s->pos0 + s->T > s->cache_rows) {
+        set_error("context full (%lld tokens)", (long long) s->cache_rows);  // forward.rs:839-841
+        return (int) cudaErrorInvalidValue;
+    }
+    cudaStream_t st = (cudaStream_t) stream;
+    const size_t q_bytes = (size_t) s->T * s->H * s->d_qk * 2, kv_bytes = (size_t) s->T * s->d_qk * 4;
+    GS_TRY(cudaMemcpyAsync(s->q_dev, s->q_host, q_bytes, cudaMemcpyHostToDevice, st));
+    GS_TRY(cudaMemcpyAsync(s->kv_dev, s->kv_host, kv_bytes, cudaMemcpyHostToDevice, st));
+    AppendParams P{};
+    P.kv = (const float *) s->kv_dev;
+    P.cache = (__half *) s->cache + s->pos0 * s->d_qk;
+    P.pos0 = nullptr;
+    P.pos0_host = s->pos0;
+    P.page_rows = 1;
+    P.T = s->T;
+    P.d_row = s->d_qk;
+    P.d_rope = s->d_rope;
+    P.len_out = s->seq_len_dev;
+    P.len_val = (int32_t) (s->pos0 + s->T);
+    fill_table(P.tab, s->d_rope, s->rope_base);
+    k_rope_append<<<dim3(s->T, 1), 128, 0, st>>>(P);
+    GS_TRY(cudaGetLastError());
+    gs_mla_decode_args a{};
+    a.q = s->q_dev;
+    a.cache = s->cache;
+    a.cache_rows = s->cache_rows;
+    a.seq_lens = s->seq_len_dev;
+    a.page_rows = 64;
+    a.scale = s->scale;
+    a.tail_causal = 1;
+    a.o = (float *) s->o_dev;
+    a.workspace = s->workspace;
+    a.workspace_bytes = s->workspace_bytes;
+    a.n_seq = 1;
+    a.T = s->T;
+    a.H = s->H;
+    a.d_qk = s->d_qk;
+    a.d_v = s->d_v;
+    a.max_seq_len = (int32_t) (s->pos0 + s->T);
+    if (int e = gs_mla_decode(&a, stream)) return e;
+    GS_TRY(cudaMemcpyAsync(s->o_host, s->o_dev, (size_t) s->T * s->H * s->d_v * 4, cudaMemcpyDeviceToHost, st));
     return 0;
 }

@@ -171,6 +171,27 @@ int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos0, const i
  * position pos0 + s. */
 int gs_rope_f16_inplace(void *x, int S, int H, int d, int d_rope, int64_t pos0, float rope_base, void *stream);
 
+/* One decode step of one MLA layer with HOST buffers: the sequence of Engine::mla around the
+ * attention call (forward.rs:849-860 then :900-906) enqueued by a single call - copy the queries and
+ * the new latent rows in (pinned host memory for true asynchrony), append the rows at pos0 with
+ * RoPE, attend seq_len = pos0 + T rows with the new rows visible, copy the output back.  Nothing is
+ * synchronised: the result is in o_host once `stream` has drained.  The caller owns every buffer. */
+typedef struct gs_mla_layer_step {
+    const void *q_host;   /* f16 [T][H][d_qk] */
+    const float *kv_host; /* f32 [T][d_qk] new latent rows */
+    float *o_host;        /* f32 [T][H][d_v] */
+    void *q_dev, *kv_dev, *o_dev; /* device staging of the same sizes */
+    void *cache;          /* f16 [cache_rows][d_qk] */
+    int64_t cache_rows;
+    int32_t *seq_len_dev; /* one int32 on the device, written by the step */
+    void *workspace;      /* gs_mla_decode_workspace_bytes(1, T, H, d_v) */
+    int64_t workspace_bytes;
+    int64_t pos0;         /* position of the first new row */
+    int32_t T, H, d_qk, d_v, d_rope;
+    float rope_base, scale;
+} gs_mla_layer_step;
+int gs_mla_layer_step_host(const gs_mla_layer_step *step /* host */, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Diagnostics.
  * ---------------------------------------------------------------------------------------------- */
