@@ -74,8 +74,9 @@ constexpr int STAGES = 2;
 constexpr int N_MMA_WARPS = 3;           // concurrently issuing MMA warps
 constexpr int NTHREADS = 32 * (1 + N_MMA_WARPS + 4);  // warp 0 producer, warps 1-3 MMA, warps 4-7 softmax group
 constexpr int TMEM_COLS = 512;
-constexpr int SLOT = 64;                 // TMEM column slot: one S^T partial per issuer, then the O tiles
-constexpr int O_COL0 = N_MMA_WARPS * SLOT;
+// TMEM columns (slots of NQ columns): S^T partials [2 buffers][N_MMA_WARPS issuers], then the 4 O^T tiles:
+// 10 x 48 = 480 of the 512 columns for NQ = 48
+constexpr int O_SLOT0 = 2 * N_MMA_WARPS;
 constexpr int NVT = 4;                   // 128-column value tiles (d_v = 512)
 constexpr int MAX_SEQ = 1024;
 constexpr float RESCALE_LOG2 = 6.0f;     // lazy rescale threshold, in log2 units
@@ -101,7 +102,7 @@ struct UmmaParams {
 
 struct Barriers {
     uint64_t kv_full[STAGES], kv_empty[STAGES];
-    uint64_t s_full, s_empty, p_full[2], p_empty[2];
+    uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
     uint64_t q_full, q_empty, o_full, o_empty;
 };
 
@@ -174,7 +175,7 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t 
         for (int ks = 0; ks < 4; ks++)
 #pragma unroll
             for (int mt = MT_LO; mt < MT_HI; mt++)
-                umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128), d_pt + (p_lo + ks * 16),
+                umma_ss(tmem + (O_SLOT0 + mt) * NQ, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128), d_pt + (p_lo + ks * 16),
                         idesc, acc0 || ks > 0);
     } else {
 #pragma unroll
@@ -182,7 +183,7 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t 
             if (ks < nk) {
 #pragma unroll
                 for (int mt = MT_LO; mt < MT_HI; mt++)
-                    umma_ss(tmem + O_COL0 + mt * SLOT, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128),
+                    umma_ss(tmem + (O_SLOT0 + mt) * NQ, d_vt + (kv_lo + 2 * mt * (BLK_BYTES >> 4) + ks * 128),
                             d_pt + (p_lo + ks * 16), idesc, acc0 || ks > 0);
             }
     }
@@ -222,9 +223,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             mbar_init(&B.kv_full[s], 1);
             mbar_init(&B.kv_empty[s], N_MMA_WARPS);
         }
-        mbar_init(&B.s_full, N_MMA_WARPS);
-        mbar_init(&B.s_empty, 4);
         for (int s = 0; s < 2; s++) {
+            mbar_init(&B.s_full[s], N_MMA_WARPS);
+            mbar_init(&B.s_empty[s], 4);
             mbar_init(&B.p_full[s], 4);
             mbar_init(&B.p_empty[s], N_MMA_WARPS);
         }
@@ -366,30 +367,52 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         bool ok = true;
         while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
             ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
+            // S of tile j+1 is issued ahead of P.V of tile j whenever its data has already landed, so it
+            // runs on the tensor pipe while the softmax of tile j is computed.
+            auto issue_s = [&](uint32_t i) {
+                const int s = i & 1;
+                const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
+                tc_fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < K_PER; k++) {
+                        const int kidx = mw * K_PER + k;
+                        if (kidx < KSTEPS) {
+                            const int kb = kidx >> 2, ks = kidx & 3;
+                            umma_ss(tmem + (s * N_MMA_WARPS + mw) * NQ, d_kmaj + (kv_lo + kb * (BLK_BYTES >> 4) + ks * 2),
+                                    d_kmaj + (q_lo + kb * (NQ * 128 >> 4) + ks * 2), idesc_s, k != 0);
+                        }
+                    }
+                    umma_commit(&B.s_full[s]);
+                }
+                __syncwarp();
+            };
+            bool s_ahead = false;  // S of the current tile was already issued during the previous iteration
             for (int j = 0; ok && j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
                 const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
-                // ---- S^T(partial) = C_tile[:, my k-steps] . Q^T[my k-steps] ----
-                ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
-                     mbar_wait(&B.s_empty, (it & 1) ^ 1, abort_flag, P.status, ST_MMA);
-                if (!ok) break;
-                if (mw == 0 && lane == 0) GS_STAMP(it, PF_KV_FULL);
-                tc_fence_after();
-                if (elect_one()) {
-#pragma unroll
-                    for (int i = 0; i < K_PER; i++) {
-                        const int kidx = mw * K_PER + i;
-                        if (kidx < KSTEPS) {
-                            const int kb = kidx >> 2, ks = kidx & 3;
-                            umma_ss(tmem + mw * SLOT, d_kmaj + (kv_lo + kb * (BLK_BYTES >> 4) + ks * 2),
-                                    d_kmaj + (q_lo + kb * (NQ * 128 >> 4) + ks * 2), idesc_s, i != 0);
-                        }
-                    }
-                    umma_commit(&B.s_full);
+                if (!s_ahead) {
+                    ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
+                         mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
+                    if (!ok) break;
+                    if (mw == 0 && lane == 0) GS_STAMP(it, PF_KV_FULL);
+                    issue_s(it);
+                    if (mw == 0 && lane == 0) GS_STAMP(it, PF_S_ISSUED);
                 }
-                __syncwarp();
-                if (mw == 0 && lane == 0) GS_STAMP(it, PF_S_ISSUED);
+                s_ahead = false;
+                if (j + 1 < sg.n_tiles) {
+                    const uint32_t i1 = it + 1;
+                    const uint32_t ph1 = (i1 >> 1) & 1;
+                    // uniform over the warp: every lane polls the same barriers
+                    const bool landed = mbar_test(&B.kv_full[i1 & 1], ph1) && mbar_test(&B.s_empty[i1 & 1], ph1 ^ 1);
+                    if (__all_sync(0xffffffffu, landed)) {
+                        if (mw == 0 && lane == 0) GS_STAMP(i1, PF_KV_FULL);
+                        issue_s(i1);
+                        if (mw == 0 && lane == 0) GS_STAMP(i1, PF_S_ISSUED);
+                        s_ahead = true;
+                    }
+                }
                 // ---- O^T[my tiles] += V^T . P^T ----
                 ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
                 if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
@@ -451,7 +474,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                (void) mbar_wait(&B.s_full, it & 1, abort_flag, P.status, ST_SOFTMAX);
+                (void) mbar_wait(&B.s_full[s], ph, abort_flag, P.status, ST_SOFTMAX);
                 GS_STAMP(it, PF_S_FULL);
                 tc_fence_after();
                 const int row0 = sg.r0 + j * TILE;
@@ -462,9 +485,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
                     uint32_t r0[16], r1[16], r2[16];
-                    tmem_ld16(tmem + lane_base + 0 * SLOT + c * 16, r0);
-                    tmem_ld16(tmem + lane_base + 1 * SLOT + c * 16, r1);
-                    tmem_ld16(tmem + lane_base + 2 * SLOT + c * 16, r2);
+                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 0) * NQ + c * 16, r0);
+                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 1) * NQ + c * 16, r1);
+                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 2) * NQ + c * 16, r2);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
@@ -481,7 +504,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&B.s_empty);
+                if (lane == 0) mbar_arrive(&B.s_empty[s]);
                 GS_STAMP(it, PF_S_LOADED);
                 if (boundary) {
 #pragma unroll
@@ -558,13 +581,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     *reinterpret_cast<uint4 *>(pbuf + g * 1024) = v;
                 }
                 if (rescale) {
-                    // every MMA issued before this tile's S has completed, P.V of the previous tile included
+                    // S of this tile may have been issued ahead of P.V of the previous one: wait for that P.V
+                    (void) mbar_wait(&B.p_empty[s ^ 1], ((it - 1) >> 1) & 1, abort_flag, P.status, ST_SOFTMAX);
+                    tc_fence_after();
 #pragma unroll 1
                     for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                         for (int c = 0; c < NQ / 16; c++) {
                             uint32_t r[16];
-                            const uint32_t addr = tmem + lane_base + O_COL0 + mt * SLOT + c * 16;
+                            const uint32_t addr = tmem + lane_base + (O_SLOT0 + mt) * NQ + c * 16;
                             tmem_ld16(addr, r);
                             tmem_wait_ld();
 #pragma unroll
@@ -617,12 +642,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
             float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
-#pragma unroll 1
+#pragma unroll
             for (int mt = 0; mt < NVT; mt++) {
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
                     uint32_t r[16];
-                    tmem_ld16(tmem + lane_base + O_COL0 + mt * SLOT + c * 16, r);
+                    tmem_ld16(tmem + lane_base + (O_SLOT0 + mt) * NQ + c * 16, r);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; i++) {

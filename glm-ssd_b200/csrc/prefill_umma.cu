@@ -154,9 +154,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
         for (int j = 0; ok && j < n_tiles; j++) {
             if (j + 1 < n_tiles) {
                 ok = mbar_wait(&B.k_full, (j + 1) & 1, abort_flag, P.status, 2);
+                // S(j+1) overwrites the tensor-memory columns P(j-1) lives in.  Two MMAs are only ordered with
+                // respect to each other on the same accumulator, so P.V(j-1) must have completed first.
+                if (ok && j > 0) ok = mbar_wait(&B.pv_done, (j - 1) & 1, abort_flag, P.status, 2);
                 if (!ok) break;
                 tc_fence_after();
-                issue_s(j + 1);  // S(j+1) reuses the buffer of S(j-1)/P(j-1): P.V(j-1) was issued before it
+                issue_s(j + 1);
             }
             ok = mbar_wait(&B.p_full[j & 1], (j >> 1) & 1, abort_flag, P.status, 2) &&
                  mbar_wait(&B.v_full, j & 1, abort_flag, P.status, 2);

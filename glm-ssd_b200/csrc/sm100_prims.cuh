@@ -53,6 +53,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test of a phase (try_wait may suspend the thread for microseconds until the phase completes).
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Every wait in the kernels is bounded: after kWaitLimitCycles without completion (or as soon as
 // another thread of the CTA has flagged an abort) the wait gives up, records where in the device
 // status word and returns false; the caller then leaves through the kernel's common exit, which

@@ -52,6 +52,17 @@ def test_config4_prefill_8192_with_rope(pkg, cuda, oracle):
     check_close(o12.cpu().numpy(), (got + o2).cpu().numpy(), "linearity in V", 4e-3, 4e-4)
 
 
+def test_prefill_run_to_run_bit_stable(pkg, cuda):
+    # many key tiles per query block: any unordered reuse of tensor memory shows up as run-to-run differences
+    Q, K, V = _qkv(6, 4096, 8, 256)
+    Qd, Kd, Vd = to_dev(cuda, Q), to_dev(cuda, K), to_dev(cuda, V)
+    first = pkg.prefill_attn(Qd, Kd, Vd).clone()
+    for _ in range(8):
+        again = pkg.prefill_attn(Qd, Kd, Vd)
+        cuda.cuda.synchronize()
+        assert cuda.equal(first, again)
+
+
 def test_prefill_f16_output(pkg, cuda, oracle):
     Q, K, V = _qkv(5, 200, 4, 256)
     got = pkg.prefill_attn(to_dev(cuda, Q), to_dev(cuda, K), to_dev(cuda, V), out_f16=True)
