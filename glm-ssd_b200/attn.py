@@ -50,6 +50,12 @@ def f32_to_f16(x, y, n):
     _lib.check(_lib.load().gs_f32_to_f16(_ptr(x), _ptr(y), n, _stream()), "gs_f32_to_f16")
 
 
+def quant_q8_rows(x, q, d, n):
+    """``gs_quant_q8_rows`` (crates/cuda/src/lib.rs:96): the KV-append of the Q8 latent cache.
+    x f32 [n]; q int8 [n]; d f16 [n/32]."""
+    _lib.check(_lib.load().gs_quant_q8_rows(_ptr(x), _ptr(q), _ptr(d), n, _stream()), "gs_quant_q8_rows")
+
+
 # ---- extended entry points -------------------------------------------------------------------------
 
 def decode_workspace_bytes(n_seq: int, T: int, H: int, d_v: int = 512) -> int:

@@ -121,7 +121,6 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
                           void *stream) {
     // same rejections as the reference launcher (ops.cu:581)
     if (R != 512 || H % 16 != 0 || splits < 1) return fail_invalid("gs_mla_attn: need R == 512, H % 16 == 0, splits >= 1");
-    if (C_scales) return fail_invalid("gs_mla_attn: the Q8 latent cache (C_scales != NULL) is not implemented");
     if (T <= 0 || H <= 0) return 0;
     if (!q || !C || !sel || !cnt || !o) return fail_invalid("gs_mla_attn: null pointer");
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
@@ -130,6 +129,7 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     p.q = q;
     p.q_is_f32 = true;
     p.cache = (const __half *) C;
+    p.cache_scales = (const __half *) C_scales;  // non-null: int8 rows + f16 scale per 32 values (ops.cu:427)
     p.cache_rows = 0;
     p.seq_lens = cnt;
     p.sel = sel;

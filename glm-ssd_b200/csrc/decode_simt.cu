@@ -21,7 +21,8 @@ constexpr int NT = 256;  // threads per CTA
 
 struct SimtParams {
     const void *q;
-    const __half *cache;
+    const __half *cache;        // f16 rows, or int8 rows when `scales` is set
+    const __half *scales;       // Q8 cache: one f16 scale per 32 values, [rows][d_qk/32]; nullptr = f16 cache
     const int32_t *seq_lens, *seq_base, *page_table, *sel;
     int page_table_stride, page_rows, sel_stride;
     float scale;
@@ -30,7 +31,7 @@ struct SimtParams {
     int T, H, d_qk, d_v, splits;
 };
 
-template <typename QT>
+template <typename QT, bool Q8>
 __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
     const int split = blockIdx.x, hg = blockIdx.y, bt = blockIdx.z;
     const int b = bt / P.T, t = bt % P.T;
@@ -76,11 +77,41 @@ __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
     const int vec_per_row = d_qk / 8;
     for (int kb = s0; kb < s1; kb += KT) {
         const int nk = min(KT, s1 - kb);
-        for (int i = tid; i < KT * vec_per_row; i += NT) {
-            const int kk = i / vec_per_row, c = i % vec_per_row;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (kk < nk) val = reinterpret_cast<const uint4 *>(P.cache + rows(kb + kk) * d_qk)[c];
-            reinterpret_cast<uint4 *>(tile + kk * d_qk)[c] = val;
+        if (Q8) {
+            // int8 rows with one f16 scale per 32 values: rebuild the f16 tile as half_rn(scale * q), the
+            // values the reference's Q8 branch attends over (crates/cuda/kernels/ops.cu:461-477)
+            const int chunks = d_qk / 16;  // one 16-byte load of int8 -> two 16-byte stores of f16
+            const int8_t *c8 = reinterpret_cast<const int8_t *>(P.cache);
+            for (int i = tid; i < KT * chunks; i += NT) {
+                const int kk = i / chunks, c = i - kk * chunks;
+                uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                if (kk < nk) {
+                    const int64_t row = rows(kb + kk);
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(c8 + row * d_qk) + c);
+                    const float sc = __half2float(P.scales[row * (d_qk / 32) + (c >> 1)]);
+                    auto pack = [sc](uint32_t w, uint32_t &h01, uint32_t &h23) {
+                        const float f0 = sc * (float) (int8_t) (w), f1 = sc * (float) (int8_t) (w >> 8);
+                        const float f2 = sc * (float) (int8_t) (w >> 16), f3 = sc * (float) (int8_t) (w >> 24);
+                        const __half2 a = __floats2half2_rn(f0, f1), b2 = __floats2half2_rn(f2, f3);
+                        h01 = *reinterpret_cast<const uint32_t *>(&a);
+                        h23 = *reinterpret_cast<const uint32_t *>(&b2);
+                    };
+                    pack(raw.x, lo.x, lo.y);
+                    pack(raw.y, lo.z, lo.w);
+                    pack(raw.z, hi.x, hi.y);
+                    pack(raw.w, hi.z, hi.w);
+                }
+                uint4 *dst = reinterpret_cast<uint4 *>(tile + kk * d_qk + c * 16);
+                dst[0] = lo;
+                dst[1] = hi;
+            }
+        } else {
+            for (int i = tid; i < KT * vec_per_row; i += NT) {
+                const int kk = i / vec_per_row, c = i % vec_per_row;
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (kk < nk) val = reinterpret_cast<const uint4 *>(P.cache + rows(kb + kk) * d_qk)[c];
+                reinterpret_cast<uint4 *>(tile + kk * d_qk)[c] = val;
+            }
         }
         __syncthreads();
         // scores: each warp takes two keys, every lane a strided slice of the row
@@ -233,13 +264,20 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     const size_t smem = (size_t) HG * p.d_qk * 4 + (size_t) KT * p.d_qk * 2 + (size_t) HG * KT * 4 + 3 * HG * 4;
     dim3 grid(splits, n_hg, groups);
     // attributes are set on every call: a cached flag would go stale across a device reset
-    if (p.q_is_f32) {
-        GS_TRY(cudaFuncSetAttribute(k_decode_gather<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-        k_decode_gather<float><<<grid, NT, smem, st>>>(P);
+    P.scales = p.cache_scales;
+    auto launch = [&](auto kernel) -> int {
+        GS_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        kernel<<<grid, NT, smem, st>>>(P);
+        return 0;
+    };
+    int e;
+    if (p.cache_scales) {
+        if (p.d_qk % 32 != 0) return fail_invalid("decode: a Q8 cache needs d_qk % 32 == 0");
+        e = p.q_is_f32 ? launch(k_decode_gather<float, true>) : launch(k_decode_gather<__half, true>);
     } else {
-        GS_TRY(cudaFuncSetAttribute(k_decode_gather<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-        k_decode_gather<__half><<<grid, NT, smem, st>>>(P);
+        e = p.q_is_f32 ? launch(k_decode_gather<float, false>) : launch(k_decode_gather<__half, false>);
     }
+    if (e) return e;
     GS_TRY(cudaGetLastError());
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
     if (p.no_combine) return 0;

@@ -9,6 +9,7 @@ struct DecodeProblem {
     const void *q;        // f16, or f32 when q_is_f32
     bool q_is_f32;
     const __half *cache;
+    const __half *cache_scales;  // Q8 cache: `cache` holds int8 rows and this one f16 scale per 32 values
     int64_t cache_rows;
     const int32_t *seq_lens;
     const int32_t *seq_base;

@@ -44,6 +44,20 @@ __global__ void k_f32_to_f16_rows(const float *__restrict__ x, __half *__restric
     }
 }
 
+// Q8 latent rows: per block of 32 values d = amax / 127, q = round-to-nearest-even(x / d), d kept as f16.
+// One warp per block.  (Exact division and reciprocal: this file is not built with fast-math.)
+__global__ void k_quant_q8(const float *__restrict__ x, int8_t *__restrict__ q, __half *__restrict__ d, int64_t n_blocks) {
+    const int64_t b = (int64_t) blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x & 31;
+    if (b >= n_blocks) return;
+    const float v = x[b * 32 + lane];
+    const float amax = warp_max(fabsf(v));
+    const float dd = __fdiv_rn(amax, 127.f);
+    const float inv = dd > 0.f ? __fdiv_rn(1.f, dd) : 0.f;
+    q[b * 32 + lane] = (int8_t) __float2int_rn(__fmul_rn(v, inv));
+    if (lane == 0) d[b] = __float2half_rn(dd);
+}
+
 struct AppendParams {
     const float *kv;
     __half *cache;
@@ -125,6 +139,15 @@ GS_EXPORT int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream) {
     }
     const int64_t pairs = (n + 1) / 2;
     k_f32_to_f16_rows<<<(unsigned) ((pairs + 255) / 256), 256, 0, (cudaStream_t) stream>>>(x, (__half *) y, n);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_quant_q8_rows(const float *x, void *q, void *d, int64_t n, void *stream) {
+    if (n % 32 != 0) return fail_invalid("gs_quant_q8_rows: n must be a multiple of 32");  // ops.cu:612
+    const int64_t nb = n / 32;
+    if (nb <= 0) return 0;
+    k_quant_q8<<<(unsigned) ((nb + 7) / 8), 256, 0, (cudaStream_t) stream>>>(x, (int8_t *) q, (__half *) d, nb);
     GS_TRY(cudaGetLastError());
     return 0;
 }

@@ -29,10 +29,16 @@ extern "C" {
  *   sel  i32 [T][sel_stride] attended rows         cnt  i32 [T] rows attended by query t
  *   o    f32 [T][H][R]                             part f32 workspace, T*H*splits*(R+2) floats
  *                                                       when splits > 1 (same size as ops.cu:578)
- * Returns cudaErrorInvalidValue for R != 512, H % 16 != 0, splits < 1 (as the reference) and for
- * C_scales != NULL (the Q8 cache format is not implemented). */
+ *   C_scales NULL: f16 cache.  Non-NULL: the Q8 cache of ops.cu:427 - C is int8 [ctx][R] and C_scales one
+ *   f16 scale per 32 values, [ctx][R/32]; rows are rebuilt as half_rn(scale * q) exactly as ops.cu:461-477.
+ * Returns cudaErrorInvalidValue for R != 512, H % 16 != 0, splits < 1 (as the reference). */
 int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride, const int *cnt,
                 float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
+
+/* Replaces gs_quant_q8_rows, crates/cuda/kernels/ops.cu:599-617 (Rust declaration crates/cuda/src/lib.rs:96;
+ * caller crates/engine/src/forward.rs:852-856): the KV-append of the Q8 cache.  Per block of 32 values
+ * d = amax / 127 (stored as f16), q = round-to-nearest-even(x / d) as int8.  n % 32 != 0 is rejected. */
+int gs_quant_q8_rows(const float *x, void *q, void *d, int64_t n, void *stream);
 
 /* Replaces gs_f32_to_f16, crates/cuda/kernels/gemm.cu:159-163 (Rust declaration crates/cuda/src/lib.rs:123;
  * caller crates/engine/src/forward.rs:857-860): y[i] = half_rn(x[i]) for i < n.  This is the reference's

@@ -477,3 +477,30 @@ void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0,
             }
         }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Q8 latent cache (the engine's --kv-cache q8).  Quantiser: per block of 32 values d = amax / 127,
+ * q = round_to_nearest_even(x / d) stored as int8, d stored as f16 (crates/cuda/kernels/ops.cu:599-610).
+ * Reader: the attention kernel rebuilds an f16 tile as half_rn(float(d) * q) (ops.cu:461-477) and
+ * then proceeds as with an f16 cache, so the Q8 oracle is dequantise-to-f16 + the f16 oracle.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_quant_q8_rows(const float *x, int8_t *q, uint16_t *d, int64_t n_blocks) {
+    for (int64_t b = 0; b < n_blocks; b++) {
+        float amax = 0.f;
+        for (int i = 0; i < 32; i++) {
+            const float a = fabsf(x[b * 32 + i]);
+            if (a > amax) amax = a;
+        }
+        const float dd = amax / 127.f;
+        const float inv = dd > 0.f ? 1.f / dd : 0.f;
+        for (int i = 0; i < 32; i++) q[b * 32 + i] = (int8_t) lrintf(x[b * 32 + i] * inv);
+        d[b] = oracle_f32_to_f16(dd);
+    }
+}
+
+void oracle_dequant_q8(const int8_t *q, const uint16_t *d, uint16_t *out, int64_t n_blocks) {
+    for (int64_t b = 0; b < n_blocks; b++) {
+        const float dd = oracle_f16_to_f32(d[b]);
+        for (int i = 0; i < 32; i++) out[b * 32 + i] = oracle_f32_to_f16(dd * (float) q[b * 32 + i]);
+    }
+}

@@ -39,6 +39,8 @@ def lib() -> C.CDLL:
                                             i32]
     L.oracle_prefill.restype = i32
     L.oracle_prefill.argtypes = [vp, vp, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, i32]
+    L.oracle_quant_q8_rows.argtypes = [vp, vp, vp, i64]
+    L.oracle_dequant_q8.argtypes = [vp, vp, vp, i64]
     L.oracle_rope_inv_freq.argtypes = [vp, i32, C.c_double]
     L.oracle_rope_append.argtypes = [vp, vp, i32, i32, i32, i64, C.c_double]
     L.oracle_rope_f16.argtypes = [vp, i32, i32, i32, i32, i64, C.c_double]
@@ -155,3 +157,22 @@ def rope_f16(x, pos0=0, d_rope=64, base=10000.0) -> np.ndarray:
     S, H, d = xb.shape
     lib().oracle_rope_f16(_p(xb), S, H, d, d_rope, pos0, base)
     return xb.view(np.float16)
+
+
+def quant_q8_rows(x):
+    """x f32 [..., 32k] -> (q int8 same shape, d f16 [..., k]) : per block of 32, d = amax/127, q = rn(x/d)."""
+    x = _c(x, np.float32)
+    assert x.shape[-1] % 32 == 0
+    q = np.empty(x.shape, np.int8)
+    d = np.empty(x.shape[:-1] + (x.shape[-1] // 32,), np.uint16)
+    lib().oracle_quant_q8_rows(_p(x), _p(q), _p(d), x.size // 32)
+    return q, d.view(np.float16)
+
+
+def dequant_q8(q, d):
+    """The f16 tile the attention kernel rebuilds from a Q8 cache: half_rn(float(d) * q)."""
+    q = _c(q, np.int8)
+    db = f16_bits(d)
+    out = np.empty(q.shape, np.uint16)
+    lib().oracle_dequant_q8(_p(q), _p(db), _p(out), q.size // 32)
+    return out.view(np.float16)

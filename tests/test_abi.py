@@ -55,11 +55,10 @@ def test_reference_abi_rejections(pkg, R, H, splits):
     assert b"gs_mla_attn" in L.gs_attn_last_error_string()
 
 
-def test_q8_cache_is_rejected(pkg):
+def test_quant_q8_rows_rejects_ragged_length(pkg):
     L = pkg._lib.load()
-    dummy = C.c_void_p(16)
-    rc = L.gs_mla_attn(dummy, dummy, dummy, dummy, 8, dummy, 0.0625, dummy, dummy, 1, 64, 512, 4, None)
-    assert rc == CUDA_ERROR_INVALID_VALUE and b"Q8" in L.gs_attn_last_error_string()
+    assert L.gs_quant_q8_rows(None, None, None, 33, None) == CUDA_ERROR_INVALID_VALUE  # ops.cu:612
+    assert L.gs_quant_q8_rows(None, None, None, 0, None) == 0
 
 
 def test_decode_argument_validation(pkg):

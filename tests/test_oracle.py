@@ -167,3 +167,39 @@ def test_golden_vectors_from_reference_kernel(oracle):
         o = oracle.mla_attn_ref(z["q"], z["C"].view(np.float16), z["sel"], z["cnt"], float(z["scale"]))
         # the reference kernel is built with fast-math (__expf) and sums in tiles of 32
         check_close(o, z["o"], os.path.basename(f), 2e-5, 2e-6)
+
+
+def test_quant_q8_rows_matches_numpy_restatement(oracle):
+    # crates/cuda/kernels/ops.cu:599-610: d = amax / 127 (kept as f16), q = round-to-nearest-even(x * (1 / d))
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((37, 512)).astype(np.float32) * np.float32(3.0)
+    x[5] = 0.0                       # an all-zero block keeps q = 0, d = 0
+    x[6, :32] = np.float32(1e-30)    # amax / 127 underflows towards a subnormal scale
+    q, d = oracle.quant_q8_rows(x)
+    xb = x.reshape(-1, 32)
+    dd = (np.abs(xb).max(axis=1) / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore", over="ignore", invalid="ignore"):
+        inv = np.where(dd > 0, np.float32(1.0) / dd, np.float32(0.0)).astype(np.float32)
+        want_q = np.clip(np.rint(xb * inv[:, None]), -128, 127).astype(np.int8)
+    ok = np.isfinite(inv)
+    assert np.array_equal(q.reshape(-1, 32)[ok], want_q[ok])
+    assert np.array_equal(d.reshape(-1).view(np.uint16), dd.astype(np.float16).view(np.uint16))
+    assert np.abs(q).max() == 127 and not q[5].any() and not d[5].any()
+
+
+def test_dequant_q8_is_half_of_scale_times_q(oracle):
+    rng = np.random.default_rng(12)
+    q = rng.integers(-127, 128, size=(9, 512), dtype=np.int8)
+    d = (rng.random((9, 16), dtype=np.float32) * np.float32(0.05)).astype(np.float16)
+    got = oracle.dequant_q8(q, d)
+    want = (np.repeat(d.astype(np.float32), 32, axis=1) * q.astype(np.float32)).astype(np.float16)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_q8_round_trip_error_is_half_a_step(oracle):
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((64, 512)).astype(np.float32)
+    q, d = oracle.quant_q8_rows(x)
+    back = oracle.dequant_q8(q, d).astype(np.float32)
+    step = np.repeat(d.astype(np.float32), 32, axis=1)
+    assert np.all(np.abs(back - x) <= 0.5 * step * 1.01 + 2e-3 * np.abs(x))

@@ -28,12 +28,13 @@ def _legacy_inputs(seed, T, H, n, ctx, dense=True):
     return q, Cc, sel, cnt
 
 
-def _call(torch, fn, q, Cc, sel, cnt, splits):
+def _call(torch, fn, q, Cc, sel, cnt, splits, scales=None):
     T, H, R = q.shape
     qd, cd, sd, nd = to_dev(torch, q), to_dev(torch, Cc), to_dev(torch, sel), to_dev(torch, cnt)
+    scd = None if scales is None else to_dev(torch, scales)
     o = torch.zeros((T, H, R), dtype=torch.float32, device="cuda")
     part = torch.zeros(T * H * splits * (R + 2), dtype=torch.float32, device="cuda")
-    rc = fn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16, o.data_ptr(),
+    rc = fn(qd.data_ptr(), cd.data_ptr(), None if scd is None else scd.data_ptr(), sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16, o.data_ptr(),
             part.data_ptr(), T, H, R, splits, None)
     assert rc == 0
     torch.cuda.synchronize()
@@ -94,3 +95,80 @@ def test_reference_kernel_pins_oracle_and_agrees_with_ours(pkg, cuda, oracle, T,
     o_new = _call(cuda, pkg._lib.load().gs_mla_attn, q, Cc, sel, cnt, splits)
     check_close(o_orc, o_ref, "oracle vs reference kernel", 2e-5, 2e-6)
     check_close(o_new, o_ref, "ours vs reference kernel", 2e-5, 2e-6)
+
+
+# ---- Q8 latent cache (int8 rows + one f16 scale per 32 values; crates/cuda/kernels/ops.cu:427, :461-477) ----
+
+def _quant_gpu(torch, fn, x):
+    xd = to_dev(torch, x)
+    q = torch.zeros(x.size, dtype=torch.int8, device="cuda")
+    d = torch.zeros(x.size // 32, dtype=torch.float16, device="cuda")
+    assert fn(xd.data_ptr(), q.data_ptr(), d.data_ptr(), x.size, None) == 0
+    torch.cuda.synchronize()
+    return q.cpu().numpy().reshape(x.shape), d.cpu().numpy().reshape(x.shape[:-1] + (x.shape[-1] // 32,))
+
+
+def test_gs_quant_q8_rows_bit_exact(pkg, cuda, oracle):
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((301, 512)).astype(np.float32) * np.float32(2.0)
+    x[7] = 0.0
+    x[8, 32:64] *= np.float32(1e-4)
+    q, d = _quant_gpu(cuda, pkg._lib.load().gs_quant_q8_rows, x)
+    wq, wd = oracle.quant_q8_rows(x)
+    assert np.array_equal(q, wq)
+    assert np.array_equal(d.view(np.uint16), wd.view(np.uint16))
+
+
+@pytest.mark.parametrize("T,H,n,splits,dense", [
+    (1, 64, 4096, 16, True), (2, 64, 1500, 4, True), (1, 32, 2052, 16, False), (5, 16, 300, 1, False),
+    (1, 16, 0, 16, True), (2, 64, 33, 4, False),
+])
+def test_gs_mla_attn_q8_cache_vs_oracle(pkg, cuda, oracle, T, H, n, splits, dense):
+    q, Cc, sel, cnt = _legacy_inputs(T * 77 + n, T, H, n, max(n, 1) + 100, dense)
+    cq, cs = oracle.quant_q8_rows(Cc.astype(np.float32))
+    got = _call(cuda, pkg._lib.load().gs_mla_attn, q, cq, sel, cnt, splits, scales=cs)
+    # the oracle attends over exactly the f16 rows the kernel rebuilds from (q, scale)
+    want = oracle.mla_attn_ref(q, oracle.dequant_q8(cq, cs), sel, cnt, 1 / 16)
+    check_close(got, want, "gs_mla_attn q8")
+    if n > 8:
+        check_not_degenerate(got, "gs_mla_attn q8")
+
+
+def test_q8_append_then_attend_round_trip(pkg, cuda, oracle):
+    # Engine::mla with a Q8 cache (forward.rs:852-856): quantise the new f32 rows on the device, attend over them
+    T, H, n = 1, 64, 1024
+    q, Cc, sel, cnt = _legacy_inputs(5, T, H, n, n, True)
+    L = pkg._lib.load()
+    cq, cs = _quant_gpu(cuda, L.gs_quant_q8_rows, Cc.astype(np.float32))
+    got = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, 16, scales=cs)
+    want_q8 = oracle.mla_attn_ref(q, oracle.dequant_q8(cq, cs), sel, cnt, 1 / 16)
+    check_close(got, want_q8, "q8 append + attend")
+    # and the quantisation itself stays a small perturbation of the f16-cache result
+    want_f16 = oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16)
+    assert np.abs(got - want_f16).max() < 5e-2
+
+
+@pytest.mark.skipif(not os.path.exists(REF_SO), reason="reference kernels were not compiled (oracle/_ref absent)")
+def test_reference_q8_kernels_pin_oracle(pkg, cuda, oracle):
+    ref = C.CDLL(REF_SO)
+    ref.gs_mla_attn.restype = C.c_int
+    ref.gs_mla_attn.argtypes = pkg._lib.SIGNATURES["gs_mla_attn"][1]
+    ref.gs_quant_q8_rows.restype = C.c_int
+    ref.gs_quant_q8_rows.argtypes = pkg._lib.SIGNATURES["gs_quant_q8_rows"][1]
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((257, 512)).astype(np.float32)
+    rq, rd = _quant_gpu(cuda, ref.gs_quant_q8_rows, x)
+    oq, od = oracle.quant_q8_rows(x)
+    # the reference is built with fast-math (approximate reciprocal and division): the scale may differ by one f16
+    # ulp and a value that sits on a rounding boundary by one step; everything else must be identical
+    assert np.abs(rq.astype(np.int32) - oq.astype(np.int32)).max() <= 1
+    assert (rq != oq).mean() < 1e-3
+    assert np.abs(rd.view(np.uint16).astype(np.int32) - od.view(np.uint16).astype(np.int32)).max() <= 1
+    # attention over the same (q, scale) bytes: reference kernel, oracle and the new kernel agree
+    T, H, n = 2, 32, 200
+    q, _, sel, cnt = _legacy_inputs(9, T, H, n, 257, False)
+    o_ref = _call(cuda, ref.gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
+    o_orc = oracle.mla_attn_ref(q, oracle.dequant_q8(oq, od), sel, cnt, 1 / 16)
+    o_new = _call(cuda, pkg._lib.load().gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
+    check_close(o_orc, o_ref, "oracle vs reference kernel (q8)", 2e-5, 2e-6)
+    check_close(o_new, o_ref, "ours vs reference kernel (q8)", 2e-5, 2e-6)
