@@ -4,7 +4,7 @@
 //   o = sum acc_s w_s / L, zeros when L == 0.
 // One "item" is (output row, 128-column chunk), worked on by 256 threads: 32 column quads x 8 segment
 // lanes.  The accumulator loads are issued before the weights are known, so an item costs one round
-// trip to memory.  
+// trip to memory.
 #pragma once
 #include "internal.cuh"
 
@@ -12,96 +12,160 @@ namespace gs {
 
 constexpr int CB_COLS = 128;
 constexpr int CB_LANES = 8;
-constexpr int CB_NT = (CB_COLS / 4) * CB_LANES;  // 256
+constexpr int CB_NT = (CB_COLS / 4) * CB_LANES;  // 256: warp w is segment lane w, its 32 lanes are the column quads
 constexpr int CB_MAX_SEG = 1024;
 constexpr int CB_REG_SEG = 20;                   // segments per lane held in registers (covers 160 segments)
+static_assert(CB_COLS / 4 == 32 && CB_REG_SEG <= 32, "a warp is one segment lane; lane j also owns the weight of segment j");
 
 struct CombineSmem {
-    float m[CB_MAX_SEG], l[CB_MAX_SEG];
-    float red[CB_NT / 32];
+    float m[CB_MAX_SEG], l[CB_MAX_SEG];  // only the path for more than 160 segments
+    float red[CB_NT / 32], lred[CB_NT / 32];
+    int ired[2][CB_NT / 32];
     float M, L;
     float4 part[CB_LANES][CB_COLS / 4];
 };
 
+// Where the segments of output row `row` lie.
+struct SegRange {
+    int first, nseg, row_in_seg;
+};
+
+// True when combine_locate() needs nothing the preceding kernel writes, so it may run before the
+// grid-dependency wait of a programmatic dependent launch.  (seq_lens is an input of the attention kernel,
+// complete before that kernel's own dependency wait returned in any of its CTAs, and a dependent kernel
+// starts only after every CTA of the attention kernel has passed that point.)
+__device__ __forceinline__ bool combine_locate_is_early(const CombinePlan &C) { return C.desc == nullptr || C.seq_lens != nullptr; }
+
+// All CB_NT threads call this.  The schedule of the tcgen05 kernel is recomputed from the sequence lengths:
+// sequences are cut into units of `unit_rows` rows, the units are dealt in equal contiguous chunks to the
+// n_ctas CTAs, and CTA c keeps the record of sequence b in segment c + b.
+__device__ __forceinline__ SegRange combine_locate(const CombinePlan &C, int row, CombineSmem &S) {
+    const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
+    SegRange r;
+    if (!C.desc) {
+        r.first = (b * C.T + t) * C.regular_segments;
+        r.nseg = C.regular_segments;
+        r.row_in_seg = h;
+        return r;
+    }
+    r.row_in_seg = t * C.H + h;
+    if (!C.seq_lens) {
+        const int2 d = __ldcg(C.desc + b);
+        r.first = d.x;
+        r.nseg = d.y;
+        return r;
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int before = 0, total = 0;
+    for (int i = tid; i < C.n_seq; i += CB_NT) {
+        const int u = (max(__ldg(C.seq_lens + i), 0) + C.unit_rows - 1) / C.unit_rows;
+        total += u;
+        if (i < b) before += u;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        total += __shfl_xor_sync(0xffffffffu, total, o);
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+    }
+    if (lane == 0) {
+        S.ired[0][warp] = total;
+        S.ired[1][warp] = before;
+    }
+    __syncthreads();
+    total = before = 0;
+#pragma unroll
+    for (int w = 0; w < CB_NT / 32; w++) {
+        total += S.ired[0][w];
+        before += S.ired[1][w];
+    }
+    const int mine = (max(__ldg(C.seq_lens + b), 0) + C.unit_rows - 1) / C.unit_rows;
+    const int chunk = max(1, (total + C.n_ctas - 1) / C.n_ctas);
+    r.first = b;
+    r.nseg = 0;
+    if (mine > 0) {
+        const int c_first = before / chunk, c_last = (before + mine - 1) / chunk;
+        r.first = c_first + b;
+        r.nseg = c_last - c_first + 1;
+    }
+    return r;
+}
+
 // All CB_NT threads of the CTA call this with the same (row, col0).  Returns true in the threads that hold a
 // result: `a` = 4 merged (unnormalised) accumulator columns starting at `col`, with the row's M and L.
-__device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, int row, int col0, CombineSmem &S, float4 &a_out,
-                                                     float &M_out, float &L_out, int &col_out) {
-    const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
+__device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, const SegRange &R, int col0, CombineSmem &S,
+                                                     float4 &a_out, float &M_out, float &L_out, int &col_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int quad = tid % (CB_COLS / 4), sl = tid / (CB_COLS / 4);
+    const int quad = lane, sl = warp;
     const int col = col0 + quad * 4;
-    int first, nseg, row_in_seg;
-    if (C.desc) {
-        const int2 d = __ldcg(C.desc + b);
-        first = d.x;
-        nseg = d.y;
-        row_in_seg = t * C.H + h;
-    } else {
-        first = (b * C.T + t) * C.regular_segments;
-        nseg = C.regular_segments;
-        row_in_seg = h;
-    }
-    nseg = min(nseg, CB_MAX_SEG);
+    const int first = R.first, row_in_seg = R.row_in_seg;
+    const int nseg = min(R.nseg, CB_MAX_SEG);
     const float *acc0 = C.acc + (int64_t) first * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col;
-    const bool in_regs = nseg <= CB_LANES * CB_REG_SEG;
-    float4 v[CB_REG_SEG];
-    if (in_regs && col < C.d_v) {
+    const float *ml0 = C.ml + (int64_t) first * C.seg_stride_ml + row_in_seg * 2;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    float M, L;
+    if (nseg <= CB_LANES * CB_REG_SEG) {
+        // One round trip: lane j of segment lane sl fetches (m, l) of segment sl + 8 j, and every lane the four
+        // columns of all the segments of its segment lane, before any weight is known.
+        const int sj = sl + CB_LANES * lane;
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (lane < CB_REG_SEG && sj < nseg) ml = __ldcg(reinterpret_cast<const float2 *>(ml0 + (int64_t) sj * C.seg_stride_ml));
+        float4 v[CB_REG_SEG];
 #pragma unroll
         for (int i = 0; i < CB_REG_SEG; i++) {
             const int s = sl + i * CB_LANES;
-            v[i] = s < nseg ? __ldcg(reinterpret_cast<const float4 *>(acc0 + (int64_t) s * C.seg_stride_acc))
-                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[i] = (s < nseg && col < C.d_v) ? __ldcg(reinterpret_cast<const float4 *>(acc0 + (int64_t) s * C.seg_stride_acc))
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-    }
-    float mx = -INFINITY;
-    for (int s = tid; s < nseg; s += CB_NT) {
-        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(C.ml + (int64_t) (first + s) * C.seg_stride_ml + row_in_seg * 2));
-        S.m[s] = ml.x;
-        S.l[s] = ml.y;
-        mx = fmaxf(mx, ml.x);
-    }
-    mx = warp_max(mx);
-    if (lane == 0) S.red[warp] = mx;
-    __syncthreads();
-    if (tid == 0) {
-        float m = -INFINITY;
-        for (int w = 0; w < CB_NT / 32; w++) m = fmaxf(m, S.red[w]);
-        S.M = m;
-    }
-    __syncthreads();
-    const float M = S.M;
-    // weights e^(m-M) replace m in shared memory; L = sum l w
-    float lsum = 0.f;
-    for (int s = tid; s < nseg; s += CB_NT) {
-        const float m = S.m[s];
-        const float w = m == -INFINITY ? 0.f : expf(m - M);
-        S.m[s] = w;
-        lsum += S.l[s] * w;
-    }
-    lsum = warp_sum(lsum);
-    if (lane == 0) S.red[warp] = lsum;
-    __syncthreads();
-    if (tid == 0) {
-        float l = 0.f;
-        for (int w = 0; w < CB_NT / 32; w++) l += S.red[w];
-        S.L = l;
-    }
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (col < C.d_v) {
-        if (in_regs) {
+        const float mx = warp_max(ml.x);
+        if (lane == 0) S.red[warp] = mx;
+        __syncthreads();
+        M = S.red[0];
 #pragma unroll
-            for (int i = 0; i < CB_REG_SEG; i++) {
-                const int s = sl + i * CB_LANES;
-                const float w = s < nseg ? S.m[s] : 0.f;
-                if (w != 0.f) {  // an empty segment's accumulator never enters the sum
-                    a.x = fmaf(v[i].x, w, a.x);
-                    a.y = fmaf(v[i].y, w, a.y);
-                    a.z = fmaf(v[i].z, w, a.z);
-                    a.w = fmaf(v[i].w, w, a.w);
-                }
+        for (int w = 1; w < CB_NT / 32; w++) M = fmaxf(M, S.red[w]);
+        const float wj = ml.x == -INFINITY ? 0.f : expf(ml.x - M);
+        const float ls = warp_sum(ml.y * wj);
+        if (lane == 0) S.lred[warp] = ls;
+#pragma unroll
+        for (int i = 0; i < CB_REG_SEG; i++) {
+            const float w = __shfl_sync(0xffffffffu, wj, i);
+            if (w != 0.f) {  // an empty segment's accumulator never enters the sum
+                a.x = fmaf(v[i].x, w, a.x);
+                a.y = fmaf(v[i].y, w, a.y);
+                a.z = fmaf(v[i].z, w, a.z);
+                a.w = fmaf(v[i].w, w, a.w);
             }
-        } else {
+        }
+        S.part[sl][quad] = a;
+        __syncthreads();
+        L = 0.f;
+#pragma unroll
+        for (int w = 0; w < CB_NT / 32; w++) L += S.lred[w];
+    } else {
+        float mx = -INFINITY;
+        for (int s = tid; s < nseg; s += CB_NT) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(ml0 + (int64_t) s * C.seg_stride_ml));
+            S.m[s] = ml.x;
+            S.l[s] = ml.y;
+            mx = fmaxf(mx, ml.x);
+        }
+        mx = warp_max(mx);
+        if (lane == 0) S.red[warp] = mx;
+        __syncthreads();
+        M = S.red[0];
+#pragma unroll
+        for (int w = 1; w < CB_NT / 32; w++) M = fmaxf(M, S.red[w]);
+        // weights e^(m-M) replace m in shared memory; L = sum l w
+        float lsum = 0.f;
+        for (int s = tid; s < nseg; s += CB_NT) {
+            const float m = S.m[s];
+            const float w = m == -INFINITY ? 0.f : expf(m - M);
+            S.m[s] = w;
+            lsum += S.l[s] * w;
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) S.lred[warp] = lsum;
+        __syncthreads();
+        if (col < C.d_v) {
             for (int s = sl; s < nseg; s += CB_LANES) {
                 const float w = S.m[s];
                 if (w != 0.f) {
@@ -113,10 +177,12 @@ __device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, int r
                 }
             }
         }
+        S.part[sl][quad] = a;
+        __syncthreads();
+        L = 0.f;
+#pragma unroll
+        for (int w = 0; w < CB_NT / 32; w++) L += S.lred[w];
     }
-    S.part[sl][quad] = a;
-    __syncthreads();
-    const float L = S.L;
     bool holds = false;
     if (sl == 0 && col < C.d_v) {
 #pragma unroll
@@ -138,11 +204,11 @@ __device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, int r
 }
 
 // Merge one item and write it: normalised output and/or the merged record.
-__device__ __forceinline__ void combine_item(const CombinePlan &C, int row, int col0, CombineSmem &S) {
+__device__ __forceinline__ void combine_item(const CombinePlan &C, const SegRange &R, int row, int col0, CombineSmem &S) {
     float4 a;
     float M, L;
     int col;
-    if (combine_item_compute(C, row, col0, S, a, M, L, col)) {
+    if (combine_item_compute(C, R, col0, S, a, M, L, col)) {
         if (C.part_out) {
             const int64_t rows_total = (int64_t) C.n_seq * C.T * C.H;
             *reinterpret_cast<float4 *>(C.part_out + (int64_t) row * C.d_v + col) = a;

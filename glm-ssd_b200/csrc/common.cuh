@@ -29,15 +29,20 @@ inline int fail_invalid(const char *what) {
     } while (0)
 
 // ---- decode workspace layout -------------------------------------------------------------------
-// [0, 4096)                status block: int32 status word (sticky, kernels only OR into it);
+// [0, 32768)               status block: int32 status word (sticky, kernels only OR into it);
 //                           int32 at byte 4: when non-zero, CTA 0 of the tcgen05 kernel writes clock64
 //                           stamps of its first tiles as int64 from byte 256 on (a tuning aid, off by default)
-// [4096, ...)              per-sequence segment descriptors, then
+//   [4096, 16384)           with the same switch every CTA of the tcgen05 kernel writes eight int64 %globaltimer
+//                           stamps (entry, inputs visible, first tile landed, drain start/end, exit, SM id)
+//   [16384, 32768)          and every CTA of the combine kernel eight stamps of its own
+// [32768, ...)             per-sequence segment descriptors, then
 //                           partial accumulators f32 [n_segments][rows_q][d_v]
 // then                     partial (m, l)       f32 [n_segments][rows_q][2]
 // A "segment" is the share of one sequence handled by one CTA (tcgen05 kernel: at most
 // n_ctas + n_seq of them) or one (sequence, token, split) triple (CUDA-core kernel).
-constexpr int kStatusBytes = 4096;
+constexpr int kStatusBytes = 32768;
+constexpr int kCtaProfOffsetBytes = 4096;       // [cta][8] int64
+constexpr int kCombineProfOffsetBytes = 16384;  // [cta][8] int64, first 256 CTAs
 constexpr int kProfOffsetBytes = 256;
 constexpr int kProfSlots = 16;   // stamps per tile
 constexpr int kProfTiles = 24;   // tiles recorded

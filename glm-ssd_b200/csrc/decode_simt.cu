@@ -9,6 +9,7 @@
 //   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
 // with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
 #include "combine.cuh"
+#include "sm100_prims.cuh"
 #include "internal.cuh"
 
 namespace gs {
@@ -199,10 +200,21 @@ __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
 // overlaps the tail of the kernel that writes the partials.
 __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
     __shared__ CombineSmem S;
+    long long *prof = nullptr;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (C.status && C.status[1] != 0 && cta < 256 && threadIdx.x == 0)
+        prof = reinterpret_cast<long long *>(const_cast<char *>(reinterpret_cast<const char *>(C.status)) + kCombineProfOffsetBytes) + cta * 8;
+    if (prof) prof[0] = sm100::global_timer_ns();
+    const bool early = combine_locate_is_early(C);
+    SegRange R;
+    if (early) R = combine_locate(C, blockIdx.x, S);
 #if __CUDA_ARCH__ >= 900
-    cudaGridDependencySynchronize();  // the partials (and desc) are written by the preceding kernel
+    cudaGridDependencySynchronize();  // the partial records (and desc) are written by the preceding kernel
 #endif
-    combine_item(C, blockIdx.x, blockIdx.y * CB_COLS, S);
+    if (prof) prof[1] = sm100::global_timer_ns();
+    if (!early) R = combine_locate(C, blockIdx.x, S);
+    combine_item(C, R, blockIdx.x, blockIdx.y * CB_COLS, S);
+    if (prof) prof[2] = sm100::global_timer_ns();
 }
 
 }  // namespace

@@ -213,7 +213,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         if (prof && (tile) < (uint32_t) kProfTiles) prof[(tile) * kProfSlots + (slot)] = clock64(); \
     } while (0)
 
+    long long *cta_prof = nullptr;  // wall-clock stamps of every CTA
+    if (P.status[1] != 0)
+        cta_prof = reinterpret_cast<long long *>(reinterpret_cast<char *>(P.status) + kCtaProfOffsetBytes) + blockIdx.x * 8;
+#define GS_CTA_STAMP(slot)                              \
+    do {                                                \
+        if (cta_prof) cta_prof[slot] = global_timer_ns(); \
+    } while (0)
     if (tid == 0) GS_STAMP(kProfTiles - 1, 0);  // kernel-level stamps live in the last row
+    if (tid == 0) {
+        GS_CTA_STAMP(0);
+        if (cta_prof) cta_prof[6] = sm_id();
+    }
     // ---- set-up: barriers, tensor memory, the unit schedule -------------------------------------------
     if (tid == 0) {
         tma_prefetch_desc(&P.tm_kv64);
@@ -244,6 +255,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     }
     // everything above touched only this CTA's own resources; inputs written by earlier kernels come next
     griddep_wait();
+    if (tid == 0) GS_CTA_STAMP(1);
     for (int b = tid; b < P.n_seq; b += NTHREADS) {
         const int len = max(P.seq_lens[b], 0);
         M.len[b] = len;
@@ -304,6 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         // =================================== TMA producer ==================================================
         // The whole warp runs the loop (uniform control flow); one elected lane issues each copy.
         bool ok = true;
+        const uint64_t pol_stream = l2_policy_evict_first();  // every cache row is read once per step
         while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
             const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
             for (int j = 0; j < sg.n_tiles; j++, it++) {
@@ -321,7 +334,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (NBLK * BLK_BYTES));
 #pragma unroll
                         for (int k = 0; k < NBLK; k++)
-                            tma_load_2d(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, grow);
+                            tma_load_2d_hint(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, grow, pol_stream);
                     }
                 } else {
                     const int ng = (valid + 15) >> 4;
@@ -330,8 +343,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         for (int g = 0; g < ng; g++) {
 #pragma unroll
                             for (int k = 0; k < NBLK; k++)
-                                tma_load_2d(dst + k * BLK_BYTES + g * 2048, &P.tm_kv16, &B.kv_full[s], k * 64,
-                                            (int) (base_row + row + g * 16));
+                                tma_load_2d_hint(dst + k * BLK_BYTES + g * 2048, &P.tm_kv16, &B.kv_full[s], k * 64,
+                                                 (int) (base_row + row + g * 16), pol_stream);
                         }
                     }
                 }
@@ -397,6 +410,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                          mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
                     if (!ok) break;
                     if (mw == 0 && lane == 0) GS_STAMP(it, PF_KV_FULL);
+                    if (mw == 0 && lane == 0 && it == 0) GS_CTA_STAMP(2);
                     issue_s(it);
                     if (mw == 0 && lane == 0) GS_STAMP(it, PF_S_ISSUED);
                 }
@@ -452,6 +466,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         constexpr int HQ = NQ / 2;
         const int hi = lane >> 4;                     // which half of the query rows this lane handles
         const int col0 = hi * HQ;
+        const uint64_t pol_keep = l2_policy_evict_last();  // the partial records are read next, by the combine kernel
         float l_part[HQ];                             // row sums of this thread's cache row, per query row
         float nm[HQ];                                 // minus the reference maximum (log2 units) per query row
         bool ok = true;
@@ -624,6 +639,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             if (*abort_flag) { ok = false; break; }
             tc_fence_after();
             if (wg_tid == 0) GS_STAMP(kProfTiles - 1, 2);
+            if (wg_tid == 0) GS_CTA_STAMP(3);
 #pragma unroll
             for (int i = 0; i < HQ; i++) {
                 float v = l_part[i];
@@ -652,7 +668,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const int q = c * 16 + i;
-                        if (q < P.rows_q) acc[(int64_t) q * P.d_v + mt * 128] = __uint_as_float(r[i]);
+                        if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(r[i]), pol_keep);
                     }
                 }
             }
@@ -660,6 +676,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(&B.o_empty);
             if (wg_tid == 0) GS_STAMP(kProfTiles - 1, 3);
+            if (wg_tid == 0) GS_CTA_STAMP(4);
             sgc++;
         }
     }
@@ -679,7 +696,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tmem_dealloc(tmem, TMEM_COLS);
     }
     if (tid == 32) GS_STAMP(kProfTiles - 1, 4);
+    if (tid == 32) GS_CTA_STAMP(5);
 #undef GS_STAMP
+#undef GS_CTA_STAMP
 }
 
 template <int NQ, int NBLK>
@@ -761,6 +780,10 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     c.d_v = p.d_v;
     c.o = p.o;
     c.part_out = p.part_out;
+    c.status = p.status;
+    c.seq_lens = p.seq_lens;
+    c.unit_rows = P.paged ? TILE : 16;
+    c.n_ctas = grid;
     int e;
     if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
     else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);

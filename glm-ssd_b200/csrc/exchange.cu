@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(CB_NT) k_exchange_combine(const CombinePlan C,
         float4 a;
         float M, L;
         int col;
-        if (combine_item_compute(C, row, chunk * CB_COLS, S, a, M, L, col)) {
+        const SegRange R = combine_locate(C, row, S);
+        if (combine_item_compute(C, R, chunk * CB_COLS, S, a, M, L, col)) {
             for (int r = 0; r < X.world; r++) {
                 uint2 *dst = reinterpret_cast<uint2 *>(X.bufs[r]) + slot + (int64_t) X.rank * X.block_words;
                 uint2 *w = dst + (int64_t) row * X.d_v + col;

@@ -47,6 +47,11 @@ struct CombinePlan {
     int n_seq, T, H, d_v;
     float *o;              // may be nullptr
     float *part_out;       // may be nullptr
+    const int32_t *status; // workspace status block (stamps switch at word 1) or nullptr
+    // with desc: when seq_lens is set, the (first_segment, n_segments) pairs are recomputed from the lengths
+    // (unit_rows rows per unit, units dealt in equal chunks to n_ctas CTAs) instead of being read from desc
+    const int32_t *seq_lens;
+    int unit_rows, n_ctas;
 };
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
