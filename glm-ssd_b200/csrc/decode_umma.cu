@@ -120,6 +120,7 @@ struct Smem {
         int flag[2];
         int cum[MAX_SEQ + 1];
         int len[MAX_SEQ];
+        int base[MAX_SEQ];
         float smax[4][NQ];
         float sl[4][NQ];
         float mref[NQ];
@@ -256,10 +257,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     // everything above touched only this CTA's own resources; inputs written by earlier kernels come next
     griddep_wait();
     if (tid == 0) GS_CTA_STAMP(1);
-    for (int b = tid; b < P.n_seq; b += NTHREADS) {
-        const int len = max(P.seq_lens[b], 0);
-        M.len[b] = len;
-        M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
+    {
+        // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
+        const uint64_t pol_keep = l2_policy_evict_last();
+        for (int b = tid; b < P.n_seq; b += NTHREADS) {
+            const int len = max(ld_global_hint(P.seq_lens + b, pol_keep), 0);
+            M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b, pol_keep) : 0;
+            M.len[b] = len;
+            M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -318,12 +324,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         bool ok = true;
         const uint64_t pol_stream = l2_policy_evict_first();  // every cache row is read once per step
         while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
-            const int64_t base_row = P.seq_base ? (int64_t) P.seq_base[sg.b] : 0;
+            const int64_t base_row = M.base[sg.b];
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
                 if (!ok) break;
                 if (lane == 0) GS_STAMP(it, PF_LOAD_ISSUE);
+                if (lane == 0 && it == 0) GS_CTA_STAMP(7);
                 const int row = sg.r0 + j * TILE;
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
@@ -658,19 +665,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
             float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
+            // one value tile (NQ columns of this lane's row) per step; the loads of the next tile are in flight
+            // while the current one is stored
+            uint32_t rbuf[2][NQ];
+#pragma unroll
+            for (int c = 0; c < NQ / 16; c++) tmem_ld16(tmem + lane_base + O_SLOT0 * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
 #pragma unroll
             for (int mt = 0; mt < NVT; mt++) {
+                tmem_wait_ld();
+                if (mt + 1 < NVT) {
 #pragma unroll
-                for (int c = 0; c < NQ / 16; c++) {
-                    uint32_t r[16];
-                    tmem_ld16(tmem + lane_base + (O_SLOT0 + mt) * NQ + c * 16, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int q = c * 16 + i;
-                        if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(r[i]), pol_keep);
-                    }
+                    for (int c = 0; c < NQ / 16; c++)
+                        tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
+                                  *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
                 }
+#pragma unroll
+                for (int q = 0; q < NQ; q++)
+                    if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(rbuf[mt & 1][q]), pol_keep);
             }
             tc_fence_before();
             __syncwarp();

@@ -137,6 +137,11 @@ __device__ __forceinline__ void tma_load_2d_hint(void *smem_dst, const CUtensorM
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
         : "memory");
 }
+__device__ __forceinline__ int ld_global_hint(const int *p, uint64_t policy) {
+    int v;
+    asm volatile("ld.global.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_global_hint(float *p, float v, uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
 }
