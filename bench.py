@@ -13,8 +13,9 @@ queries, N(0,0.5) cache).
             steps the call rotates over distinct cache copies totalling more than twice L2.
   e2e       the same metric through the call-site mirror (MlaDecodeLayer.step): pinned host q and
             new latent rows are copied in, appended with RoPE, attended, and the output is copied
-            back to the host, every step.  The latent cache is persistent layer state and stays in
-            HBM, as in the engine.
+            back to the host, every step (one recorded CUDA graph of three kernels per layer,
+            replayed; the kernels read the page-locked inputs and write the page-locked output in
+            place).  The latent cache is persistent layer state and stays in HBM, as in the engine.
   roofline  the attention kernel alone (the same graph replay with the combine kernel skipped),
             against the measured HBM copy bandwidth.
   --impl reference   times the CPU restatement of the reference's attention semantics (the test
@@ -362,9 +363,10 @@ def run_ours(args) -> None:
     n_layers = n_copies
     layers = []
     for j in range(n_layers):
-        lay = pkg.MlaDecodeLayer(ctx=n_rows, H=H, T_max=T, device=dev)
+        lay = pkg.MlaDecodeLayer(ctx=n_rows, H=H, T_max=T, device=dev, use_graph=True)
         lay.cache.copy_(caches[j])
         layers.append(lay)
+    torch.cuda.synchronize()
     del caches
     q_host = randn_f16((T, H, D_QK)).cpu().pin_memory()
     kv_host = (torch.randn((T, D_QK), generator=gen, device=dev) * 0.5).cpu().pin_memory()

@@ -58,6 +58,9 @@ SIGNATURES = {
     "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "gs_rope_f16_inplace": (i32, [vp, i32, i32, i32, i32, i64, f32, vp]),
     "gs_mla_layer_step_host": (i32, [C.POINTER(LayerStep), vp]),
+    "gs_mla_layer_graph_create": (i32, [C.POINTER(LayerStep), vp, C.POINTER(vp)]),
+    "gs_mla_layer_graph_step": (i32, [vp, i64, vp, i32]),
+    "gs_mla_layer_graph_destroy": (i32, [vp]),
     "gs_attn_last_error_string": (C.c_char_p, []),
     "gs_attn_version": (C.c_char_p, []),
     "gs_mla_decode_status": (i32, [vp, C.POINTER(C.c_int32), vp]),

@@ -192,7 +192,7 @@ class MlaDecodeLayer:
     The latent cache is persistent layer state in HBM (forward.rs:388-404), not a per-step input.
     """
 
-    def __init__(self, ctx: int, H: int, *, d_qk=576, d_v=512, d_rope=64, T_max=2, device=None):
+    def __init__(self, ctx: int, H: int, *, d_qk=576, d_v=512, d_rope=64, T_max=2, device=None, use_graph=False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.ctx, self.H, self.d_qk, self.d_v, self.d_rope, self.T_max = ctx, H, d_qk, d_v, d_rope, T_max
         self.cache = torch.zeros((ctx, d_qk), dtype=torch.float16, device=self.device)  # zero-initialised, forward.rs:390
@@ -213,20 +213,62 @@ class MlaDecodeLayer:
         st.H, st.d_qk, st.d_v, st.d_rope = H, d_qk, d_v, d_rope
         st.rope_base, st.scale = 10000.0, SCALE_256
         self._step = st
+        # graph mode: the whole step (staging, append, attention) is one replayed CUDA graph of three kernels on a
+        # stream of the layer's own; the kernels read and write the page-locked host tensors in place
+        self.use_graph = bool(use_graph)
+        self._graphs = {}
+        self._graph_stream = None
+        if self.use_graph:
+            torch.cuda.synchronize(self.device)
+            self._graph_stream = torch.cuda.Stream(device=self.device)
+            self._graph_stream_handle = self._graph_stream.cuda_stream
+            self._graph_step = _lib.load().gs_mla_layer_graph_step
+
+    def __del__(self):
+        try:
+            L = _lib.load()
+            for h in self._graphs.values():
+                L.gs_mla_layer_graph_destroy(h)
+        except Exception:
+            pass
 
     def rollback(self, n: int = 1) -> None:
         """Drop the last n positions (rejected MTP draft): the rows are simply overwritten by the next
         append, as in forward.rs:1564-1575."""
         self.pos = max(0, self.pos - n)
 
+    def _graph_for(self, q_host, kv_host, T):
+        key = (q_host.data_ptr(), kv_host.data_ptr(), T)
+        h = self._graphs.get(key)
+        if h is None:
+            s = self._step
+            s.q_host, s.kv_host, s.T, s.pos0 = q_host.data_ptr(), kv_host.data_ptr(), T, 0
+            out = C.c_void_p()
+            _lib.check(_lib.load().gs_mla_layer_graph_create(C.byref(s), self._graph_stream.cuda_stream, C.byref(out)),
+                       "gs_mla_layer_graph_create")
+            h = self._graphs[key] = out.value
+        return h
+
     def step(self, q_host: torch.Tensor, kv_host: torch.Tensor) -> torch.Tensor:
         """q_host f16 [T,H,d_qk], kv_host f32 [T,d_qk] in pinned host memory -> f32 [T,H,d_v] (host).
-        One C call enqueues copy-in, append, attention and copy-out; then the stream is drained."""
+        One C call enqueues copy-in, append, attention and copy-out; then the stream is drained.  In graph
+        mode the host buffers are part of the recorded graph: reuse the same two tensors every step."""
         T = q_host.shape[0]
         if T > self.T_max:
             raise ValueError("T exceeds T_max")
         if self.pos + T > self.ctx:
             raise RuntimeError(f"context full ({self.ctx} tokens)")
+        if self.use_graph:
+            h = self._graphs.get((q_host.data_ptr(), kv_host.data_ptr(), T))
+            if h is None:
+                if not (q_host.is_pinned() and kv_host.is_pinned()):
+                    raise ValueError("graph mode needs page-locked host tensors")
+                h = self._graph_for(q_host, kv_host, T)
+            rc = self._graph_step(h, self.pos, self._graph_stream_handle, 1)
+            if rc:
+                _lib.check(rc, "gs_mla_layer_graph_step")
+            self.pos += T
+            return self._o_host[0, :T]
         s = self._step
         s.q_host, s.kv_host = q_host.data_ptr(), kv_host.data_ptr()
         s.pos0, s.T = self.pos, T

@@ -30,6 +30,8 @@
 // through the common exit, which frees tensor memory.
 #include <string.h>
 
+#include <atomic>
+
 #include "internal.cuh"
 #include "sm100_prims.cuh"
 
@@ -40,13 +42,18 @@ int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64
     typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    // looked up on every call: a cached pointer could go stale across a device reset
-    GS_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (!fn || qres != cudaDriverEntryPointSuccess) {
-        set_error("cuTensorMapEncodeTiled is not available from this driver");
-        return (int) cudaErrorNotSupported;
+    // The entry point is a host function of the driver library: it stays valid for the life of the process
+    // (also across a device reset), so it is looked up once.  Racing first calls store the same value.
+    static std::atomic<void *> cached{nullptr};
+    void *fn = cached.load(std::memory_order_acquire);
+    if (!fn) {
+        cudaDriverEntryPointQueryResult qres;
+        GS_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) {
+            set_error("cuTensorMapEncodeTiled is not available from this driver");
+            return (int) cudaErrorNotSupported;
+        }
+        cached.store(fn, std::memory_order_release);
     }
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {row_stride_bytes};

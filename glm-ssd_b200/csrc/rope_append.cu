@@ -9,6 +9,8 @@
 // f32 functions (this file must not be built with fast-math).
 #include <math.h>
 
+#include <new>
+
 #include "internal.cuh"
 
 namespace gs {
@@ -97,6 +99,67 @@ __global__ void k_rope_append(const AppendParams P) {
             v = rotate(v, cs, sn);
         }
         *reinterpret_cast<__half2 *>(dst + c) = __floats2half2_rn(v.x, v.y);
+    }
+}
+
+// First kernel of a replayed step.  Block 0 reads the position from a page-locked host word (so the launch
+// itself carries no per-step argument and can be replayed from a CUDA graph), appends the T rows of one
+// dense sequence there and leaves the new length in *len_dev for the attention kernel.  A step that would
+// run past the cache writes nothing, sets bit 17 of the status word and reports through host_words[1].
+// `kv` is page-locked host memory read in place.  The other blocks bring the query rows over from
+// page-locked host memory (16-byte words); a step then needs no copy-engine operation.
+constexpr int STAGE_T_MAX = 4;   // new rows per replayed step
+constexpr int STAGE_PAIRS = 3;   // column pairs per thread: rows of up to 768 values
+__global__ void __launch_bounds__(128) k_stage_append(const AppendParams P, volatile int64_t *host_words, int32_t *len_dev,
+                                                      int64_t cache_rows, int32_t *status, const uint4 *q_src, uint4 *q_dst,
+                                                      int q_words) {
+    if (blockIdx.x > 0) {
+        const int nb = gridDim.x - 1;
+        for (int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < q_words; i += nb * blockDim.x) q_dst[i] = q_src[i];
+        return;
+    }
+    // every read that crosses to the host is issued before any is used: the position and the new rows arrive in
+    // one round trip (STAGE_T_MAX rows of up to STAGE_PAIRS * 128 column pairs)
+    const int pairs = P.d_row / 2;
+    float2 v[STAGE_T_MAX][STAGE_PAIRS];
+#pragma unroll
+    for (int t = 0; t < STAGE_T_MAX; t++)
+#pragma unroll
+        for (int k = 0; k < STAGE_PAIRS; k++) {
+            const int j = threadIdx.x + k * 128;
+            v[t][k] = (t < P.T && j < pairs) ? *reinterpret_cast<const float2 *>(P.kv + (int64_t) t * P.d_row + 2 * j)
+                                             : make_float2(0.f, 0.f);
+        }
+    const int64_t pos0 = host_words[0];
+    if (pos0 < 0 || pos0 + P.T > cache_rows) {
+        if (threadIdx.x == 0) {
+            atomicOr(status, 1 << 17);
+            host_words[1] = 1;
+            *len_dev = 0;  // the attention that follows sees an empty sequence
+        }
+        return;
+    }
+    if (threadIdx.x == 0) *len_dev = (int32_t) (pos0 + P.T);
+    const int d0 = P.d_row - P.d_rope;
+#pragma unroll
+    for (int t = 0; t < STAGE_T_MAX; t++) {
+        if (t >= P.T) break;
+        const int64_t pos = pos0 + t;
+        __half *dst = P.cache + pos * P.d_row;
+#pragma unroll
+        for (int k = 0; k < STAGE_PAIRS; k++) {
+            const int j = threadIdx.x + k * 128;
+            if (j >= pairs) break;
+            const int c = 2 * j;
+            float2 u = v[t][k];
+            if (c >= d0) {
+                const float ang = (float) pos * P.tab.inv_freq[(c - d0) >> 1];
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                u = rotate(u, cs, sn);
+            }
+            *reinterpret_cast<__half2 *>(dst + c) = __floats2half2_rn(u.x, u.y);
+        }
     }
 }
 
@@ -260,5 +323,130 @@ GS_EXPORT int gs_mla_layer_step_host(const gs_mla_layer_step *s, void *stream) {
     a.max_seq_len = (int32_t) (s->pos0 + s->T);
     if (int e = gs_mla_decode(&a, stream)) return e;
     GS_TRY(cudaMemcpyAsync(s->o_host, s->o_dev, (size_t) s->T * s->H * s->d_v * 4, cudaMemcpyDeviceToHost, st));
+    return 0;
+}
+
+// ---- the same step as a replayable CUDA graph ---------------------------------------------------------
+struct gs_mla_layer_graph {
+    cudaGraphExec_t exec;
+    int64_t *host_words;  // page-locked: [0] position of the step (host -> device), [1] refusal flag (device -> host)
+    int64_t cache_rows;
+    int T;
+};
+
+GS_EXPORT int gs_mla_layer_graph_create(const gs_mla_layer_step *s, void *stream, gs_mla_layer_graph **out) {
+    if (!s || !out) return fail_invalid("gs_mla_layer_graph_create: null argument");
+    *out = nullptr;
+    if (s->T <= 0 || s->H <= 0) return fail_invalid("gs_mla_layer_graph_create: T and H must be positive");
+    if (s->T > STAGE_T_MAX || s->d_qk > STAGE_PAIRS * 256)
+        return fail_invalid("gs_mla_layer_graph_create: at most 4 new rows of at most 768 values per step");
+    if (!s->q_host || !s->kv_host || !s->o_host || !s->q_dev || !s->cache || !s->seq_len_dev || !s->workspace)
+        return fail_invalid("gs_mla_layer_graph_create: null pointer");
+    if (!stream) return fail_invalid("gs_mla_layer_graph_create: stream capture needs a stream other than the default one");
+    if (int e = check_rope(s->d_qk, s->d_rope)) return e;
+    if (s->cache_rows <= 0 || s->cache_rows >= (1ll << 31)) return fail_invalid("gs_mla_layer_graph_create: cache_rows out of range");
+    cudaStream_t st = (cudaStream_t) stream;
+    // the page-locked host buffers as the device sees them: the kernels read q / kv and write o in place
+    void *q_map = nullptr, *kv_map = nullptr, *o_map = nullptr, *w_map = nullptr;
+    GS_TRY(cudaHostGetDevicePointer(&q_map, const_cast<void *>(s->q_host), 0));
+    GS_TRY(cudaHostGetDevicePointer(&kv_map, const_cast<float *>(s->kv_host), 0));
+    GS_TRY(cudaHostGetDevicePointer(&o_map, s->o_host, 0));
+    const size_t q_bytes = (size_t) s->T * s->H * s->d_qk * 2;
+    if (q_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(q_map) & 15) || (reinterpret_cast<uintptr_t>(s->q_dev) & 15) ||
+        (reinterpret_cast<uintptr_t>(kv_map) & 7) || (reinterpret_cast<uintptr_t>(o_map) & 15))
+        return fail_invalid("gs_mla_layer_graph_create: host buffers must be 16-byte aligned");
+    int64_t *words = nullptr;
+    GS_TRY(cudaHostAlloc((void **) &words, 2 * sizeof(int64_t), cudaHostAllocMapped));
+    words[0] = words[1] = 0;
+    cudaError_t ce = cudaHostGetDevicePointer(&w_map, words, 0);
+    if (ce == cudaSuccess) ce = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    if (ce != cudaSuccess) {
+        cudaFreeHost(words);
+        GS_TRY(ce);
+    }
+    auto enqueue = [&]() -> int {
+        AppendParams P{};
+        P.kv = (const float *) kv_map;
+        P.cache = (__half *) s->cache;
+        P.T = s->T;
+        P.d_row = s->d_qk;
+        P.d_rope = s->d_rope;
+        fill_table(P.tab, s->d_rope, s->rope_base);
+        const int q_words = (int) (q_bytes / 16);
+        const int copy_blocks = (q_words + 127) / 128 < 24 ? (q_words + 127) / 128 : 24;
+        k_stage_append<<<1 + copy_blocks, 128, 0, st>>>(P, (volatile int64_t *) w_map, s->seq_len_dev, s->cache_rows,
+                                                        (int32_t *) s->workspace, (const uint4 *) q_map, (uint4 *) s->q_dev,
+                                                        q_words);
+        GS_TRY(cudaGetLastError());
+        gs_mla_decode_args a{};
+        a.q = s->q_dev;
+        a.cache = s->cache;
+        a.cache_rows = s->cache_rows;
+        a.seq_lens = s->seq_len_dev;
+        a.page_rows = 64;
+        a.scale = s->scale;
+        a.tail_causal = 1;
+        a.o = (float *) o_map;  // the combine kernel stores the result straight into the host buffer
+        a.workspace = s->workspace;
+        a.workspace_bytes = s->workspace_bytes;
+        a.n_seq = 1;
+        a.T = s->T;
+        a.H = s->H;
+        a.d_qk = s->d_qk;
+        a.d_v = s->d_v;
+        a.max_seq_len = (int32_t) s->cache_rows;
+        return gs_mla_decode(&a, stream);
+    };
+    const int e = enqueue();
+    cudaGraph_t graph = nullptr;
+    ce = cudaStreamEndCapture(st, &graph);  // always ends the capture, also after an error
+    cudaGraphExec_t exec = nullptr;
+    if (!e && ce == cudaSuccess) ce = cudaGraphInstantiate(&exec, graph, 0);
+    if (graph) cudaGraphDestroy(graph);
+    gs_mla_layer_graph *g = (!e && ce == cudaSuccess) ? new (std::nothrow) gs_mla_layer_graph : nullptr;
+    if (!g) {
+        if (exec) cudaGraphExecDestroy(exec);
+        cudaFreeHost(words);
+        if (e) {
+            (void) cudaGetLastError();
+            return e;
+        }
+        GS_TRY(ce);
+        set_error("gs_mla_layer_graph_create: out of host memory");
+        return (int) cudaErrorMemoryAllocation;
+    }
+    g->exec = exec;
+    g->host_words = words;
+    g->cache_rows = s->cache_rows;
+    g->T = s->T;
+    *out = g;
+    return 0;
+}
+
+GS_EXPORT int gs_mla_layer_graph_step(gs_mla_layer_graph *g, int64_t pos0, void *stream, int wait) {
+    if (!g) return fail_invalid("gs_mla_layer_graph_step: null handle");
+    if (pos0 < 0 || pos0 + g->T > g->cache_rows) {
+        set_error("context full (%lld tokens)", (long long) g->cache_rows);  // forward.rs:839-841
+        return (int) cudaErrorInvalidValue;
+    }
+    *(volatile int64_t *) g->host_words = pos0;
+    GS_TRY(cudaGraphLaunch(g->exec, (cudaStream_t) stream));
+    if (wait) {
+        GS_TRY(cudaStreamSynchronize((cudaStream_t) stream));
+        if (((volatile int64_t *) g->host_words)[1] != 0) {
+            set_error("gs_mla_layer_graph_step: the device refused a step past the end of the cache");
+            return (int) cudaErrorInvalidValue;
+        }
+    }
+    return 0;
+}
+
+GS_EXPORT int gs_mla_layer_graph_destroy(gs_mla_layer_graph *g) {
+    if (!g) return 0;
+    const cudaError_t e = cudaGraphExecDestroy(g->exec);
+    const cudaError_t f = cudaFreeHost(g->host_words);
+    delete g;
+    GS_TRY(e);
+    GS_TRY(f);
     return 0;
 }

@@ -198,6 +198,21 @@ typedef struct gs_mla_layer_step {
 } gs_mla_layer_step;
 int gs_mla_layer_step_host(const gs_mla_layer_step *step /* host */, void *stream);
 
+/* The same step recorded once as a CUDA graph of three kernels and replayed (no counterpart in the reference,
+ * which enqueues every call separately).  q_host / kv_host / o_host must be page-locked, 16-byte aligned and
+ * stay where they are: the first kernel reads the inputs from them in place, the combine kernel stores the
+ * result into o_host in place (no copy-engine operation; kv_dev / o_dev are unused), and the caller refills
+ * them between steps.  The position of a step travels through a page-locked word the handle owns, so one
+ * graph serves every step with the same T; step->pos0 is ignored at creation.  One step may be in flight per
+ * handle.  `stream` must not be the default stream.
+ *   gs_mla_layer_graph_step(g, pos0, stream, wait): rejects pos0 + T > cache_rows ("context full",
+ *   forward.rs:839-841) before launching; wait != 0 also synchronises the stream, after which o_host is valid.
+ *   Moving pos0 back (a rejected MTP draft, forward.rs:1564-1575) needs no other call. */
+typedef struct gs_mla_layer_graph gs_mla_layer_graph;
+int gs_mla_layer_graph_create(const gs_mla_layer_step *step /* host */, void *stream, gs_mla_layer_graph **out);
+int gs_mla_layer_graph_step(gs_mla_layer_graph *g, int64_t pos0, void *stream, int wait);
+int gs_mla_layer_graph_destroy(gs_mla_layer_graph *g);
+
 /* ------------------------------------------------------------------------------------------------
  * Diagnostics.
  * ---------------------------------------------------------------------------------------------- */

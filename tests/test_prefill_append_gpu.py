@@ -137,3 +137,52 @@ def test_decode_layer_step_matches_oracle(pkg, cuda, oracle):
         check_close(o, want, f"step pos={pos}", 4e-3, 4e-4)
     layer.rollback(1)
     assert layer.pos == pos - 1
+
+
+def test_decode_layer_graph_step_matches_eager_and_oracle(pkg, cuda, oracle):
+    """The same step replayed from a CUDA graph with the position kept on the device: equal to the eager
+    step bit for bit, right against the oracle, and a moved-back position (rejected draft) is honoured."""
+    rng = np.random.default_rng(22)
+    H, ctx = 20, 700
+    eager = pkg.MlaDecodeLayer(ctx=ctx, H=H)
+    graph = pkg.MlaDecodeLayer(ctx=ctx, H=H, use_graph=True)
+    bufs = {T: (cuda.empty((T, H, 576), dtype=cuda.float16).pin_memory(), cuda.empty((T, 576), dtype=cuda.float32).pin_memory())
+            for T in (1, 2)}
+    ref_cache = np.zeros((ctx, 576), np.float16)
+    pos = 0
+    for i, T in enumerate((2, 2, 1, 2, 1, 1, 2)):
+        q = rng.standard_normal((T, H, 576), dtype=np.float32).astype(np.float16)
+        kv = rng.standard_normal((T, 576), dtype=np.float32) * np.float32(0.5)
+        qh, kvh = bufs[T]
+        qh.copy_(cuda.from_numpy(q))
+        kvh.copy_(cuda.from_numpy(kv))
+        o_g = graph.step(qh, kvh).numpy().copy()
+        o_e = eager.step(qh, kvh).numpy().copy()
+        assert np.array_equal(o_g, o_e), f"graph and eager step differ at step {i}"
+        ref_cache[pos:pos + T] = oracle.rope_append(kv, pos)
+        pos += T
+        check_close(o_g, oracle.mla_decode(q[None], ref_cache, [pos], 1 / 16)[0], f"graph step pos={pos}", 4e-3, 4e-4)
+        if i == 3:  # the second token of this draft is rejected
+            graph.rollback(1)
+            eager.rollback(1)
+            pos -= 1
+    assert graph.pos == eager.pos == pos
+    assert len(graph._graphs) == 2  # one graph per T
+    assert pkg.decode_status(graph.workspace) == 0
+
+
+def test_decode_layer_graph_refuses_to_run_past_the_cache(pkg, cuda):
+    H, ctx = 20, 64
+    layer = pkg.MlaDecodeLayer(ctx=ctx, H=H, T_max=2, use_graph=True)
+    qh = cuda.zeros((2, H, 576), dtype=cuda.float16).pin_memory()
+    kvh = cuda.ones((2, 576), dtype=cuda.float32).pin_memory()
+    layer.pos = ctx - 2
+    layer.step(qh, kvh)  # records the graph; the last two rows fit
+    layer.pos = ctx - 1
+    with pytest.raises(RuntimeError, match="context full"):
+        layer.step(qh, kvh)
+    h = next(iter(layer._graphs.values()))
+    L = pkg._lib.load()
+    assert L.gs_mla_layer_graph_step(h, ctx - 1, layer._graph_stream.cuda_stream, 1) != 0
+    assert b"context full" in L.gs_attn_last_error_string()
+    assert L.gs_mla_layer_graph_step(None, 0, layer._graph_stream.cuda_stream, 1) != 0
