@@ -205,6 +205,11 @@ __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
     if (C.status && C.status[1] != 0 && cta < 256 && threadIdx.x == 0)
         prof = reinterpret_cast<long long *>(const_cast<char *>(reinterpret_cast<const char *>(C.status)) + kCombineProfOffsetBytes) + cta * 8;
     if (prof) prof[0] = sm100::global_timer_ns();
+#if __CUDA_ARCH__ >= 900
+    // the kernel behind this one may be scheduled as soon as every CTA of this grid is running: its CTAs
+    // then start on each SM as this grid's leave it, and their own dependency wait still covers our stores
+    cudaTriggerProgrammaticLaunchCompletion();
+#endif
     const bool early = combine_locate_is_early(C);
     SegRange R;
     if (early) R = combine_locate(C, blockIdx.x, S);

@@ -78,6 +78,7 @@ constexpr int BLK_BYTES = TILE * 128;    // one 64-column block of a tile: 64 ro
 constexpr int NBLK_MAX = 9;              // 576 / 64
 constexpr int STAGE_BYTES = NBLK_MAX * BLK_BYTES;
 constexpr int STAGES = 2;
+constexpr int AHEAD = 2;                 // tiles of a CTA's range asked into L2 before the inputs are final (1-3 measured: 2 best)
 constexpr int N_MMA_WARPS = 3;           // concurrently issuing MMA warps
 constexpr int NTHREADS = 32 * (1 + N_MMA_WARPS + 4);  // warp 0 producer, warps 1-3 MMA, warps 4-7 softmax group
 constexpr int TMEM_COLS = 512;
@@ -105,6 +106,7 @@ struct UmmaParams {
     int2 *ws_desc;
     int32_t *status;
     int n_seq, T, H, rows_q, d_v;
+    int64_t cache_rows;
 };
 
 struct Barriers {
@@ -261,43 +263,79 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tmem_alloc(&M.tmem_base, TMEM_COLS);
         tmem_relinquish();
     }
-    // everything above touched only this CTA's own resources; inputs written by earlier kernels come next
+    // The schedule: units per sequence, their running sum, this CTA's chunk and the sequence it starts in.
+    int total = 0, chunk = 1, start = 0, end = 0, b_cur = 0;
+    auto build_schedule = [&]() {
+        {
+            // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
+            const uint64_t pol_keep = l2_policy_evict_last();
+            for (int b = tid; b < P.n_seq; b += NTHREADS) {
+                const int len = max(ld_global_hint(P.seq_lens + b, pol_keep), 0);
+                M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b, pol_keep) : 0;
+                M.len[b] = len;
+                M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 0 && P.n_seq > 1) {  // inclusive scan of cum[1..n_seq], 32 entries per step
+            int carry = 0;
+            for (int base = 1; base <= P.n_seq; base += 32) {
+                const int i = base + lane;
+                int v = i <= P.n_seq ? M.cum[i] : 0;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += u;
+                }
+                v += carry;
+                if (i <= P.n_seq) M.cum[i] = v;
+                carry = __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+        if (P.n_seq > 1) __syncthreads();
+        tc_fence_after();
+        total = M.cum[P.n_seq];
+        chunk = max(1, (total + (int) gridDim.x - 1) / (int) gridDim.x);
+        start = min(total, (int) blockIdx.x * chunk);
+        end = min(total, start + chunk);
+        // first sequence of this CTA's range (binary search: largest b with cum[b] <= start)
+        int lo = 0, hi = P.n_seq - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (M.cum[mid] <= start) lo = mid; else hi = mid - 1;
+        }
+        b_cur = lo;
+    };
+    // Everything above touched only this CTA's own resources.  While the kernel in front of this one is still
+    // running (programmatic dependent launch), the schedule is built once from whatever the length / base /
+    // page arrays hold at the moment - the values of the previous step when that kernel is about to update
+    // them - and the first tiles of this CTA's range are asked into L2.  Nothing read here is used for a
+    // result: a stale value costs a useless prefetch, and every index is checked before it is followed.
+    build_schedule();
+    if (warp == 0) {
+        int pp = start, bb = b_cur, asked = 0;
+        Segment s2;
+        while (asked < AHEAD && next_segment(pp, bb, end, M.cum, unit_rows, M.len, s2)) {
+            for (int j = 0; j < s2.n_tiles && asked < AHEAD; j++, asked++) {
+                const int row = s2.r0 + j * TILE;
+                int64_t grow = -1;
+                if (!P.paged) grow = (int64_t) M.base[s2.b] + row;
+                else if (row / TILE < P.page_table_stride)
+                    grow = (int64_t) P.page_table[(int64_t) s2.b * P.page_table_stride + row / TILE] * TILE;
+                if (grow >= 0 && grow < P.cache_rows && elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < NBLK; k++) tma_prefetch_2d(&P.tm_kv64, k * 64, (int) grow);
+                }
+                __syncwarp();
+            }
+        }
+    }
+    __syncthreads();  // the arrays are rebuilt below
     griddep_wait();
     if (tid == 0) GS_CTA_STAMP(1);
-    {
-        // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
-        const uint64_t pol_keep = l2_policy_evict_last();
-        for (int b = tid; b < P.n_seq; b += NTHREADS) {
-            const int len = max(ld_global_hint(P.seq_lens + b, pol_keep), 0);
-            M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b, pol_keep) : 0;
-            M.len[b] = len;
-            M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0 && P.n_seq > 1) {  // inclusive scan of cum[1..n_seq], 32 entries per step
-        int carry = 0;
-        for (int base = 1; base <= P.n_seq; base += 32) {
-            const int i = base + lane;
-            int v = i <= P.n_seq ? M.cum[i] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int u = __shfl_up_sync(0xffffffffu, v, o);
-                if (lane >= o) v += u;
-            }
-            v += carry;
-            if (i <= P.n_seq) M.cum[i] = v;
-            carry = __shfl_sync(0xffffffffu, v, 31);
-        }
-    }
-    if (P.n_seq > 1) __syncthreads();
-    tc_fence_after();
+    build_schedule();
     const uint32_t tmem = M.tmem_base;
-    const int total = M.cum[P.n_seq];
-    const int chunk = max(1, (total + (int) gridDim.x - 1) / (int) gridDim.x);
-    const int start = min(total, (int) blockIdx.x * chunk);
-    const int end = min(total, start + chunk);
     if (blockIdx.x == 0) {  // where the combine kernel finds each sequence's segments
         for (int b = tid; b < P.n_seq; b += NTHREADS) {
             const int u0 = M.cum[b], u1 = M.cum[b + 1];
@@ -308,16 +346,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             }
             P.ws_desc[b] = d;
         }
-    }
-    // first sequence of this CTA's range (binary search: largest b with cum[b] <= start)
-    int b_cur = 0;
-    {
-        int lo = 0, hi = P.n_seq - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (M.cum[mid] <= start) lo = mid; else hi = mid - 1;
-        }
-        b_cur = lo;
     }
     griddep_launch_dependents();
     if (tid == 0) GS_STAMP(kProfTiles - 1, 1);
@@ -782,6 +810,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.H = p.H;
     P.rows_q = rows_q;
     P.d_v = p.d_v;
+    P.cache_rows = p.cache_rows;
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");

@@ -145,6 +145,12 @@ __device__ __forceinline__ int ld_global_hint(const int *p, uint64_t policy) {
 __device__ __forceinline__ void st_global_hint(float *p, float v, uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
 }
+// Ask for one box of a tiled tensor to be brought into L2 (no destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)),
+                 "r"(c0), "r"(c1)
+                 : "memory");
+}
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / tcgen05 operand reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
