@@ -191,24 +191,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
                 tc_fence_after();
                 const int k0 = j * BN;
                 const bool need_mask = k0 + BN - 1 > P.p0 + q0;  // some row of the block must not see some key
-                // pass 1: row maximum of the scaled scores
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t r0[16], r1[16];
-                    tmem_ld16(s_addr + c * 32, r0);
-                    tmem_ld16(s_addr + c * 32 + 16, r1);
-                    tmem_wait_ld();
+                // the whole score row of this thread (128 keys) is read once and kept in registers: one
+                // tensor-memory round trip per tile instead of eight
+                uint32_t r[BN];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]);
-                        if (need_mask) {
-                            if (k0 + c * 32 + i > k_lim) a = -INFINITY;
-                            if (k0 + c * 32 + 16 + i > k_lim) b = -INFINITY;
-                        }
-                        mx = fmaxf(mx, fmaxf(a, b));
-                    }
+                for (int c = 0; c < BN / 16; c++) tmem_ld16(s_addr + c * 16, *reinterpret_cast<uint32_t(*)[16]>(r + c * 16));
+                tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < BN; i++)
+                        if (k0 + i > k_lim) r[i] = __float_as_uint(-INFINITY);
                 }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < BN; i += 4) {
+                    mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
+                    mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
+                    mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
+                    mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
+                }
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 mx *= P.scale_log2;  // scale > 0
                 // lazy reference update, decided per warp (tensor-memory accesses are warp-wide)
                 const bool grow = mx > m_run + PF_RESCALE;
@@ -234,39 +236,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
                     l_run *= f;
                     m_run = m_new;
                 }
-                // pass 2: probabilities, row sum, P as packed f16 pairs over the first columns of this S buffer
+                // probabilities, row sum, P as packed f16 pairs (keys 2i, 2i+1 -> column i of this S buffer)
                 const float nm = -m_run;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; c++) {
-                    uint32_t r0[16], r1[16], pk[16];
-                    tmem_ld16(s_addr + c * 32, r0);
-                    tmem_ld16(s_addr + c * 32 + 16, r1);
-                    tmem_wait_ld();
-                    float p[32];
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]);
-                        if (need_mask) {
-                            if (k0 + c * 32 + i > k_lim) a = -INFINITY;
-                            if (k0 + c * 32 + 16 + i > k_lim) b = -INFINITY;
-                        }
-                        p[i] = ex2_approx(fmaf(a, P.scale_log2, nm));
-                        p[16 + i] = ex2_approx(fmaf(b, P.scale_log2, nm));
-                    }
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        l_run += p[2 * i] + p[2 * i + 1];
-                        const __half2 hh = __floats2half2_rn(p[2 * i], p[2 * i + 1]);
-                        pk[i] = *reinterpret_cast<const uint32_t *>(&hh);
-                    }
-                    tmem_st16(s_addr + c * 16, pk);  // keys 32c .. 32c+31 -> 16 packed columns
+                for (int i = 0; i < BN / 2; i++) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), P.scale_log2, nm));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), P.scale_log2, nm));
+                    l4[i & 3] += p0 + p1;
+                    const __half2 hh = __floats2half2_rn(p0, p1);
+                    r[i] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
+                l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+#pragma unroll
+                for (int c = 0; c < BN / 32; c++) tmem_st16(s_addr + c * 16, *reinterpret_cast<const uint32_t(*)[16]>(r + c * 16));
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B.p_full[j & 1]);
             }
             // ---- epilogue: O / l -> global ------------------------------------------------------------------------
+            // A parity wait only tells phases apart when the waiter is at most one phase behind.  These warps last
+            // saw P.V(n-3) complete (through S(n-1), which was issued after it), so P.V(n-2) is awaited first:
+            // asking for the parity of P.V(n-1) while P.V(n-2) is still running would return at once.
+            if (ok && n_tiles >= 2) ok = mbar_wait(&B.pv_done, (n_tiles - 2) & 1, abort_flag, P.status, 4);
             if (ok) ok = mbar_wait(&B.pv_done, (n_tiles - 1) & 1, abort_flag, P.status, 4);
             if (ok) {
                 tc_fence_after();
