@@ -4,18 +4,22 @@
 // queries, crates/engine/src/forward.rs:61, :898-908): query i of head h attends keys 0 .. p0+i,
 // score = scale * q.k over d = 256, softmax, o = P V.
 //
-// One CTA per (128-query block, head).  Per 128-key tile:
-//   S[128 x 128]  = Q[128 x 256] . K_tile^T      16 MMAs (M = 128, N = 128, K = 16), both operands
+// One CTA per (128-query block, head).  Per 64-key tile:
+//   S[128 x 64]   = Q[128 x 256] . K_tile^T      16 MMAs (M = 128, N = 64, K = 16), both operands
 //                                                 K-major in 128-byte-swizzled shared memory
 //   P = exp2(S*c - m) as f16, written back into the tensor memory columns of S (one query row per
 //       thread, so the row maximum and row sum need no shuffles)
-//   O[128 x 256] += P . V_tile                    8 MMAs (M = 128, N = 256, K = 16) with P read from
+//   O[128 x 256] += P . V_tile                    4 MMAs (M = 128, N = 256, K = 16) with P read from
 //                                                 tensor memory and V_tile read MN-major
-// S is double-buffered in tensor memory (2 x 128 columns + 256 columns of O = all 512), so the
-// scores of tile j+1 are computed while the softmax of tile j runs.  K and V tiles are single
-// 64 KB buffers fed by two independent TMA producers; K of tile j+1 is fetched as soon as S of tile j
-// has been computed, V of tile j+1 as soon as P.V of tile j has.  The accumulator is rescaled lazily
-// (only when a row maximum grows by more than 2^8), decided per warp.
+// Tensor memory holds four score / probability buffers (4 x 64 columns) and the accumulator (256 columns), so
+// the scores run up to three tiles ahead of the softmax.  Shared memory holds the 64 KB query tile, three 32 KB
+// K stages and two 32 KB V stages, fed by two independent TMA producers: every load has more than a tile period
+// to land (128-key tiles in single buffers left the tensor pipe waiting for every load).  Three warps issue
+// MMAs (scores of even tiles, scores of odd tiles, P.V): a single thread issues one MMA per ~65 cycles whatever
+// its size, which for 20 MMAs per 64-key tile is more than the tensor time.  What bounds the steady state now is
+// the tensor pipe itself: an N = 64 MMA occupies it for ~45 cycles (33 at full rate), so a tile takes
+// 16 x 45 + 4 x 131 = 1244 cycles (measured 1240) against 1049 at peak.
+// The accumulator is rescaled lazily (only when a row maximum grows by more than 2^8), decided per warp.
 // Every mbarrier wait is bounded and ends in an error status instead of a hang.
 #include <string.h>
 
@@ -27,13 +31,18 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;                  // query rows per CTA
-constexpr int BN = 128;                  // keys per tile
+constexpr int BN = 64;                   // keys per tile
 constexpr int HD = 256;                  // head width
 constexpr int NDB = HD / 64;             // 64-column blocks per row
-constexpr int TBLK = 128 * 128;          // bytes of one [128 rows][64 cols] block
-constexpr int TILE_BYTES = NDB * TBLK;   // 64 KB: a Q, K or V tile
-constexpr int PF_THREADS = 224;          // warp 0 K producer, 1 MMA, 2-5 softmax, 6 V producer
-constexpr int S_COLS = 128, O_COL = 256;
+constexpr int QBLK = BM * 128;           // bytes of one [128 query rows][64 cols] block
+constexpr int KBLK = BN * 128;           // bytes of one [64 key rows][64 cols] block
+constexpr int Q_BYTES = NDB * QBLK;      // 64 KB
+constexpr int KV_BYTES = NDB * KBLK;     // 32 KB: a K or V tile
+constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int S_BUFS = 4;                // score / probability buffers in tensor memory: 4 x 64 columns + 256 of O
+// warp 0 K producer, 1 score MMAs of even tiles, 2-5 softmax, 6 V producer, 7 score MMAs of odd tiles, 8 P.V MMAs
+constexpr int PF_THREADS = 288;
+constexpr int S_COLS = 64, O_COL = 256;
 constexpr float PF_RESCALE = 8.0f;
 
 struct PrefillParams {
@@ -45,8 +54,20 @@ struct PrefillParams {
     int32_t *status;  // may be nullptr
 };
 
+// Tuning aid, compiled in only for the timing probe: clock stamps of the heaviest CTA's first tiles.
+#ifdef GS_PF_PROF
+__device__ long long g_pf_prof[32 * 8];
+#define PF_STAMP(j, slot)                                                                                  \
+    do {                                                                                                   \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (j) >= 8 && (j) < 40) g_pf_prof[((j) - 8) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define PF_STAMP(j, slot) do { } while (0)
+#endif
+
 struct PfBarriers {
-    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2], pv_done;
+    uint64_t q_full, k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
+    uint64_t s_full[S_BUFS], p_full[S_BUFS], p_free[S_BUFS];  // p_free[b]: P.V has read the probabilities in buffer b
 };
 
 struct PfSmemMisc {
@@ -54,13 +75,13 @@ struct PfSmemMisc {
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr int PF_SMEM = 3 * TILE_BYTES + (int) sizeof(PfSmemMisc) + 1024;
+constexpr int PF_SMEM = Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES + (int) sizeof(PfSmemMisc) + 1024;
 
 __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_constant__ PrefillParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    uint8_t *q_smem = smem, *k_smem = smem + TILE_BYTES, *v_smem = smem + 2 * TILE_BYTES;
-    PfSmemMisc &M = *reinterpret_cast<PfSmemMisc *>(smem + 3 * TILE_BYTES);
+    uint8_t *q_smem = smem, *k_smem = smem + Q_BYTES, *v_smem = k_smem + K_STAGES * KV_BYTES;
+    PfSmemMisc &M = *reinterpret_cast<PfSmemMisc *>(v_smem + V_STAGES * KV_BYTES);
     PfBarriers &B = M.bar;
     volatile int *abort_flag = &M.abort_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -76,15 +97,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
         tma_prefetch_desc(&P.tm_k);
         tma_prefetch_desc(&P.tm_v);
         mbar_init(&B.q_full, 1);
-        mbar_init(&B.k_full, 1);
-        mbar_init(&B.k_empty, 1);
-        mbar_init(&B.v_full, 1);
-        mbar_init(&B.v_empty, 1);
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < K_STAGES; i++) {
+            mbar_init(&B.k_full[i], 1);
+            mbar_init(&B.k_empty[i], 1);
+        }
+        for (int i = 0; i < V_STAGES; i++) {
+            mbar_init(&B.v_full[i], 1);
+            mbar_init(&B.v_empty[i], 1);
+        }
+        for (int i = 0; i < S_BUFS; i++) {
             mbar_init(&B.s_full[i], 1);
             mbar_init(&B.p_full[i], 4);
+            mbar_init(&B.p_free[i], 1);
         }
-        mbar_init(&B.pv_done, 1);
         M.abort_flag = 0;
         fence_barrier_init();
     }
@@ -100,77 +125,85 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
     if (warp == 0) {
         // ---- Q once, then the K tiles -------------------------------------------------------------------
         if (elect_one()) {
-            mbar_arrive_expect_tx(&B.q_full, TILE_BYTES);
+            mbar_arrive_expect_tx(&B.q_full, Q_BYTES);
 #pragma unroll
-            for (int b = 0; b < NDB; b++) tma_load_2d(q_smem + b * TBLK, &P.tm_q, &B.q_full, col0 + b * 64, q0);
+            for (int b = 0; b < NDB; b++) tma_load_2d(q_smem + b * QBLK, &P.tm_q, &B.q_full, col0 + b * 64, q0);
         }
         __syncwarp();
         for (int j = 0; j < n_tiles; j++) {
-            if (j > 0 && !mbar_wait(&B.k_empty, (j - 1) & 1, abort_flag, P.status, 1)) break;
+            const int st = j % K_STAGES;
+            if (!mbar_wait(&B.k_empty[st], ((j / K_STAGES) & 1) ^ 1, abort_flag, P.status, 1)) break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&B.k_full, TILE_BYTES);
+                mbar_arrive_expect_tx(&B.k_full[st], KV_BYTES);
 #pragma unroll
-                for (int b = 0; b < NDB; b++) tma_load_2d(k_smem + b * TBLK, &P.tm_k, &B.k_full, col0 + b * 64, j * BN);
+                for (int b = 0; b < NDB; b++)
+                    tma_load_2d(k_smem + st * KV_BYTES + b * KBLK, &P.tm_k, &B.k_full[st], col0 + b * 64, j * BN);
             }
             __syncwarp();
         }
     } else if (warp == 6) {
         // ---- the V tiles ------------------------------------------------------------------------------------
         for (int j = 0; j < n_tiles; j++) {
-            if (j > 0 && !mbar_wait(&B.v_empty, (j - 1) & 1, abort_flag, P.status, 1)) break;
+            const int st = j & 1;
+            if (!mbar_wait(&B.v_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, P.status, 1)) break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&B.v_full, TILE_BYTES);
+                mbar_arrive_expect_tx(&B.v_full[st], KV_BYTES);
 #pragma unroll
-                for (int b = 0; b < NDB; b++) tma_load_2d(v_smem + b * TBLK, &P.tm_v, &B.v_full, col0 + b * 64, j * BN);
+                for (int b = 0; b < NDB; b++)
+                    tma_load_2d(v_smem + st * KV_BYTES + b * KBLK, &P.tm_v, &B.v_full[st], col0 + b * 64, j * BN);
             }
             __syncwarp();
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer ---------------------------------------------------------------------------------------
+    } else if (warp == 1 || warp == 7) {
+        // ---- score MMA issuers: S = Q . K^T, warp 1 the even tiles, warp 7 the odd ones --------------------------
+        // One thread issues an MMA about every 65 cycles whatever its size, and a tile needs 16 of these (N = 64)
+        // besides the 4 P.V MMAs: three issuing warps keep the issue time below the tensor time.
         constexpr uint32_t idesc_s = make_idesc_f16(BM, BN, 0, 0);
-        constexpr uint32_t idesc_pv = make_idesc_f16(BM, HD, 0, 1);  // A = P from tensor memory, B = V MN-major
         const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);
-        const uint64_t d_v = make_smem_desc(0, TBLK, 1024, kSwizzle128B);
-        const uint32_t q_lo = smem_u32(q_smem) >> 4, k_lo = smem_u32(k_smem) >> 4, v_lo = smem_u32(v_smem) >> 4;
+        const uint32_t q_lo = smem_u32(q_smem) >> 4, k_lo = smem_u32(k_smem) >> 4;
         bool ok = mbar_wait(&B.q_full, 0, abort_flag, P.status, 2);
-        auto issue_s = [&](int j) {
+        // Scores run up to three tiles ahead of the softmax: S(j) goes into tensor-memory buffer j & 3, where
+        // P(j-4) lives until P.V(j-4) has read it.  Two MMAs are only ordered with respect to each other on the
+        // same accumulator, so that P.V is awaited explicitly.
+        for (int j = warp == 1 ? 0 : 1; ok && j < n_tiles; j += 2) {
+            const int st = j % K_STAGES, sb = j & (S_BUFS - 1);
+            ok = mbar_wait(&B.k_full[st], (j / K_STAGES) & 1, abort_flag, P.status, 2) &&
+                 mbar_wait(&B.p_free[sb], ((j / S_BUFS) & 1) ^ 1, abort_flag, P.status, 2);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) PF_STAMP(j, 0);
             if (elect_one()) {
 #pragma unroll
                 for (int b = 0; b < NDB; b++)
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
-                        umma_ss(tmem + (j & 1) * S_COLS, d_kmaj + (q_lo + b * (TBLK >> 4) + ks * 2),
-                                d_kmaj + (k_lo + b * (TBLK >> 4) + ks * 2), idesc_s, (b | ks) != 0);
-                umma_commit(&B.s_full[j & 1]);
-                umma_commit(&B.k_empty);
+                        umma_ss(tmem + sb * S_COLS, d_kmaj + (q_lo + b * (QBLK >> 4) + ks * 2),
+                                d_kmaj + (k_lo + st * (KV_BYTES >> 4) + b * (KBLK >> 4) + ks * 2), idesc_s, (b | ks) != 0);
+                umma_commit(&B.s_full[sb]);
+                umma_commit(&B.k_empty[st]);
             }
             __syncwarp();
-        };
-        if (ok) ok = mbar_wait(&B.k_full, 0, abort_flag, P.status, 2);
-        if (ok) {
-            tc_fence_after();
-            issue_s(0);
         }
+    } else if (warp == 8) {
+        // ---- P.V MMA issuer: O += P . V ----------------------------------------------------------------------------
+        constexpr uint32_t idesc_pv = make_idesc_f16(BM, HD, 0, 1);  // A = P from tensor memory, B = V MN-major
+        const uint64_t d_v = make_smem_desc(0, KBLK, 1024, kSwizzle128B);
+        const uint32_t v_lo = smem_u32(v_smem) >> 4;
+        bool ok = true;
         for (int j = 0; ok && j < n_tiles; j++) {
-            if (j + 1 < n_tiles) {
-                ok = mbar_wait(&B.k_full, (j + 1) & 1, abort_flag, P.status, 2);
-                // S(j+1) overwrites the tensor-memory columns P(j-1) lives in.  Two MMAs are only ordered with
-                // respect to each other on the same accumulator, so P.V(j-1) must have completed first.
-                if (ok && j > 0) ok = mbar_wait(&B.pv_done, (j - 1) & 1, abort_flag, P.status, 2);
-                if (!ok) break;
-                tc_fence_after();
-                issue_s(j + 1);
-            }
-            ok = mbar_wait(&B.p_full[j & 1], (j >> 1) & 1, abort_flag, P.status, 2) &&
-                 mbar_wait(&B.v_full, j & 1, abort_flag, P.status, 2);
+            const int sb = j & (S_BUFS - 1);
+            ok = mbar_wait(&B.p_full[sb], (j / S_BUFS) & 1, abort_flag, P.status, 2) &&
+                 mbar_wait(&B.v_full[j & 1], (j >> 1) & 1, abort_flag, P.status, 2);
             if (!ok) break;
             tc_fence_after();
+            if (lane == 0) PF_STAMP(j, 1);
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ks++)
-                    umma_ts(tmem + O_COL, tmem + (j & 1) * S_COLS + ks * 8, d_v + (v_lo + ks * 128), idesc_pv, j > 0 || ks > 0);
-                umma_commit(&B.v_empty);
-                umma_commit(&B.pv_done);
+                    umma_ts(tmem + O_COL, tmem + sb * S_COLS + ks * 8, d_v + (v_lo + (j & 1) * (KV_BYTES >> 4) + ks * 128),
+                            idesc_pv, j > 0 || ks > 0);
+                umma_commit(&B.v_empty[j & 1]);
+                umma_commit(&B.p_free[sb]);
             }
             __syncwarp();
         }
@@ -185,10 +218,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_tiles; j++) {
-                const uint32_t s_addr = tmem + lane_base + (j & 1) * S_COLS;
-                ok = mbar_wait(&B.s_full[j & 1], (j >> 1) & 1, abort_flag, P.status, 4);
+                const int sb = j & (S_BUFS - 1);
+                const uint32_t s_addr = tmem + lane_base + sb * S_COLS;
+                ok = mbar_wait(&B.s_full[sb], (j / S_BUFS) & 1, abort_flag, P.status, 4);
                 if (!ok) break;
                 tc_fence_after();
+                if (warp == 2 && lane == 0) PF_STAMP(j, 3);
                 const int k0 = j * BN;
                 const bool need_mask = k0 + BN - 1 > P.p0 + q0;  // some row of the block must not see some key
                 // the whole score row of this thread (128 keys) is read once and kept in registers: one
@@ -197,6 +232,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
 #pragma unroll
                 for (int c = 0; c < BN / 16; c++) tmem_ld16(s_addr + c * 16, *reinterpret_cast<uint32_t(*)[16]>(r + c * 16));
                 tmem_wait_ld();
+                if (warp == 2 && lane == 0) PF_STAMP(j, 4);
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < BN; i++)
@@ -218,8 +254,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
                     const float m_new = grow ? mx : m_run;
                     const float f = m_run == -INFINITY ? 0.f : exp2f(m_run - m_new);
                     if (j > 0) {
-                        // the accumulator holds tiles 0..j-1: wait for P.V(j-1), then scale this row
-                        ok = mbar_wait(&B.pv_done, (j - 1) & 1, abort_flag, P.status, 4);
+                        // the accumulator holds tiles 0..j-1: wait for P.V(j-1), then scale this row.  (Its
+                        // barrier is the one of buffer (j-1) & 3, whose previous phase, P.V(j-5), was over before
+                        // S(j-1) could be issued: the parity cannot be mistaken.)
+                        ok = mbar_wait(&B.p_free[(j - 1) & (S_BUFS - 1)], ((j - 1) / S_BUFS) & 1, abort_flag, P.status, 4);
                         if (!ok) break;
                         tc_fence_after();
 #pragma unroll 1
@@ -237,6 +275,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
                     m_run = m_new;
                 }
                 // probabilities, row sum, P as packed f16 pairs (keys 2i, 2i+1 -> column i of this S buffer)
+                if (warp == 2 && lane == 0) PF_STAMP(j, 5);
                 const float nm = -m_run;
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -248,19 +287,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
                     r[i] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
                 l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                if (warp == 2 && lane == 0) PF_STAMP(j, 6);
 #pragma unroll
                 for (int c = 0; c < BN / 32; c++) tmem_st16(s_addr + c * 16, *reinterpret_cast<const uint32_t(*)[16]>(r + c * 16));
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&B.p_full[j & 1]);
+                if (lane == 0) mbar_arrive(&B.p_full[sb]);
+                if (warp == 2 && lane == 0) PF_STAMP(j, 7);
             }
             // ---- epilogue: O / l -> global ------------------------------------------------------------------------
-            // A parity wait only tells phases apart when the waiter is at most one phase behind.  These warps last
-            // saw P.V(n-3) complete (through S(n-1), which was issued after it), so P.V(n-2) is awaited first:
-            // asking for the parity of P.V(n-1) while P.V(n-2) is still running would return at once.
-            if (ok && n_tiles >= 2) ok = mbar_wait(&B.pv_done, (n_tiles - 2) & 1, abort_flag, P.status, 4);
-            if (ok) ok = mbar_wait(&B.pv_done, (n_tiles - 1) & 1, abort_flag, P.status, 4);
+            // The P.V MMAs come from one thread and share one accumulator, so they complete in order: the last one
+            // done means all done.  Its barrier's previous phase, P.V(n-5), was over before S(n-1) was issued.
+            if (ok) ok = mbar_wait(&B.p_free[(n_tiles - 1) & (S_BUFS - 1)], ((n_tiles - 1) / S_BUFS) & 1, abort_flag, P.status, 4);
             if (ok) {
                 tc_fence_after();
                 const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

@@ -135,4 +135,77 @@ class MlaLayer {
     DeviceBuffer latent_, ws_, q_, kv_, olat_, seq_len_;
 };
 
+// Page-locked host memory the kernels of a replayed step read and write in place.
+class PinnedBuffer {
+  public:
+    explicit PinnedBuffer(size_t len) : len_(len) { check((int) cudaHostAlloc(&ptr_, len ? len : 1, cudaHostAllocMapped), "pinned alloc"); }
+    ~PinnedBuffer() { cudaFreeHost(ptr_); }
+    PinnedBuffer(const PinnedBuffer &) = delete;
+    PinnedBuffer &operator=(const PinnedBuffer &) = delete;
+    void *ptr() const { return ptr_; }
+    size_t len() const { return len_; }
+
+  private:
+    void *ptr_ = nullptr;
+    size_t len_ = 0;
+};
+
+// The same layer with the whole step (stage inputs, append, attend, store the result) recorded once per T as
+// a CUDA graph and replayed: the caller fills q() / kv(), calls mla(t), reads out().  The position is host
+// state, as in the engine; moving it back (forward.rs:1564-1575) needs no device work.
+class MlaLayerGraph {
+  public:
+    MlaLayerGraph(int ctx, int n_head, const Stream &s, int t_max = 2, int d_qk = 576, int d_v = 512, int d_rope = 64)
+        : ctx_(ctx), h_(n_head), t_max_(t_max), d_qk_(d_qk), d_v_(d_v), d_rope_(d_rope), stream_(s),
+          latent_((size_t) ctx * d_qk * 2), ws_((size_t) gs_mla_decode_workspace_bytes(1, t_max, n_head, d_v)),
+          q_dev_((size_t) t_max * n_head * d_qk * 2), seq_len_(sizeof(int32_t)),
+          q_((size_t) t_max * n_head * d_qk * 2), kv_((size_t) t_max * d_qk * 4), out_((size_t) t_max * n_head * d_v * 4) {
+        for (auto &g : graphs_) g = nullptr;
+    }
+    ~MlaLayerGraph() {
+        for (auto g : graphs_) gs_mla_layer_graph_destroy(g);
+    }
+    uint16_t *q() { return (uint16_t *) q_.ptr(); }
+    float *kv() { return (float *) kv_.ptr(); }
+    const float *out() const { return (const float *) out_.ptr(); }
+    int pos() const { return pos_; }
+    void set_pos(int p) { pos_ = p; }
+
+    void mla(int t) {
+        if (t < 1 || t > t_max_ || t > 4) throw std::invalid_argument("t out of range");
+        if (pos_ + t > ctx_) throw std::runtime_error("context full (" + std::to_string(ctx_) + " tokens)");
+        if (!graphs_[t]) {
+            gs_mla_layer_step st{};
+            st.q_host = q_.ptr();
+            st.kv_host = (const float *) kv_.ptr();
+            st.o_host = (float *) out_.ptr();
+            st.q_dev = q_dev_.ptr();
+            st.cache = latent_.ptr();
+            st.cache_rows = ctx_;
+            st.seq_len_dev = (int32_t *) seq_len_.ptr();
+            st.workspace = ws_.ptr();
+            st.workspace_bytes = (int64_t) ws_.len();
+            st.T = t;
+            st.H = h_;
+            st.d_qk = d_qk_;
+            st.d_v = d_v_;
+            st.d_rope = d_rope_;
+            st.rope_base = 10000.0f;
+            st.scale = 1.0f / std::sqrt(256.0f);
+            check((int) cudaDeviceSynchronize(), "device sync");
+            check(gs_mla_layer_graph_create(&st, stream_.raw(), &graphs_[t]), "gs_mla_layer_graph_create");
+        }
+        check(gs_mla_layer_graph_step(graphs_[t], pos_, stream_.raw(), 1), "gs_mla_layer_graph_step");
+        pos_ += t;
+    }
+
+  private:
+    int ctx_, h_, t_max_, d_qk_, d_v_, d_rope_;
+    int pos_ = 0;
+    const Stream &stream_;
+    DeviceBuffer latent_, ws_, q_dev_, seq_len_;
+    PinnedBuffer q_, kv_, out_;
+    gs_mla_layer_graph *graphs_[5];
+};
+
 }  // namespace glmssd

@@ -113,6 +113,47 @@ int main(int argc, char **argv) {
             if (!strstr(e.what(), "context full")) fails++;
         }
     }
+    // the same session through the replayed-graph layer, with one rejected draft in the middle
+    double g_worst = 0;
+    {
+        glmssd::MlaLayerGraph gl(256, H, s);
+        std::vector<uint16_t> cache2((size_t) 256 * d_qk, 0);
+        int p2 = 0;
+        for (int rep = 0; rep < 12; rep++) {
+            const int t = steps[rep % 4];
+            std::vector<float> want((size_t) t * H * d_v);
+            for (size_t i = 0; i < (size_t) t * H * d_qk; i++) gl.q()[i] = oracle_f32_to_f16(rng.normal());
+            for (size_t i = 0; i < (size_t) t * d_qk; i++) gl.kv()[i] = 0.5f * rng.normal();
+            gl.mla(t);
+            oracle_rope_append(gl.kv(), cache2.data() + (size_t) p2 * d_qk, t, d_qk, 64, p2, 10000.0);
+            p2 += t;
+            const int32_t len = p2;
+            oracle_mla_decode(gl.q(), cache2.data(), &len, nullptr, nullptr, 0, 64, 1.0f / 16.0f, want.data(), 1, t, H, d_qk, d_v, 0);
+            double mx = 0;
+            for (size_t i = 0; i < want.size(); i++) {
+                const double e = std::fabs((double) gl.out()[i] - want[i]);
+                mx = e > mx ? e : mx;
+            }
+            if (!(mx <= 4e-3)) {
+                printf("graph step %d (t=%d, pos=%d): max %.3e FAILED\n", rep, t, p2, mx);
+                fails++;
+            }
+            g_worst = mx > g_worst ? mx : g_worst;
+            if (rep == 4) {  // the second token of this two-token step is rejected
+                p2 -= 1;
+                gl.set_pos(p2);
+            }
+        }
+        if (gl.pos() != p2) fails++;
+        gl.set_pos(255);
+        try {
+            gl.mla(2);
+            fails++;
+        } catch (const std::runtime_error &e) {
+            if (!strstr(e.what(), "context full")) fails++;
+        }
+    }
+    printf("graph session: 12 steps, worst max-abs %.3e\n", g_worst);
     printf("host session: 20 steps, worst max-abs %.3e, worst mean-abs %.3e: %s\n", worst, worst_mean, fails ? "FAILED" : "ok");
     return fails ? 1 : 0;
 }
