@@ -469,7 +469,7 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if int(ok.item()) != 1:
                 raise RuntimeError("a rank reported an exchange time-out")
-            exchange = "peer-to-peer stores of the (acc, m, l) records + flags, merged in one kernel (CUDA graph)"
+            exchange = "peer-to-peer stores of the (acc, m, l) records as {value, epoch} words, merged in one kernel (CUDA graph)"
             dist.barrier()
             ex.close()
         except Exception as exc:
