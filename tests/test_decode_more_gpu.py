@@ -1,0 +1,121 @@
+"""More GPU parity cases of the decode path: the largest batch the tcgen05 kernel takes, inputs that
+change between back-to-back calls (the kernel builds its schedule once speculatively, before the inputs
+of the call are final, and must not let anything from that pass reach a result), wider query blocks,
+and the combine for every segment count around its register-resident limit."""
+import numpy as np
+import pytest
+
+from conftest import check_close, check_not_degenerate, make_decode_inputs
+from gpu_util import paged_layout, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def test_batch_of_1024_sequences(pkg, cuda, oracle):
+    rng = np.random.default_rng(31)
+    lens = rng.integers(0, 200, size=1024).astype(np.int32)
+    lens[[3, 500, 1023]] = 0
+    base = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+    q, cache = make_decode_inputs(31, 1024, 1, 20, int(lens.sum()) + 1)
+    for impl in (2, 1):
+        o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, lens), seq_base=to_dev(cuda, base), impl=impl)
+        cuda.cuda.synchronize()
+        got = o.cpu().numpy()
+        check_close(got, oracle.mla_decode(q, cache, lens, 1 / 16, seq_base=base), f"1024 sequences impl={impl}")
+        assert (got[lens == 0] == 0).all()
+    with pytest.raises(Exception):
+        pkg.mla_decode(to_dev(cuda, np.repeat(q, 2, 0)[:1025]), to_dev(cuda, cache), to_dev(cuda, np.zeros(1025, np.int32)), impl=2)
+
+
+@pytest.mark.parametrize("T,H", [(3, 16), (4, 8), (4, 12), (1, 48), (2, 24)])
+def test_wider_query_blocks(pkg, cuda, oracle, T, H):
+    q, cache = make_decode_inputs(40 + T * H, 1, T, H, 1500)
+    o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, np.array([1500], np.int32)), impl=2)
+    cuda.cuda.synchronize()
+    check_close(o.cpu().numpy(), oracle.mla_decode(q, cache, [1500], 1 / 16), f"T={T} H={H}")
+
+
+def test_lengths_and_pages_that_change_between_calls(pkg, cuda, oracle):
+    """Back-to-back launches on one stream, each with lengths / page table rewritten on the device just
+    before it: the speculative schedule of every launch sees the previous call's values."""
+    rng = np.random.default_rng(77)
+    n_seq, H = 6, 20
+    q = rng.standard_normal((n_seq, 1, H, 576), dtype=np.float32).astype(np.float16)
+    cases = []
+    for k in range(5):
+        lens = rng.integers(0, 3000, size=n_seq).astype(np.int32)
+        if k == 2:
+            lens[:] = 0
+        pool, pt = paged_layout(rng, np.maximum(lens, 1), spare_pages=2)
+        cases.append((lens, pool, pt))
+    rows = max(c[1].shape[0] for c in cases)
+    stride = max(c[2].shape[1] for c in cases)
+    pool_d = cuda.zeros((rows, 576), dtype=cuda.float16, device="cuda")
+    pt_d = cuda.zeros((n_seq, stride), dtype=cuda.int32, device="cuda")
+    lens_d = cuda.zeros(n_seq, dtype=cuda.int32, device="cuda")
+    qd = to_dev(cuda, q)
+    ws = pkg.new_workspace(n_seq, 1, H)
+    outs = []
+    staged = []
+    for lens, pool, pt in cases:
+        p = np.zeros((rows, 576), np.float16)
+        p[:pool.shape[0]] = np.nan_to_num(pool, nan=0.0)
+        t = np.zeros((n_seq, stride), np.int32)
+        t[:, :pt.shape[1]] = pt
+        staged.append((to_dev(cuda, lens), to_dev(cuda, p), to_dev(cuda, t), lens, p, t))
+    cuda.cuda.synchronize()
+    for ld, pd, td, *_ in staged:  # no host synchronisation inside this loop
+        lens_d.copy_(ld, non_blocking=True)
+        pool_d.copy_(pd, non_blocking=True)
+        pt_d.copy_(td, non_blocking=True)
+        outs.append(pkg.mla_decode(qd, pool_d, lens_d, page_table=pt_d, workspace=ws, impl=2).clone())
+    cuda.cuda.synchronize()
+    assert pkg.decode_status(ws) == 0
+    for k, (o, (_, _, _, lens, p, t)) in enumerate(zip(outs, staged)):
+        want = oracle.mla_decode(q, p, lens, 1 / 16, page_table=t)
+        check_close(o.cpu().numpy(), want, f"call {k}")
+
+
+def test_dense_length_growing_step_by_step_in_a_graph(pkg, cuda, oracle):
+    """A decode loop: the length word is advanced on the device between replays of one captured call."""
+    n0, steps, H = 700, 6, 20
+    q, cache = make_decode_inputs(55, 1, 1, H, n0 + steps + 3)
+    qd, cd = to_dev(cuda, q), to_dev(cuda, cache)
+    lens_d = cuda.full((1,), n0, dtype=cuda.int32, device="cuda")
+    ws = pkg.new_workspace(1, 1, H)
+    out = cuda.empty((1, 1, H, 512), dtype=cuda.float32, device="cuda")
+    keep = cuda.empty((steps, 1, 1, H, 512), dtype=cuda.float32, device="cuda")
+    pkg.mla_decode(qd, cd, lens_d, workspace=ws, out=out, impl=2)
+    cuda.cuda.synchronize()
+    s = cuda.cuda.Stream()
+    g = cuda.cuda.CUDAGraph()
+    with cuda.cuda.stream(s):
+        with cuda.cuda.graph(g, stream=s):
+            pkg.mla_decode(qd, cd, lens_d, workspace=ws, out=out, impl=2)
+            lens_d.add_(1)
+        for k in range(steps):
+            g.replay()
+            keep[k].copy_(out, non_blocking=True)
+    cuda.cuda.synchronize()
+    for k in range(steps):
+        check_close(keep[k].cpu().numpy(), oracle.mla_decode(q, cache, [n0 + k], 1 / 16), f"replay {k}")
+
+
+@pytest.mark.parametrize("n_parts", [1, 2, 8, 159, 160, 161, 300, 1024])
+def test_combine_parts_segment_counts(pkg, cuda, oracle, n_parts):
+    rng = np.random.default_rng(n_parts)
+    rows, d_v = 8, 512
+    acc = rng.standard_normal((n_parts, rows, d_v), dtype=np.float32)
+    m = rng.standard_normal((n_parts, rows), dtype=np.float32) * 3
+    l = rng.random((n_parts, rows), dtype=np.float32) + 0.1
+    if n_parts > 2:
+        m[1] = -np.inf          # an empty segment: its accumulator (NaN here) must not enter the sum
+        l[1] = 0
+        acc[1] = np.nan
+    blocks = np.concatenate([acc.reshape(n_parts, -1), np.stack([m, l], -1).reshape(n_parts, -1)], 1)
+    got = pkg.combine_parts(to_dev(cuda, blocks.reshape(-1)), n_parts, rows, d_v)
+    cuda.cuda.synchronize()
+    recs = np.concatenate([acc, m[..., None], l[..., None]], -1).transpose(1, 0, 2)  # [rows][parts][d_v + 2]
+    recs = np.nan_to_num(recs, nan=0.0, neginf=-np.inf)
+    want = oracle.combine(np.ascontiguousarray(recs))
+    check_close(got.cpu().numpy(), want, f"combine of {n_parts} parts", 1e-4, 1e-5)
