@@ -202,7 +202,7 @@ def reference_cuda_twin():
         torch.cuda.set_device(0)
         out = {}
         for name, n, T, Hh, splits in (("ctx32k_T2_H32", 32768, 2, 32, 4), ("ctx32k_T1_H32", 32768, 1, 32, 16),
-                                       ("ctx128k_T1_H32", 131072, 1, 32, 16)):
+                                       ("ctx128k_T1_H32", 131072, 1, 32, 16), ("ctx32k_T1_H64", 32768, 1, 64, 16)):
             n_copies = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
             caches = [(torch.randn((n, 512), device=dev) * 0.5).half() for _ in range(n_copies)]
             q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
@@ -534,17 +534,17 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     del pool
     torch.cuda.empty_cache()
 
-    # -- twin shapes of the reference kernel (R = 512, H = 32), for a like-for-like ratio --------------
+    # -- twin shapes of the reference kernel (R = 512, H = 32 or 64), for a like-for-like ratio --------
+    # (more than 48 packed query rows run as head groups, one pass over the cache per group)
     twin = {}
-    for name, n, T in (("ctx32k_T2_H32", 32768, 2), ("ctx32k_T1_H32", 32768, 1), ("ctx128k_T1_H32", 131072, 1)):
-        if T * 32 > 48:
-            continue  # 64 packed query rows: outside the tcgen05 kernel's 48-row limit
+    for name, n, T, Ht in (("ctx32k_T2_H32", 32768, 2, 32), ("ctx32k_T1_H32", 32768, 1, 32),
+                           ("ctx128k_T1_H32", 131072, 1, 32), ("ctx32k_T1_H64", 32768, 1, 64)):
         nc = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
         cs = [randn_f16((n, 512), 0.5) for _ in range(nc)]
-        qt = randn_f16((1, T, 32, 512))
+        qt = randn_f16((1, T, Ht, 512))
         lt = torch.tensor([n], dtype=torch.int32, device=dev)
-        ot = torch.empty((1, T, 32, 512), dtype=torch.float32, device=dev)
-        wt = pkg.new_workspace(1, T, 32, 512, dev)
+        ot = torch.empty((1, T, Ht, 512), dtype=torch.float32, device=dev)
+        wt = pkg.new_workspace(1, T, Ht, 512, dev)
         sec = time_loop(lambda i: pkg.mla_decode(qt, cs[i % nc], lt, out=ot, workspace=wt, max_seq_len=n), steps, warm,
                         period=nc)
         twin[name] = {"us_per_call": sec * 1e6, "GB/s": n * 1024 / sec / 1e9}

@@ -209,17 +209,20 @@ __device__ __forceinline__ void combine_item(const CombinePlan &C, const SegRang
     float M, L;
     int col;
     if (combine_item_compute(C, R, col0, S, a, M, L, col)) {
+        // the records may cover a group of the output's heads: row (b, t, h) of the group is row (b, t, h0 + h) there
+        const int H_out = C.H_out > 0 ? C.H_out : C.H;
+        const int64_t orow = (int64_t) (row / C.H) * H_out + C.h0 + row % C.H;
         if (C.part_out) {
-            const int64_t rows_total = (int64_t) C.n_seq * C.T * C.H;
-            *reinterpret_cast<float4 *>(C.part_out + (int64_t) row * C.d_v + col) = a;
+            const int64_t rows_total = (int64_t) C.n_seq * C.T * H_out;
+            *reinterpret_cast<float4 *>(C.part_out + orow * C.d_v + col) = a;
             if (col == 0) {
-                C.part_out[rows_total * C.d_v + (int64_t) row * 2] = M;
-                C.part_out[rows_total * C.d_v + (int64_t) row * 2 + 1] = L;
+                C.part_out[rows_total * C.d_v + orow * 2] = M;
+                C.part_out[rows_total * C.d_v + orow * 2 + 1] = L;
             }
         }
         if (C.o) {
             const float inv = L > 0.f ? 1.f / L : 0.f;
-            *reinterpret_cast<float4 *>(C.o + (int64_t) row * C.d_v + col) =
+            *reinterpret_cast<float4 *>(C.o + orow * C.d_v + col) =
                 make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         }
     }

@@ -105,7 +105,8 @@ struct UmmaParams {
     float *ws_acc, *ws_ml;
     int2 *ws_desc;
     int32_t *status;
-    int n_seq, T, H, rows_q, d_v;
+    int n_seq, T, H, rows_q, d_v;  // H: heads handled by this launch (a group of the H_full heads of q)
+    int H_full, h0;                // q holds H_full heads per token; this launch takes heads h0 .. h0+H-1
     int64_t cache_rows;
 };
 
@@ -394,10 +395,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
                     if (!ok) break;
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * NQ * 128));
+                        if (P.H_full == P.H) {  // the sequence's T*H query rows are contiguous: one box per block
+                            mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * NQ * 128));
 #pragma unroll
-                        for (int k = 0; k < NBLK; k++)
-                            tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
+                            for (int k = 0; k < NBLK; k++)
+                                tma_load_2d(q_smem + k * NQ * 128, &P.tm_q, &B.q_full, k * 64, sg.b * P.rows_q);
+                        } else {  // a head group: H rows per token (H % 8 == 0, so every box starts on a swizzle atom)
+                            mbar_arrive_expect_tx(&B.q_full, (uint32_t) (NBLK * P.rows_q * 128));
+                            for (int t = 0; t < P.T; t++) {
+#pragma unroll
+                                for (int k = 0; k < NBLK; k++)
+                                    tma_load_2d(q_smem + k * NQ * 128 + t * P.H * 128, &P.tm_q, &B.q_full, k * 64,
+                                                (sg.b * P.T + t) * P.H_full + P.h0);
+                            }
+                        }
                     }
                 }
                 __syncwarp();
@@ -773,7 +784,11 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
     if (p.q_is_f32) { *why = "f32 queries"; return false; }
     if (p.sel) { *why = "explicit position lists"; return false; }
     if (!((p.d_qk == 576 || p.d_qk == 512) && p.d_v == 512)) { *why = "row widths other than 576/512 or 512/512"; return false; }
-    if (p.T * p.H > 48) { *why = "more than 48 query rows per sequence"; return false; }
+    if (p.T * p.H > 48) {
+        // wider blocks run as head groups of at most 48 rows, one launch each (the cache is read once per group)
+        if (p.T > 4 || p.H % 8 != 0) { *why = "more than 48 query rows per sequence with T > 4 or H % 8 != 0"; return false; }
+        if (p.exchange) { *why = "more than 48 query rows per sequence together with a cross-GPU exchange"; return false; }
+    }
     if (!(p.scale > 0.f)) { *why = "non-positive softmax scale"; return false; }
     if (p.n_seq > MAX_SEQ) { *why = "more than 1024 sequences"; return false; }
     if (p.page_table && p.page_rows != TILE) { *why = "page size other than 64"; return false; }
@@ -783,8 +798,13 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
 }
 
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
-    const int rows_q = p.T * p.H;
-    const int NQ = rows_q <= 32 ? 32 : 48;
+    // Head groups: up to 48 query rows (T tokens x Hg heads) ride on the N side of one launch.
+    int Hg = p.H, n_groups = 1;
+    if (p.T * p.H > 48) {
+        const int hg_max = (48 / p.T) & ~7;          // a multiple of 8 heads
+        n_groups = (p.H + hg_max - 1) / hg_max;
+        Hg = (((p.H + n_groups - 1) / n_groups) + 7) & ~7;  // balanced, rounded up to 8
+    }
     UmmaParams P;
     memset(&P, 0, sizeof(P));
     const int kSw128 = (int) CU_TENSOR_MAP_SWIZZLE_128B;
@@ -792,8 +812,6 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
                                    TILE, 64, kSw128)) return e;
     if (int e = encode_tmap_2d_f16(&P.tm_kv16, p.cache, (uint64_t) p.cache_rows, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
                                    16, 64, kSw128)) return e;
-    if (int e = encode_tmap_2d_f16(&P.tm_q, p.q, (uint64_t) p.n_seq * rows_q, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
-                                   (uint32_t) NQ, 64, kSw128)) return e;
     P.seq_lens = p.seq_lens;
     P.seq_base = p.seq_base;
     P.page_table = p.page_table;
@@ -807,38 +825,53 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.status = p.status;
     P.n_seq = p.n_seq;
     P.T = p.T;
-    P.H = p.H;
-    P.rows_q = rows_q;
+    P.H_full = p.H;
     P.d_v = p.d_v;
     P.cache_rows = p.cache_rows;
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
-    CombinePlan c{};
-    c.acc = p.ws_acc;
-    c.ml = p.ws_ml;
-    c.desc = p.ws_desc;
-    c.regular_segments = 0;
-    c.seg_stride_acc = (int64_t) rows_q * p.d_v;
-    c.seg_stride_ml = (int64_t) rows_q * 2;
-    c.n_seq = p.n_seq;
-    c.T = p.T;
-    c.H = p.H;
-    c.d_v = p.d_v;
-    c.o = p.o;
-    c.part_out = p.part_out;
-    c.status = p.status;
-    c.seq_lens = p.seq_lens;
-    c.unit_rows = P.paged ? TILE : 16;
-    c.n_ctas = grid;
-    int e;
-    if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
-    else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
-    if (e) return e;
-    if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
-    if (p.no_combine) return 0;
-    if (p.exchange) return launch_exchange_combine(c, *p.exchange, p.o, p.status, p.sm_count, st);
-    return launch_combine(c, st);
+    for (int g = 0; g < n_groups; g++) {
+        const int h0 = g * Hg;
+        const int hg = p.H - h0 < Hg ? p.H - h0 : Hg;
+        if (hg <= 0) break;
+        const int rows_q = p.T * hg;
+        const int NQ = rows_q <= 32 ? 32 : 48;
+        // one box of NQ rows when the rows of a sequence are contiguous, else one box of hg rows per token
+        if (int e = encode_tmap_2d_f16(&P.tm_q, p.q, (uint64_t) p.n_seq * p.T * p.H, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
+                                       (uint32_t) (n_groups == 1 ? NQ : hg), 64, kSw128)) return e;
+        P.H = hg;
+        P.h0 = h0;
+        P.rows_q = rows_q;
+        CombinePlan c{};
+        c.acc = p.ws_acc;
+        c.ml = p.ws_ml;
+        c.desc = p.ws_desc;
+        c.regular_segments = 0;
+        c.seg_stride_acc = (int64_t) rows_q * p.d_v;
+        c.seg_stride_ml = (int64_t) rows_q * 2;
+        c.n_seq = p.n_seq;
+        c.T = p.T;
+        c.H = hg;
+        c.H_out = p.H;
+        c.h0 = h0;
+        c.d_v = p.d_v;
+        c.o = p.o;
+        c.part_out = p.part_out;
+        c.status = p.status;
+        c.seq_lens = p.seq_lens;
+        c.unit_rows = P.paged ? TILE : 16;
+        c.n_ctas = grid;
+        int e;
+        if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
+        else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
+        if (e) return e;
+        if (p.ev_after_main && g == n_groups - 1) GS_TRY(cudaEventRecord(p.ev_after_main, st));
+        if (p.no_combine) continue;
+        if (p.exchange) return launch_exchange_combine(c, *p.exchange, p.o, p.status, p.sm_count, st);
+        if (int ce = launch_combine(c, st)) return ce;
+    }
+    return 0;
 }
 
 }  // namespace gs

@@ -44,7 +44,8 @@ struct CombinePlan {
     int regular_segments;  // desc == nullptr: segments per (sequence, token) group, consecutive
     int64_t seg_stride_acc;  // floats between the accumulator blocks of consecutive segments
     int64_t seg_stride_ml;   // floats between the (m, l) blocks of consecutive segments
-    int n_seq, T, H, d_v;
+    int n_seq, T, H, d_v;  // H: heads in the records being merged
+    int H_out, h0;         // the output has H_out heads per token and these are heads h0 .. h0+H-1 (0, 0: H_out = H)
     float *o;              // may be nullptr
     float *part_out;       // may be nullptr
     const int32_t *status; // workspace status block (stamps switch at word 1) or nullptr

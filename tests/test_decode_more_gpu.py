@@ -119,3 +119,36 @@ def test_combine_parts_segment_counts(pkg, cuda, oracle, n_parts):
     recs = np.nan_to_num(recs, nan=0.0, neginf=-np.inf)
     want = oracle.combine(np.ascontiguousarray(recs))
     check_close(got.cpu().numpy(), want, f"combine of {n_parts} parts", 1e-4, 1e-5)
+
+
+@pytest.mark.parametrize("T,H", [(1, 64), (2, 64), (2, 48), (2, 32), (3, 32), (4, 16), (1, 56)])
+def test_head_groups_beyond_48_query_rows(pkg, cuda, oracle, T, H):
+    """The reference's models have up to 64 heads (validate.rs:52-54): blocks of more than 48 query rows run on the
+    tcgen05 kernel as head groups, one launch per group, and must land in the right rows of the output."""
+    rng = np.random.default_rng(T * 100 + H)
+    lens = np.array([900, 0, 65, 2100], np.int32)
+    pool, pt = paged_layout(rng, lens)
+    q = rng.standard_normal((len(lens), T, H, 576), dtype=np.float32).astype(np.float16)
+    o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, pool), to_dev(cuda, lens), page_table=to_dev(cuda, pt), impl=2)
+    cuda.cuda.synchronize()
+    got = o.cpu().numpy()
+    check_close(got, oracle.mla_decode(q, pool, lens, 1 / 16, page_table=pt), f"T={T} H={H} paged")
+    check_not_degenerate(got[0], "head groups")
+    # dense single sequence, and the merged records instead of the normalised output
+    q1, cache = make_decode_inputs(T + H, 1, T, H, 3000)
+    part = cuda.zeros(pkg.part_floats(T * H), dtype=cuda.float32, device="cuda")
+    o1 = pkg.mla_decode(to_dev(cuda, q1), to_dev(cuda, cache), to_dev(cuda, np.array([3000], np.int32)), impl=2, part_out=part)
+    cuda.cuda.synchronize()
+    want = oracle.mla_decode(q1, cache, [3000], 1 / 16)
+    check_close(o1.cpu().numpy(), want, f"T={T} H={H} dense")
+    pr = part.cpu().numpy()
+    acc, ml = pr[:T * H * 512].reshape(T * H, 512), pr[T * H * 512:].reshape(T * H, 2)
+    check_close((acc / ml[:, 1:2]).reshape(1, T, H, 512), want, "records of the head groups")
+
+
+def test_reference_twin_shape_64_heads_runs_on_the_tensor_core_kernel(pkg, cuda, oracle):
+    # R = 512 rows (V = all columns), 64 heads: the shape of the reference's own models
+    q, cache = make_decode_inputs(64, 1, 1, 64, 4096, d_qk=512)
+    o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, np.array([4096], np.int32)), impl=2, d_v=512)
+    cuda.cuda.synchronize()
+    check_close(o.cpu().numpy(), oracle.mla_decode(q, cache, [4096], 1 / 16, d_v=512), "R=512 H=64")
