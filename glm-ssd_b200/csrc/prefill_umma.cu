@@ -17,8 +17,9 @@
 // to land (128-key tiles in single buffers left the tensor pipe waiting for every load).  Three warps issue
 // MMAs (scores of even tiles, scores of odd tiles, P.V): a single thread issues one MMA per ~65 cycles whatever
 // its size, which for 20 MMAs per 64-key tile is more than the tensor time.  What bounds the steady state now is
-// the tensor pipe itself: an N = 64 MMA occupies it for ~45 cycles (33 at full rate), so a tile takes
-// 16 x 45 + 4 x 131 = 1244 cycles (measured 1240) against 1049 at peak.
+// the tensor pipe itself: an M = 128, N = 64 MMA with both operands in shared memory occupies it for ~49
+// cycles (it is bound by reading (M + N) x 32 operand bytes, not by the math, which would take 32), so a
+// tile takes about 16 x 49 + 4 x 129 = 1300 cycles (measured 1240) against 1049 at peak.
 // The accumulator is rescaled lazily (only when a row maximum grows by more than 2^8), decided per warp.
 // Every mbarrier wait is bounded and ends in an error status instead of a hang.
 #include <string.h>
