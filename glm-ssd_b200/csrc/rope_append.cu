@@ -113,6 +113,12 @@ constexpr int STAGE_PAIRS = 3;   // column pairs per thread: rows of up to 768 v
 __global__ void __launch_bounds__(128) k_stage_append(const AppendParams P, volatile int64_t *host_words, int32_t *len_dev,
                                                       int64_t cache_rows, int32_t *status, const uint4 *q_src, uint4 *q_dst,
                                                       int q_words) {
+#if __CUDA_ARCH__ >= 900
+    // Let the attention kernel behind this one be scheduled right away: while this kernel waits for its reads
+    // over PCIe, that one sets itself up and asks the first cache tiles of its range into L2; its own dependency
+    // wait still covers everything written here.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
     if (blockIdx.x > 0) {
         const int nb = gridDim.x - 1;
         for (int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < q_words; i += nb * blockDim.x) q_dst[i] = q_src[i];
