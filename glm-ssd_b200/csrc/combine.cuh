@@ -20,7 +20,7 @@ static_assert(CB_COLS / 4 == 32 && CB_REG_SEG <= 32, "a warp is one segment lane
 struct CombineSmem {
     float m[CB_MAX_SEG], l[CB_MAX_SEG];  // only the path for more than 160 segments
     float red[CB_NT / 32], lred[CB_NT / 32];
-    int ired[2][CB_NT / 32];
+    long long lred2[2][CB_NT / 32];
     float M, L;
     float4 part[CB_LANES][CB_COLS / 4];
 };
@@ -56,9 +56,16 @@ __device__ __forceinline__ SegRange combine_locate(const CombinePlan &C, int row
         return r;
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int before = 0, total = 0;
+    // The attention kernel caps every length at what the cache can hold and lets its running sum of units
+    // saturate at 2^29; capped non-negative terms make that sum min(plain sum, 2^29), recomputed here in 64 bits.
+    constexpr long long kUnitCap = 1ll << 29;
+    auto units_of = [&](int i) -> long long {
+        const long long len = min((long long) max(__ldg(C.seq_lens + i), 0), (long long) C.len_cap);
+        return (len + C.unit_rows - 1) / C.unit_rows;
+    };
+    long long before = 0, total = 0;
     for (int i = tid; i < C.n_seq; i += CB_NT) {
-        const int u = (max(__ldg(C.seq_lens + i), 0) + C.unit_rows - 1) / C.unit_rows;
+        const long long u = units_of(i);
         total += u;
         if (i < b) before += u;
     }
@@ -68,24 +75,28 @@ __device__ __forceinline__ SegRange combine_locate(const CombinePlan &C, int row
         before += __shfl_xor_sync(0xffffffffu, before, o);
     }
     if (lane == 0) {
-        S.ired[0][warp] = total;
-        S.ired[1][warp] = before;
+        S.lred2[0][warp] = total;
+        S.lred2[1][warp] = before;
     }
     __syncthreads();
     total = before = 0;
 #pragma unroll
     for (int w = 0; w < CB_NT / 32; w++) {
-        total += S.ired[0][w];
-        before += S.ired[1][w];
+        total += S.lred2[0][w];
+        before += S.lred2[1][w];
     }
-    const int mine = (max(__ldg(C.seq_lens + b), 0) + C.unit_rows - 1) / C.unit_rows;
-    const int chunk = max(1, (total + C.n_ctas - 1) / C.n_ctas);
+    const long long mine = units_of(b);
+    const long long after = min(before + mine, kUnitCap);  // saturated running sums, as the kernel holds them
+    before = min(before, kUnitCap);
+    total = min(total, kUnitCap);
+    const long long chunk = max(1ll, (total + C.n_ctas - 1) / C.n_ctas);
     r.first = b;
     r.nseg = 0;
-    if (mine > 0) {
-        const int c_first = before / chunk, c_last = (before + mine - 1) / chunk;
-        r.first = c_first + b;
-        r.nseg = c_last - c_first + 1;
+    if (after > before) {
+        const long long c_first = before / chunk, c_last = (after - 1) / chunk;
+        // CTA indices are below n_ctas by construction; the clamp only keeps absurd inputs inside the workspace
+        r.first = (int) min(c_first, (long long) C.n_ctas - 1) + b;
+        r.nseg = (int) min(c_last - c_first + 1, (long long) C.n_ctas - min(c_first, (long long) C.n_ctas - 1));
     }
     return r;
 }

@@ -87,6 +87,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int O_SLOT0 = 2 * N_MMA_WARPS;
 constexpr int NVT = 4;                   // 128-column value tiles (d_v = 512)
 constexpr int MAX_SEQ = 1024;
+constexpr int UNIT_CAP = 1 << 29;         // the running sum of units saturates here (two such values still add in an int)
 constexpr float RESCALE_LOG2 = 6.0f;     // lazy rescale threshold, in log2 units
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -270,11 +271,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         {
             // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
             const uint64_t pol_keep = l2_policy_evict_last();
+            // A length is taken as at most what the cache (or the sequence's row of the page table) can hold,
+            // and the running sum below saturates: whatever the arrays contain - they are read once before they
+            // are final - the schedule stays monotone and every index derived from it stays in range.
+            const int64_t len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
             for (int b = tid; b < P.n_seq; b += NTHREADS) {
-                const int len = max(ld_global_hint(P.seq_lens + b, pol_keep), 0);
+                const int len = (int) min((int64_t) max(ld_global_hint(P.seq_lens + b, pol_keep), 0), len_cap);
                 M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b, pol_keep) : 0;
                 M.len[b] = len;
-                M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;
+                M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;  // < 2^27
             }
         }
         tc_fence_before();
@@ -287,9 +292,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const int u = __shfl_up_sync(0xffffffffu, v, o);
-                    if (lane >= o) v += u;
+                    if (lane >= o) v = min(v + u, UNIT_CAP);
                 }
-                v += carry;
+                v = min(v + carry, UNIT_CAP);
                 if (i <= P.n_seq) M.cum[i] = v;
                 carry = __shfl_sync(0xffffffffu, v, 31);
             }
@@ -322,7 +327,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int row = s2.r0 + j * TILE;
                 int64_t grow = -1;
                 if (!P.paged) grow = (int64_t) M.base[s2.b] + row;
-                else if (row / TILE < P.page_table_stride)
+                else if (row >= 0 && row / TILE < P.page_table_stride)
                     grow = (int64_t) P.page_table[(int64_t) s2.b * P.page_table_stride + row / TILE] * TILE;
                 if (grow >= 0 && grow < P.cache_rows && elect_one()) {
 #pragma unroll
@@ -371,7 +376,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
                 if (P.paged || valid == TILE) {
-                    const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride + row / TILE] * TILE
+                    const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride +
+                                                            min(max(row / TILE, 0), P.page_table_stride - 1)] * TILE
                                              : (int) (base_row + row);
                     if (elect_one()) {
                         mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (NBLK * BLK_BYTES));
@@ -862,6 +868,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.seq_lens = p.seq_lens;
         c.unit_rows = P.paged ? TILE : 16;
         c.n_ctas = grid;
+        c.len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
         int e;
         if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
         else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);

@@ -53,6 +53,7 @@ struct CombinePlan {
     // (unit_rows rows per unit, units dealt in equal chunks to n_ctas CTAs) instead of being read from desc
     const int32_t *seq_lens;
     int unit_rows, n_ctas;
+    int64_t len_cap;       // a length counts as at most this many rows, exactly as in the attention kernel
 };
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);

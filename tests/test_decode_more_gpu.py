@@ -152,3 +152,19 @@ def test_reference_twin_shape_64_heads_runs_on_the_tensor_core_kernel(pkg, cuda,
     o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, np.array([4096], np.int32)), impl=2, d_v=512)
     cuda.cuda.synchronize()
     check_close(o.cpu().numpy(), oracle.mla_decode(q, cache, [4096], 1 / 16, d_v=512), "R=512 H=64")
+
+
+@pytest.mark.parametrize("T", [1, 2])
+def test_length_beyond_the_cache_is_taken_as_the_cache_size(pkg, cuda, oracle, T):
+    """Input hardening: a length word larger than the cache allocation (or negative) must not be followed past the
+    cache.  The tcgen05 kernel takes it as cache_rows (or 0)."""
+    q, cache = make_decode_inputs(90 + T, 3, T, 20, 3 * 500)
+    base = np.array([0, 500, 1000], np.int32)
+    lens = np.array([2**31 - 1, -5, 400], np.int32)
+    o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, lens), seq_base=to_dev(cuda, base), impl=2)
+    cuda.cuda.synchronize()
+    got = o.cpu().numpy()
+    # sequence 0: base 0, length clamped to the 1500 rows of the allocation; sequence 1: empty
+    want = oracle.mla_decode(q, cache, np.array([1500, 0, 400], np.int32), 1 / 16, seq_base=base)
+    check_close(got, want, "clamped lengths")
+    assert (got[1] == 0).all()
