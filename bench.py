@@ -230,9 +230,42 @@ def reference_cuda_twin():
             us = e0.elapsed_time(e1) * 1e3 / reps
             out[name] = {"us_per_call": us, "GB/s": n * 1024 / us / 1e3, "splits": splits}
             del caches
+        out.update(_sparse_list_shape(torch, dev, ref.gs_mla_attn, "reference_kernel"))
         return out
     except Exception as exc:
         return {"error": f"{type(exc).__name__}: {exc}"}
+
+
+def _sparse_list_shape(torch, dev, fn, label, scratch=None):
+    """The engine's own decode shape: 64 heads, f32 queries, a sparse list of 2052 positions per query token
+    out of a 32768-row cache (forward.rs:461, :873), through the reference's entry point gs_mla_attn."""
+    res = {}
+    ctx, n, Hh = 32768, 2052, 64
+    caches = [(torch.randn((ctx, 512), device=dev) * 0.5).half() for _ in range(6)]
+    st = torch.cuda.current_stream().cuda_stream
+    for T, splits in ((1, 16), (2, 4)):
+        q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
+        sel = torch.stack([torch.randperm(ctx, device=dev)[:n].sort().values for _ in range(T)]).int().contiguous()
+        cnt = torch.full((T,), n, dtype=torch.int32, device=dev)
+        o = torch.empty((T, Hh, 512), dtype=torch.float32, device=dev)
+        part = torch.empty(T * Hh * splits * 514 + 1024, dtype=torch.float32, device=dev)
+
+        def call(i):
+            rc = fn(q.data_ptr(), caches[i % 6].data_ptr(), None, sel.data_ptr(), n, cnt.data_ptr(), SCALE, o.data_ptr(),
+                    part.data_ptr(), T, Hh, 512, splits, st)
+            assert rc == 0, rc
+
+        for i in range(3):
+            call(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(30):
+            call(i)
+        e1.record()
+        torch.cuda.synchronize()
+        res[f"sparse2052_T{T}_H64_{label}"] = {"us_per_call": e0.elapsed_time(e1) * 1e3 / 30, "splits": splits}
+    return res
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -552,6 +585,22 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
         del cs
         torch.cuda.empty_cache()
     res["twin_R512"] = twin
+
+    # -- the engine's sparse decode shape through gs_mla_attn: CUDA-core kernel, then the tensor-core path -----
+    try:
+        fn = pkg._lib.load().gs_mla_attn
+        sp = _sparse_list_shape(torch, dev, fn, "cuda_core")
+        scratch = pkg.mla_attn_scratch(4, 64, 2060, dev)
+        try:
+            sp.update(_sparse_list_shape(torch, dev, fn, "tensor_path"))
+            torch.cuda.synchronize()
+        finally:
+            pkg.mla_attn_scratch_off()
+        del scratch
+        res["gs_mla_attn_sparse"] = sp
+    except Exception as exc:
+        res["gs_mla_attn_sparse"] = {"error": f"{type(exc).__name__}: {exc}"}
+    torch.cuda.empty_cache()
 
     # -- causal prefill, 8192 tokens, 20 heads, d = 256 (replicas only; measured on every rank) -------
     S, d = 8192, 256

@@ -43,6 +43,8 @@ SIGNATURES = {
     "gs_mla_attn": (i32, [vp, vp, vp, vp, i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]),
     "gs_f32_to_f16": (i32, [vp, vp, i64, vp]),
     "gs_quant_q8_rows": (i32, [vp, vp, vp, i64, vp]),
+    "gs_mla_attn_scratch_bytes": (i64, [i32, i32, i32]),
+    "gs_mla_attn_set_scratch": (i32, [vp, i64, i32, i32, i32, vp]),
     "gs_mla_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
     "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_decode_static": (i32, [C.POINTER(DecodeArgs), vp]),

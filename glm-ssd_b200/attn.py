@@ -45,6 +45,22 @@ def mla_attn(q, C_latent, C_scales, sel, sel_stride, cnt, scale, o, part, T, H, 
                              _ptr(o), _ptr(part), T, H, R, splits, _stream()), "gs_mla_attn")
 
 
+def mla_attn_scratch(t_max: int, H: int, max_rows: int, device=None):
+    """Allocates and registers the scratch that switches ``gs_mla_attn`` to its tensor-core path on the current
+    device; returns the tensor (keep it alive).  ``mla_attn_scratch_off()`` unregisters."""
+    L = _lib.load()
+    n = int(L.gs_mla_attn_scratch_bytes(t_max, H, max_rows))
+    if n <= 0:
+        raise ValueError("t_max must be 1..4, H and max_rows positive")
+    buf = torch.zeros(n, dtype=torch.uint8, device=device or torch.cuda.current_device())
+    _lib.check(L.gs_mla_attn_set_scratch(buf.data_ptr(), n, t_max, H, max_rows, _stream()), "gs_mla_attn_set_scratch")
+    return buf
+
+
+def mla_attn_scratch_off():
+    _lib.check(_lib.load().gs_mla_attn_set_scratch(None, 0, 0, 0, 0, _stream()), "gs_mla_attn_set_scratch")
+
+
 def f32_to_f16(x, y, n):
     """``gs_f32_to_f16`` (crates/cuda/src/lib.rs:123): the reference's KV-append."""
     _lib.check(_lib.load().gs_f32_to_f16(_ptr(x), _ptr(y), n, _stream()), "gs_f32_to_f16")

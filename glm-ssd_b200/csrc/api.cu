@@ -116,6 +116,51 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
     return launch_decode_simt(p, (cudaStream_t) stream);
 }
 
+// ---- optional tensor-core path of the reference-compatible entry point ------------------------------------
+// Scratch registered by the caller, per device: [workspace of a decode with n_seq = T_max, T = 1][lens T_max]
+// [bases T_max][queries f16 T_max*H*512][rows T_max*max_rows*512 f16].
+struct AttnScratch {
+    void *ptr;
+    int64_t bytes;
+    int t_max, h, max_rows;
+};
+static AttnScratch g_attn_scratch[64] = {};
+static constexpr int kAttnTensorTmax = 4;
+
+static int64_t attn_scratch_layout(int t_max, int H, int max_rows, int64_t *off_lens, int64_t *off_q, int64_t *off_rows) {
+    const int64_t ws = ws_layout(t_max, 1, H, 512).total;
+    const int64_t lens = ws, q16 = align_up(lens + 2 * (int64_t) t_max * 4, 256);
+    const int64_t rows = align_up(q16 + (int64_t) t_max * H * 512 * 2, 256);
+    if (off_lens) *off_lens = lens;
+    if (off_q) *off_q = q16;
+    if (off_rows) *off_rows = rows;
+    return align_up(rows + (int64_t) t_max * max_rows * 512 * 2, 256);
+}
+
+GS_EXPORT int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows) {
+    if (t_max <= 0 || t_max > kAttnTensorTmax || H <= 0 || max_rows <= 0) return 0;
+    return attn_scratch_layout(t_max, H, max_rows, nullptr, nullptr, nullptr);
+}
+
+GS_EXPORT int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream) {
+    int dev = 0;
+    GS_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail_invalid("gs_mla_attn_set_scratch: device index beyond 63");
+    if (!scratch) {
+        g_attn_scratch[dev] = AttnScratch{};
+        return 0;
+    }
+    const int64_t need = gs_mla_attn_scratch_bytes(t_max, H, max_rows);
+    if (need <= 0 || bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
+        set_error("gs_mla_attn_set_scratch: need %lld bytes, 256-byte aligned, 1 <= t_max <= %d (given %lld)", (long long) need,
+                  kAttnTensorTmax, (long long) bytes);
+        return (int) cudaErrorInvalidValue;
+    }
+    GS_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes, (cudaStream_t) stream));  // sticky status block starts clean
+    g_attn_scratch[dev] = AttnScratch{scratch, bytes, t_max, H, max_rows};
+    return 0;
+}
+
 GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride,
                           const int *cnt, float scale, float *o, float *part, int T, int H, int R, int splits,
                           void *stream) {
@@ -126,6 +171,53 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
     if (splits == 1 && !part) return fail_invalid("gs_mla_attn: this implementation needs `part` (T*H*(R+2) floats) also for splits == 1");
     DecodeProblem p{};
+    if (int e = device_sm_count(&p.sm_count)) return e;
+    // Tensor-core path, only when the caller registered a scratch for this device: the listed rows of every query
+    // token are gathered into contiguous rows and the queries rounded to f16, then each token is one dense
+    // "sequence" of the tcgen05 kernel.  (A decode or MTP-verify call: few tokens, a few thousand rows each.)
+    int dev = 0;
+    GS_TRY(cudaGetDevice(&dev));
+    const AttnScratch sc = (dev >= 0 && dev < 64) ? g_attn_scratch[dev] : AttnScratch{};
+    if (sc.ptr && !C_scales && T <= sc.t_max && H == sc.h && sel_stride > 0 && sel_stride <= sc.max_rows && scale > 0.f &&
+        !(reinterpret_cast<uintptr_t>(C) & 15)) {
+        int64_t off_lens, off_q, off_rows;
+        attn_scratch_layout(sc.t_max, sc.h, sc.max_rows, &off_lens, &off_q, &off_rows);
+        char *base = (char *) sc.ptr;
+        int32_t *lens = (int32_t *) (base + off_lens), *bases = lens + sc.t_max;
+        __half *q16 = (__half *) (base + off_q), *rows = (__half *) (base + off_rows);
+        if (int e = launch_gather_rows((const __half *) C, sel, sel_stride, cnt, T, sc.max_rows, R, rows, lens, bases, q, q16,
+                                       (int64_t) T * H * R, (cudaStream_t) stream))
+            return e;
+        const WsLayout w = ws_layout(sc.t_max, 1, H, R);
+        p.q = q16;
+        p.q_is_f32 = false;
+        p.cache = rows;
+        p.cache_rows = (int64_t) sc.t_max * sc.max_rows;
+        p.seq_lens = lens;
+        p.seq_base = bases;
+        p.page_rows = 64;
+        p.scale = scale;
+        p.tail_causal = 0;
+        p.o = o;
+        p.status = (int32_t *) base;
+        p.ws_desc = (int2 *) (base + w.off_desc);
+        p.ws_acc = (float *) (base + w.off_acc);
+        p.ws_ml = (float *) (base + w.off_ml);
+        p.max_segments = w.max_segments;
+        p.n_seq = T;
+        p.T = 1;
+        p.H = H;
+        p.d_qk = R;
+        p.d_v = R;
+        p.max_seq_len = sel_stride;
+        // a few thousand rows: one CTA per 128 rows keeps the partial records (and the combine) small
+        const int64_t want = ((int64_t) T * sel_stride + 127) / 128;
+        p.max_ctas = (int) (want < 1 ? 1 : want > p.sm_count ? p.sm_count : want);
+        const char *why = "";
+        if (decode_umma_supported(p, &why)) return launch_decode_umma(p, (cudaStream_t) stream);
+        p = DecodeProblem{};
+        if (int e = device_sm_count(&p.sm_count)) return e;
+    }
     p.q = q;
     p.q_is_f32 = true;
     p.cache = (const __half *) C;
@@ -149,7 +241,6 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     p.d_qk = R;
     p.d_v = R;
     p.splits = splits;
-    if (int e = device_sm_count(&p.sm_count)) return e;
     return launch_decode_simt(p, (cudaStream_t) stream);
 }
 

@@ -835,6 +835,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.d_v = p.d_v;
     P.cache_rows = p.cache_rows;
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
+    if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
     if (grid < 1) grid = 1;
     if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
     for (int g = 0; g < n_groups; g++) {

@@ -31,6 +31,7 @@ struct DecodeProblem {
     int max_seq_len;
     int splits;           // CUDA-core kernel: splits per (sequence, token); 0 = choose
     int sm_count;
+    int max_ctas;         // tcgen05 kernel: upper bound of the persistent grid (0 = one CTA per SM)
     bool no_combine;      // stop after the attention kernel (timing aid)
     const gs_shard_exchange *exchange;  // cross-GPU merge of the records instead of a local output, or nullptr
     cudaEvent_t ev_after_main;  // recorded between the attention kernel and the combine, or nullptr
@@ -57,6 +58,10 @@ struct CombinePlan {
 };
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
+// rows named by per-token position lists -> contiguous f16 rows, f32 queries -> f16, lengths and bases (gather.cu)
+int launch_gather_rows(const __half *C, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R,
+                       __half *rows_out, int32_t *lens_out, int32_t *base_out, const float *q, __half *q16, int64_t q_elems,
+                       cudaStream_t st);
 int launch_combine(const CombinePlan &c, cudaStream_t st);
 // local merge + peer-to-peer exchange of the merged records + final merge (exchange.cu)
 int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o, int32_t *status, int sm_count,

@@ -35,6 +35,21 @@ extern "C" {
 int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride, const int *cnt,
                 float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
 
+/* Optional tensor-core path of gs_mla_attn (no counterpart in the reference).  The reference's only scratch,
+ * `part`, is too small for it, so the caller lends the library one more device buffer per device:
+ *   gs_mla_attn_scratch_bytes(t_max, H, max_rows): size for calls with T <= t_max (at most 4) query tokens, H heads
+ *     and position lists of at most max_rows entries (sel_stride <= max_rows);
+ *   gs_mla_attn_set_scratch(scratch, bytes, t_max, H, max_rows, stream): registers it for the current device
+ *     (256-byte aligned; NULL switches the path off again).  The buffer stays the caller's; it must outlive the
+ *     calls, and only one gs_mla_attn call per device may be in flight at a time while it is registered (the
+ *     engine issues its forward pass on one stream).
+ * While a scratch is registered, gs_mla_attn calls with an f16 cache that fit it gather the listed rows of every
+ * query token into contiguous rows, round the f32 queries to f16 (the precision of the f16-query entry points;
+ * outputs stay within max-abs 2e-3 of the f32-query result) and run the tcgen05 decode kernel, one token = one
+ * dense sequence.  Every other call (Q8 cache, more tokens, longer lists) runs the CUDA-core kernel as before. */
+int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows);
+int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream);
+
 /* Replaces gs_quant_q8_rows, crates/cuda/kernels/ops.cu:599-617 (Rust declaration crates/cuda/src/lib.rs:96;
  * caller crates/engine/src/forward.rs:852-856): the KV-append of the Q8 cache.  Per block of 32 values
  * d = amax / 127 (stored as f16), q = round-to-nearest-even(x / d) as int8.  n % 32 != 0 is rejected. */

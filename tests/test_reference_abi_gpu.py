@@ -172,3 +172,44 @@ def test_reference_q8_kernels_pin_oracle(pkg, cuda, oracle):
     o_new = _call(cuda, pkg._lib.load().gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
     check_close(o_orc, o_ref, "oracle vs reference kernel (q8)", 2e-5, 2e-6)
     check_close(o_new, o_ref, "ours vs reference kernel (q8)", 2e-5, 2e-6)
+
+
+# ---- tensor-core path of gs_mla_attn (opt-in through a caller-lent scratch) --------------------------------
+
+@pytest.mark.parametrize("T,H,n,dense", [(1, 64, 2052, False), (2, 64, 2052, False), (1, 32, 700, False), (4, 16, 33, False),
+                                         (1, 64, 0, True), (2, 48, 1, True), (3, 64, 1000, True)])
+def test_gs_mla_attn_tensor_path_vs_oracle_and_cuda_core_path(pkg, cuda, oracle, T, H, n, dense):
+    q, Cc, sel, cnt = _legacy_inputs(T * 31 + n + H, T, H, n, max(n, 1) + 3000, dense)
+    L = pkg._lib.load()
+    slow = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
+    scratch = pkg.mla_attn_scratch(4, H, sel.shape[1] + 5)
+    try:
+        fast = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
+        cuda.cuda.synchronize()
+        st = int(scratch[:4].view(cuda.int32)[0])
+    finally:
+        pkg.mla_attn_scratch_off()
+    assert st == 0
+    want = oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16)
+    check_close(slow, want, "CUDA-core path")
+    check_close(fast, want, "tensor-core path")          # f16-rounded queries: the tolerance of the f16-query entry points
+    if n > 8:
+        check_not_degenerate(fast, "tensor-core path")
+    # after unregistering, the exact path is back
+    again = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
+    assert np.array_equal(again, slow)
+
+
+def test_gs_mla_attn_tensor_path_falls_back_when_the_call_does_not_fit(pkg, cuda, oracle):
+    L = pkg._lib.load()
+    scratch = pkg.mla_attn_scratch(2, 64, 512)
+    try:
+        # five tokens > t_max, a list longer than max_rows, other head count, Q8 cache: all on the CUDA-core kernel
+        for T, H, n in ((5, 64, 100), (1, 64, 900), (1, 32, 100)):
+            q, Cc, sel, cnt = _legacy_inputs(T + n, T, H, n, n + 50, False)
+            got = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
+            check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "fallback", 2e-5, 2e-6)
+    finally:
+        pkg.mla_attn_scratch_off()
+    assert L.gs_mla_attn_scratch_bytes(5, 64, 100) == 0 and L.gs_mla_attn_scratch_bytes(4, 64, 100) > 0
+    assert L.gs_mla_attn_set_scratch(1 << 8, 16, 1, 64, 100, None) != 0  # too small
