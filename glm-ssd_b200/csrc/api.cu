@@ -117,19 +117,27 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
 }
 
 // ---- optional tensor-core path of the reference-compatible entry point ------------------------------------
-// Scratch registered by the caller, per device: [workspace of a decode with n_seq = T_max, T = 1][lens T_max]
-// [bases T_max][queries f16 T_max*H*512][rows T_max*max_rows*512 f16].
+// Scratch registered by the caller, per device (G = head groups per token): [workspace of a decode with
+// n_seq = G T_max, T = 1, H/G heads][lens G T_max][bases G T_max][queries f16 T_max*H*512][rows T_max*max_rows*512 f16].
 struct AttnScratch {
     void *ptr;
     int64_t bytes;
     int t_max, h, max_rows;
 };
 static AttnScratch g_attn_scratch[64] = {};
-static constexpr int kAttnTensorTmax = 4;
+static constexpr int kAttnTensorTmax = 512;  // query tokens per call (decode, MTP verify, a prefill chunk)
+
+// Head groups per token, each a "sequence" of the dense kernel: groups of at most 48 heads, a multiple of 8 each;
+// 0 when the head count cannot be cut that way.
+static int attn_head_groups(int H) {
+    const int n = (H + 47) / 48;
+    return (n > 0 && H % n == 0 && (H / n) % 8 == 0) ? n : 0;
+}
 
 static int64_t attn_scratch_layout(int t_max, int H, int max_rows, int64_t *off_lens, int64_t *off_q, int64_t *off_rows) {
-    const int64_t ws = ws_layout(t_max, 1, H, 512).total;
-    const int64_t lens = ws, q16 = align_up(lens + 2 * (int64_t) t_max * 4, 256);
+    const int ng = attn_head_groups(H) > 0 ? attn_head_groups(H) : 1;
+    const int64_t ws = ws_layout(t_max * ng, 1, H / ng, 512).total;
+    const int64_t lens = ws, q16 = align_up(lens + 2 * (int64_t) t_max * ng * 4, 256);
     const int64_t rows = align_up(q16 + (int64_t) t_max * H * 512 * 2, 256);
     if (off_lens) *off_lens = lens;
     if (off_q) *off_q = q16;
@@ -138,7 +146,8 @@ static int64_t attn_scratch_layout(int t_max, int H, int max_rows, int64_t *off_
 }
 
 GS_EXPORT int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows) {
-    if (t_max <= 0 || t_max > kAttnTensorTmax || H <= 0 || max_rows <= 0) return 0;
+    if (t_max <= 0 || t_max > kAttnTensorTmax || H <= 0 || max_rows <= 0 || attn_head_groups(H) == 0) return 0;
+    if ((int64_t) t_max * attn_head_groups(H) > 1024 || (int64_t) t_max * max_rows >= (1ll << 31)) return 0;
     return attn_scratch_layout(t_max, H, max_rows, nullptr, nullptr, nullptr);
 }
 
@@ -152,7 +161,7 @@ GS_EXPORT int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, i
     }
     const int64_t need = gs_mla_attn_scratch_bytes(t_max, H, max_rows);
     if (need <= 0 || bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
-        set_error("gs_mla_attn_set_scratch: need %lld bytes, 256-byte aligned, 1 <= t_max <= %d (given %lld)", (long long) need,
+        set_error("gs_mla_attn_set_scratch: need %lld bytes, 256-byte aligned, 1 <= t_max <= %d, H in groups of 8..48 heads (given %lld)", (long long) need,
                   kAttnTensorTmax, (long long) bytes);
         return (int) cudaErrorInvalidValue;
     }
@@ -183,12 +192,16 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
         int64_t off_lens, off_q, off_rows;
         attn_scratch_layout(sc.t_max, sc.h, sc.max_rows, &off_lens, &off_q, &off_rows);
         char *base = (char *) sc.ptr;
-        int32_t *lens = (int32_t *) (base + off_lens), *bases = lens + sc.t_max;
+        const int n_groups = attn_head_groups(H);  // > 0: checked when the scratch was registered
+        int32_t *lens = (int32_t *) (base + off_lens), *bases = lens + sc.t_max * n_groups;
         __half *q16 = (__half *) (base + off_q), *rows = (__half *) (base + off_rows);
-        if (int e = launch_gather_rows((const __half *) C, sel, sel_stride, cnt, T, sc.max_rows, R, rows, lens, bases, q, q16,
-                                       (int64_t) T * H * R, (cudaStream_t) stream))
+        // More than 48 heads: every group of Hg heads of a token becomes a sequence of its own over the same rows
+        // (q [T][H][R] and o [T][H][R] are [T * groups][Hg][R] as they lie), so one launch covers all of them.
+        const int Hg = H / n_groups;
+        if (int e = launch_gather_rows((const __half *) C, sel, sel_stride, cnt, T, sc.max_rows, R, n_groups, rows, lens, bases,
+                                       q, q16, (int64_t) T * H * R, (cudaStream_t) stream))
             return e;
-        const WsLayout w = ws_layout(sc.t_max, 1, H, R);
+        const WsLayout w = ws_layout(sc.t_max * n_groups, 1, Hg, R);
         p.q = q16;
         p.q_is_f32 = false;
         p.cache = rows;
@@ -204,14 +217,14 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
         p.ws_acc = (float *) (base + w.off_acc);
         p.ws_ml = (float *) (base + w.off_ml);
         p.max_segments = w.max_segments;
-        p.n_seq = T;
+        p.n_seq = T * n_groups;
         p.T = 1;
-        p.H = H;
+        p.H = Hg;
         p.d_qk = R;
         p.d_v = R;
         p.max_seq_len = sel_stride;
         // a few thousand rows: one CTA per 128 rows keeps the partial records (and the combine) small
-        const int64_t want = ((int64_t) T * sel_stride + 127) / 128;
+        const int64_t want = ((int64_t) T * n_groups * sel_stride + 127) / 128;
         p.max_ctas = (int) (want < 1 ? 1 : want > p.sm_count ? p.sm_count : want);
         const char *why = "";
         if (decode_umma_supported(p, &why)) return launch_decode_umma(p, (cudaStream_t) stream);

@@ -222,6 +222,63 @@ __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
     if (prof) prof[2] = sm100::global_timer_ns();
 }
 
+// Combine for large batches: a sequence then has only a few segments (about n_ctas / n_seq + 1), and one CTA per
+// (row, 128 columns) with block-wide reductions costs far more than the merge itself.  Here one thread owns four
+// columns of one output row and walks the row's segments; (m, l) loads are the same for the whole block.
+__global__ void __launch_bounds__(128) k_combine_rows(const CombinePlan C) {
+#if __CUDA_ARCH__ >= 900
+    cudaTriggerProgrammaticLaunchCompletion();
+    cudaGridDependencySynchronize();  // the partial records and desc are written by the preceding kernel
+#endif
+    const int row = blockIdx.x;
+    const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
+    int first, nseg, row_in_seg;
+    if (C.desc) {
+        const int2 d = __ldcg(C.desc + b);
+        first = d.x;
+        nseg = d.y;
+        row_in_seg = t * C.H + h;
+    } else {
+        first = (b * C.T + t) * C.regular_segments;
+        nseg = C.regular_segments;
+        row_in_seg = h;
+    }
+    const float *ml0 = C.ml + (int64_t) first * C.seg_stride_ml + row_in_seg * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < nseg; s++) M = fmaxf(M, __ldcg(ml0 + (int64_t) s * C.seg_stride_ml));
+    const int H_out = C.H_out > 0 ? C.H_out : C.H;
+    const int64_t orow = (int64_t) (row / C.H) * H_out + C.h0 + row % C.H;
+    const int64_t rows_total = (int64_t) C.n_seq * C.T * H_out;
+    for (int col = threadIdx.x * 4; col < C.d_v; col += blockDim.x * 4) {
+        const float *acc0 = C.acc + (int64_t) first * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+        for (int s = 0; s < nseg; s++) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(ml0 + (int64_t) s * C.seg_stride_ml));
+            const float w = ml.x == -INFINITY ? 0.f : expf(ml.x - M);
+            L += ml.y * w;
+            if (w != 0.f) {  // an empty segment's accumulator never enters the sum
+                const float4 u = __ldcg(reinterpret_cast<const float4 *>(acc0 + (int64_t) s * C.seg_stride_acc));
+                a.x = fmaf(u.x, w, a.x);
+                a.y = fmaf(u.y, w, a.y);
+                a.z = fmaf(u.z, w, a.z);
+                a.w = fmaf(u.w, w, a.w);
+            }
+        }
+        if (C.part_out) {
+            *reinterpret_cast<float4 *>(C.part_out + orow * C.d_v + col) = a;
+            if (col == 0) {
+                C.part_out[rows_total * C.d_v + orow * 2] = M;
+                C.part_out[rows_total * C.d_v + orow * 2 + 1] = L;
+            }
+        }
+        if (C.o) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            *reinterpret_cast<float4 *>(C.o + orow * C.d_v + col) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
+    }
+}
+
 }  // namespace
 
 int launch_combine(const CombinePlan &c, cudaStream_t st) {
@@ -229,8 +286,10 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (c.d_v % 4 != 0) return fail_invalid("combine: d_v must be a multiple of 4");
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
-    cfg.blockDim = dim3(CB_NT);
+    // many sequences: few segments each (the attention kernel spreads n_ctas + n_seq segments over them)
+    const bool by_rows = c.desc != nullptr && c.n_seq >= 16;
+    cfg.gridDim = by_rows ? dim3(rows) : dim3(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
+    cfg.blockDim = by_rows ? dim3(128) : dim3(CB_NT);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -238,7 +297,8 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GS_TRY(cudaLaunchKernelEx(&cfg, k_combine, c));
+    if (by_rows) GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_rows, c));
+    else GS_TRY(cudaLaunchKernelEx(&cfg, k_combine, c));
     return 0;
 }
 

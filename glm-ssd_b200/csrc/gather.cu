@@ -8,12 +8,16 @@ namespace gs {
 namespace {
 
 // grid (row blocks + query blocks, T), 256 threads.  A row block copies 4 rows of one token: 64 threads per
-// row of R = 512 halves.  Block (0, t) also leaves the token's length and base row; the query blocks convert
-// the f32 queries.
+// row of R = 512 halves.  Block (0, t) also leaves the token's length and base row, once per head group; the
+// query blocks convert the f32 queries.
 __global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ C, const int *__restrict__ sel, int sel_stride,
-                                                     const int *__restrict__ cnt, int max_rows, int row_blocks,
+                                                     const int *__restrict__ cnt, int max_rows, int row_blocks, int n_groups,
                                                      __half *__restrict__ rows_out, int32_t *lens_out, int32_t *base_out,
                                                      const float *__restrict__ q, __half *__restrict__ q16, int64_t q_elems) {
+#if __CUDA_ARCH__ >= 900
+    // the attention kernel behind this one may set itself up right away; its dependency wait covers these writes
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
     const int t = blockIdx.y;
     if ((int) blockIdx.x >= row_blocks) {  // query conversion, spread over the remaining blocks of every token row
         const int64_t nb = (int64_t) (gridDim.x - row_blocks) * gridDim.y;
@@ -25,9 +29,10 @@ __global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ 
         return;
     }
     const int n = min(min(max(cnt[t], 0), sel_stride), max_rows);
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        lens_out[t] = n;
-        base_out[t] = t * max_rows;
+    // every head group of the token is its own dense "sequence" over the same gathered rows
+    if (blockIdx.x == 0 && (int) threadIdx.x < n_groups) {
+        lens_out[t * n_groups + threadIdx.x] = n;
+        base_out[t * n_groups + threadIdx.x] = t * max_rows;
     }
     const int i = blockIdx.x * 4 + (threadIdx.x >> 6), c = threadIdx.x & 63;
     if (i >= n) return;
@@ -38,14 +43,14 @@ __global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ 
 
 }  // namespace
 
-int launch_gather_rows(const __half *C, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R,
+int launch_gather_rows(const __half *C, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
                        __half *rows_out, int32_t *lens_out, int32_t *base_out, const float *q, __half *q16, int64_t q_elems,
                        cudaStream_t st) {
     if (R != 512) return fail_invalid("gather: rows of 512 values only");
     const int rows = sel_stride < max_rows ? sel_stride : max_rows;
     const int row_blocks = (rows + 3) / 4 > 0 ? (rows + 3) / 4 : 1;
     const int q_blocks = 8;
-    k_gather_rows<<<dim3(row_blocks + q_blocks, T), 256, 0, st>>>(C, sel, sel_stride, cnt, max_rows, row_blocks, rows_out,
+    k_gather_rows<<<dim3(row_blocks + q_blocks, T), 256, 0, st>>>(C, sel, sel_stride, cnt, max_rows, row_blocks, n_groups, rows_out,
                                                                  lens_out, base_out, q, q16, q_elems);
     GS_TRY(cudaGetLastError());
     return 0;

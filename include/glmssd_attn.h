@@ -37,8 +37,9 @@ int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *
 
 /* Optional tensor-core path of gs_mla_attn (no counterpart in the reference).  The reference's only scratch,
  * `part`, is too small for it, so the caller lends the library one more device buffer per device:
- *   gs_mla_attn_scratch_bytes(t_max, H, max_rows): size for calls with T <= t_max (at most 4) query tokens, H heads
- *     and position lists of at most max_rows entries (sel_stride <= max_rows);
+ *   gs_mla_attn_scratch_bytes(t_max, H, max_rows): size for calls with T <= t_max (at most 512) query tokens, H heads
+ *     and position lists of at most max_rows entries (sel_stride <= max_rows): about t_max * max_rows KB, since
+ *     every token's rows are gathered separately; 0 if the sizes are not supported;
  *   gs_mla_attn_set_scratch(scratch, bytes, t_max, H, max_rows, stream): registers it for the current device
  *     (256-byte aligned; NULL switches the path off again).  The buffer stays the caller's; it must outlive the
  *     calls, and only one gs_mla_attn call per device may be in flight at a time while it is registered (the
@@ -46,7 +47,8 @@ int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *
  * While a scratch is registered, gs_mla_attn calls with an f16 cache that fit it gather the listed rows of every
  * query token into contiguous rows, round the f32 queries to f16 (the precision of the f16-query entry points;
  * outputs stay within max-abs 2e-3 of the f32-query result) and run the tcgen05 decode kernel, one token = one
- * dense sequence.  Every other call (Q8 cache, more tokens, longer lists) runs the CUDA-core kernel as before. */
+ * dense sequence (decode, MTP verify, and prefill chunks whose lists are short, i.e. sparse attention).  Every other
+ * call (Q8 cache, more tokens, longer lists) runs the CUDA-core kernel as before. */
 int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows);
 int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream);
 
