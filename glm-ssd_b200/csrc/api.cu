@@ -18,7 +18,7 @@ void set_error(const char *fmt, ...) {
 static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 struct WsLayout {
-    int64_t off_desc, off_acc, off_ml, total, max_segments;
+    int64_t off_desc, off_acc, off_ml, total, max_segments, record_rows;
 };
 
 static WsLayout ws_layout(int n_seq, int T, int H, int d_v) {
@@ -29,7 +29,9 @@ static WsLayout ws_layout(int n_seq, int T, int H, int d_v) {
     const int64_t rows_simt = (int64_t) n_seq * T * kSimtMaxSplits * H;
     const int64_t rows = rows_umma > rows_simt ? rows_umma : rows_simt;
     w.off_desc = kStatusBytes;
-    w.off_acc = align_up(w.off_desc + (int64_t) n_seq * (int64_t) sizeof(int2), 256);
+    // descriptors: up to 8 head groups of a sequence may run as sequences of their own
+    w.off_acc = align_up(w.off_desc + (int64_t) n_seq * 8 * (int64_t) sizeof(int2), 256);
+    w.record_rows = rows;
     w.off_ml = align_up(w.off_acc + rows * d_v * 4, 256);
     w.total = align_up(w.off_ml + rows * 2 * 4, 256);
     return w;
@@ -94,6 +96,7 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
     p.ws_acc = (float *) (ws + w.off_acc);
     p.ws_ml = (float *) (ws + w.off_ml);
     p.max_segments = w.max_segments;
+    p.max_record_rows = w.record_rows;
     p.n_seq = a->n_seq;
     p.T = a->T;
     p.H = a->H;
@@ -217,6 +220,7 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
         p.ws_acc = (float *) (base + w.off_acc);
         p.ws_ml = (float *) (base + w.off_ml);
         p.max_segments = w.max_segments;
+        p.max_record_rows = w.record_rows;
         p.n_seq = T * n_groups;
         p.T = 1;
         p.H = Hg;

@@ -60,7 +60,7 @@ __device__ __forceinline__ SegRange combine_locate(const CombinePlan &C, int row
     // saturate at 2^29; capped non-negative terms make that sum min(plain sum, 2^29), recomputed here in 64 bits.
     constexpr long long kUnitCap = 1ll << 29;
     auto units_of = [&](int i) -> long long {
-        const long long len = min((long long) max(__ldg(C.seq_lens + i), 0), (long long) C.len_cap);
+        const long long len = min((long long) max(__ldg(C.seq_lens + i / (C.seq_div > 1 ? C.seq_div : 1)), 0), (long long) C.len_cap);
         return (len + C.unit_rows - 1) / C.unit_rows;
     };
     long long before = 0, total = 0;

@@ -108,6 +108,8 @@ struct UmmaParams {
     int32_t *status;
     int n_seq, T, H, rows_q, d_v;  // H: heads handled by this launch (a group of the H_full heads of q)
     int H_full, h0;                // q holds H_full heads per token; this launch takes heads h0 .. h0+H-1
+    int seq_div;                   // >= 1: kernel sequence b reads the length / base / pages of caller sequence b / seq_div
+                                   // (T = 1 only: the head groups of a sequence as sequences of their own)
     int64_t cache_rows;
 };
 
@@ -276,8 +278,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             // are final - the schedule stays monotone and every index derived from it stays in range.
             const int64_t len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
             for (int b = tid; b < P.n_seq; b += NTHREADS) {
-                const int len = (int) min((int64_t) max(ld_global_hint(P.seq_lens + b, pol_keep), 0), len_cap);
-                M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b, pol_keep) : 0;
+                const int len = (int) min((int64_t) max(ld_global_hint(P.seq_lens + b / P.seq_div, pol_keep), 0), len_cap);
+                M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b / P.seq_div, pol_keep) : 0;
                 M.len[b] = len;
                 M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;  // < 2^27
             }
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 int64_t grow = -1;
                 if (!P.paged) grow = (int64_t) M.base[s2.b] + row;
                 else if (row >= 0 && row / TILE < P.page_table_stride)
-                    grow = (int64_t) P.page_table[(int64_t) s2.b * P.page_table_stride + row / TILE] * TILE;
+                    grow = (int64_t) P.page_table[(int64_t) (s2.b / P.seq_div) * P.page_table_stride + row / TILE] * TILE;
                 if (grow >= 0 && grow < P.cache_rows && elect_one()) {
 #pragma unroll
                     for (int k = 0; k < NBLK; k++) tma_prefetch_2d(&P.tm_kv64, k * 64, (int) grow);
@@ -376,7 +378,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
                 if (P.paged || valid == TILE) {
-                    const int grow = P.paged ? P.page_table[(int64_t) sg.b * P.page_table_stride +
+                    const int grow = P.paged ? P.page_table[(int64_t) (sg.b / P.seq_div) * P.page_table_stride +
                                                             min(max(row / TILE, 0), P.page_table_stride - 1)] * TILE
                                              : (int) (base_row + row);
                     if (elect_one()) {
@@ -805,12 +807,19 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
 
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     // Head groups: up to 48 query rows (T tokens x Hg heads) ride on the N side of one launch.
-    int Hg = p.H, n_groups = 1;
+    int Hg = p.H, n_groups = 1, seq_div = 1;
     if (p.T * p.H > 48) {
         const int hg_max = (48 / p.T) & ~7;          // a multiple of 8 heads
         n_groups = (p.H + hg_max - 1) / hg_max;
         Hg = (((p.H + n_groups - 1) / n_groups) + 7) & ~7;  // balanced, rounded up to 8
+        // One query token and equal groups: q [n_seq][H][d] is [n_seq * groups][Hg][d] as it lies (and so is o), so the
+        // groups of a sequence can be sequences of their own over the same rows - one launch instead of one per group.
+        if (p.T == 1 && Hg * n_groups == p.H && n_groups <= 8 && (int64_t) p.n_seq * n_groups <= MAX_SEQ) {
+            seq_div = n_groups;
+            n_groups = 1;
+        }
     }
+    const int n_seq_k = p.n_seq * seq_div;  // sequences as the kernel sees them
     UmmaParams P;
     memset(&P, 0, sizeof(P));
     const int kSw128 = (int) CU_TENSOR_MAP_SWIZZLE_128B;
@@ -829,15 +838,18 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.ws_ml = p.ws_ml;
     P.ws_desc = p.ws_desc;
     P.status = p.status;
-    P.n_seq = p.n_seq;
+    P.n_seq = n_seq_k;
     P.T = p.T;
-    P.H_full = p.H;
+    P.H_full = seq_div > 1 ? Hg : p.H;
+    P.seq_div = seq_div;
     P.d_v = p.d_v;
     P.cache_rows = p.cache_rows;
     int grid = p.sm_count < kMaxCtas ? p.sm_count : kMaxCtas;
     if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
     if (grid < 1) grid = 1;
-    if ((int64_t) grid + p.n_seq > p.max_segments) return fail_invalid("decode: workspace too small for the segment records");
+    // every CTA and every sequence can add one segment, each with the query rows of one launch
+    if (((int64_t) grid + n_seq_k) * p.T * (seq_div > 1 || n_groups > 1 ? Hg : p.H) > p.max_record_rows)
+        return fail_invalid("decode: workspace too small for the segment records");
     for (int g = 0; g < n_groups; g++) {
         const int h0 = g * Hg;
         const int hg = p.H - h0 < Hg ? p.H - h0 : Hg;
@@ -857,11 +869,12 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.regular_segments = 0;
         c.seg_stride_acc = (int64_t) rows_q * p.d_v;
         c.seg_stride_ml = (int64_t) rows_q * 2;
-        c.n_seq = p.n_seq;
+        c.n_seq = n_seq_k;
         c.T = p.T;
         c.H = hg;
-        c.H_out = p.H;
+        c.H_out = seq_div > 1 ? hg : p.H;
         c.h0 = h0;
+        c.seq_div = seq_div;
         c.d_v = p.d_v;
         c.o = p.o;
         c.part_out = p.part_out;

@@ -27,6 +27,7 @@ struct DecodeProblem {
     float *ws_ml;
     int2 *ws_desc;        // per-sequence (first_segment, n_segments), written by the tcgen05 kernel
     int64_t max_segments;
+    int64_t max_record_rows;  // query rows of partial records the workspace holds (segments x rows per segment)
     int n_seq, T, H, d_qk, d_v;
     int max_seq_len;
     int splits;           // CUDA-core kernel: splits per (sequence, token); 0 = choose
@@ -55,6 +56,7 @@ struct CombinePlan {
     const int32_t *seq_lens;
     int unit_rows, n_ctas;
     int64_t len_cap;       // a length counts as at most this many rows, exactly as in the attention kernel
+    int seq_div;           // > 1: sequence b of the records has the length of caller sequence b / seq_div (0 or 1: itself)
 };
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
