@@ -8,6 +8,8 @@
 // Arithmetic follows the reference kernel's contract (crates/cuda/kernels/ops.cu:420-424):
 //   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
 // with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
+#include <type_traits>
+
 #include "combine.cuh"
 #include "sm100_prims.cuh"
 #include "internal.cuh"
@@ -17,7 +19,7 @@ namespace gs {
 namespace {
 
 constexpr int KT = 16;   // keys per shared-memory tile
-constexpr int HG = 32;   // heads per CTA
+constexpr int HG_MAX = 32;  // heads per CTA: 32, 16 or 8 (template parameter), fewer when the grid would not fill the GPU
 constexpr int NT = 256;  // threads per CTA
 
 struct SimtParams {
@@ -32,8 +34,9 @@ struct SimtParams {
     int T, H, d_qk, d_v, splits;
 };
 
-template <typename QT, bool Q8>
+template <typename QT, bool Q8, int HG>
 __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
+    static_assert(HG <= HG_MAX && HG <= 32, "a lane per head in the score reduction");
     const int split = blockIdx.x, hg = blockIdx.y, bt = blockIdx.z;
     const int b = bt / P.T, t = bt % P.T;
     const int h0 = hg * HG;
@@ -307,6 +310,13 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
         return fail_invalid("decode: need d_qk % 8 == 0, d_qk <= 576, d_v <= min(512, d_qk), d_v % 4 == 0");
     const int groups = p.n_seq * p.T;
     if (groups <= 0 || p.H <= 0) return 0;
+    // Heads per CTA.  When the caller fixes the number of splits (the reference's entry point; a decode call there is
+    // small), fewer heads per CTA are the only way to give every SM a CTA; otherwise the splits provide the CTAs.
+    int HG = HG_MAX;
+    if (p.splits > 0) {
+        const int64_t per_hg = (int64_t) groups * p.splits;
+        while (HG > 8 && per_hg * ((p.H + HG - 1) / HG) < p.sm_count) HG >>= 1;
+    }
     const int n_hg = (p.H + HG - 1) / HG;
     int splits = p.splits;
     if (splits <= 0) {
@@ -347,12 +357,19 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
         kernel<<<grid, NT, smem, st>>>(P);
         return 0;
     };
+    auto pick = [&](auto qtag, auto q8tag) -> int {
+        using QT = decltype(qtag);
+        constexpr bool Q8 = decltype(q8tag)::value;
+        if (HG == 32) return launch(k_decode_gather<QT, Q8, 32>);
+        if (HG == 16) return launch(k_decode_gather<QT, Q8, 16>);
+        return launch(k_decode_gather<QT, Q8, 8>);
+    };
     int e;
     if (p.cache_scales) {
         if (p.d_qk % 32 != 0) return fail_invalid("decode: a Q8 cache needs d_qk % 32 == 0");
-        e = p.q_is_f32 ? launch(k_decode_gather<float, true>) : launch(k_decode_gather<__half, true>);
+        e = p.q_is_f32 ? pick(float{}, std::true_type{}) : pick(__half{}, std::true_type{});
     } else {
-        e = p.q_is_f32 ? launch(k_decode_gather<float, false>) : launch(k_decode_gather<__half, false>);
+        e = p.q_is_f32 ? pick(float{}, std::false_type{}) : pick(__half{}, std::false_type{});
     }
     if (e) return e;
     GS_TRY(cudaGetLastError());
