@@ -190,7 +190,7 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     int dev = 0;
     GS_TRY(cudaGetDevice(&dev));
     const AttnScratch sc = (dev >= 0 && dev < 64) ? g_attn_scratch[dev] : AttnScratch{};
-    if (sc.ptr && !C_scales && T <= sc.t_max && H == sc.h && sel_stride > 0 && sel_stride <= sc.max_rows && scale > 0.f &&
+    if (sc.ptr && T <= sc.t_max && H == sc.h && sel_stride > 0 && sel_stride <= sc.max_rows && scale > 0.f &&
         !(reinterpret_cast<uintptr_t>(C) & 15)) {
         int64_t off_lens, off_q, off_rows;
         attn_scratch_layout(sc.t_max, sc.h, sc.max_rows, &off_lens, &off_q, &off_rows);
@@ -201,7 +201,7 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
         // More than 48 heads: every group of Hg heads of a token becomes a sequence of its own over the same rows
         // (q [T][H][R] and o [T][H][R] are [T * groups][Hg][R] as they lie), so one launch covers all of them.
         const int Hg = H / n_groups;
-        if (int e = launch_gather_rows((const __half *) C, sel, sel_stride, cnt, T, sc.max_rows, R, n_groups, rows, lens, bases,
+        if (int e = launch_gather_rows((const __half *) C, (const __half *) C_scales, sel, sel_stride, cnt, T, sc.max_rows, R, n_groups, rows, lens, bases,
                                        q, q16, (int64_t) T * H * R, (cudaStream_t) stream))
             return e;
         const WsLayout w = ws_layout(sc.t_max * n_groups, 1, Hg, R);

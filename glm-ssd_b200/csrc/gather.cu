@@ -10,7 +10,8 @@ namespace {
 // grid (row blocks + query blocks, T), 256 threads.  A row block copies 4 rows of one token: 64 threads per
 // row of R = 512 halves.  Block (0, t) also leaves the token's length and base row, once per head group; the
 // query blocks convert the f32 queries.
-__global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ C, const int *__restrict__ sel, int sel_stride,
+__global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ C, const __half *__restrict__ C_scales,
+                                                     const int *__restrict__ sel, int sel_stride,
                                                      const int *__restrict__ cnt, int max_rows, int row_blocks, int n_groups,
                                                      __half *__restrict__ rows_out, int32_t *lens_out, int32_t *base_out,
                                                      const float *__restrict__ q, __half *__restrict__ q16, int64_t q_elems) {
@@ -37,20 +38,38 @@ __global__ void __launch_bounds__(256) k_gather_rows(const __half *__restrict__ 
     const int i = blockIdx.x * 4 + (threadIdx.x >> 6), c = threadIdx.x & 63;
     if (i >= n) return;
     const int64_t src = sel[(int64_t) t * sel_stride + i];
-    reinterpret_cast<uint4 *>(rows_out + ((int64_t) t * max_rows + i) * 512)[c] =
-        __ldg(reinterpret_cast<const uint4 *>(C + src * 512) + c);
+    uint4 *dst = reinterpret_cast<uint4 *>(rows_out + ((int64_t) t * max_rows + i) * 512) + c;
+    if (!C_scales) {
+        *dst = __ldg(reinterpret_cast<const uint4 *>(C + src * 512) + c);
+    } else {
+        // Q8 cache (ops.cu:427): int8 rows + one f16 scale per 32 values; the row is rebuilt as half_rn(scale * q),
+        // the values the reference's Q8 branch attends over (ops.cu:461-477).  8 values per thread.
+        const int8_t *row8 = reinterpret_cast<const int8_t *>(C) + src * 512;
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(row8) + c);
+        const float sc = __half2float(C_scales[src * 16 + (c >> 2)]);
+        auto pack = [sc](uint32_t w, uint32_t &h01, uint32_t &h23) {
+            const __half2 a = __floats2half2_rn(sc * (float) (int8_t) (w), sc * (float) (int8_t) (w >> 8));
+            const __half2 b = __floats2half2_rn(sc * (float) (int8_t) (w >> 16), sc * (float) (int8_t) (w >> 24));
+            h01 = *reinterpret_cast<const uint32_t *>(&a);
+            h23 = *reinterpret_cast<const uint32_t *>(&b);
+        };
+        uint4 out;
+        pack(raw.x, out.x, out.y);
+        pack(raw.y, out.z, out.w);
+        *dst = out;
+    }
 }
 
 }  // namespace
 
-int launch_gather_rows(const __half *C, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
+int launch_gather_rows(const __half *C, const __half *C_scales, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
                        __half *rows_out, int32_t *lens_out, int32_t *base_out, const float *q, __half *q16, int64_t q_elems,
                        cudaStream_t st) {
     if (R != 512) return fail_invalid("gather: rows of 512 values only");
     const int rows = sel_stride < max_rows ? sel_stride : max_rows;
     const int row_blocks = (rows + 3) / 4 > 0 ? (rows + 3) / 4 : 1;
     const int q_blocks = 8;
-    k_gather_rows<<<dim3(row_blocks + q_blocks, T), 256, 0, st>>>(C, sel, sel_stride, cnt, max_rows, row_blocks, n_groups, rows_out,
+    k_gather_rows<<<dim3(row_blocks + q_blocks, T), 256, 0, st>>>(C, C_scales, sel, sel_stride, cnt, max_rows, row_blocks, n_groups, rows_out,
                                                                  lens_out, base_out, q, q16, q_elems);
     GS_TRY(cudaGetLastError());
     return 0;

@@ -61,7 +61,7 @@ struct CombinePlan {
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
 // rows named by per-token position lists -> contiguous f16 rows, f32 queries -> f16, lengths and bases (gather.cu)
-int launch_gather_rows(const __half *C, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
+int launch_gather_rows(const __half *C, const __half *C_scales, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
                        __half *rows_out, int32_t *lens_out, int32_t *base_out, const float *q, __half *q16, int64_t q_elems,
                        cudaStream_t st);
 int launch_combine(const CombinePlan &c, cudaStream_t st);

@@ -44,11 +44,11 @@ int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *
  *     (256-byte aligned; NULL switches the path off again).  The buffer stays the caller's; it must outlive the
  *     calls, and only one gs_mla_attn call per device may be in flight at a time while it is registered (the
  *     engine issues its forward pass on one stream).
- * While a scratch is registered, gs_mla_attn calls with an f16 cache that fit it gather the listed rows of every
- * query token into contiguous rows, round the f32 queries to f16 (the precision of the f16-query entry points;
+ * While a scratch is registered, gs_mla_attn calls that fit it gather the listed rows of every query token into
+ * contiguous f16 rows (a Q8 cache is dequantised on the way, row by row as ops.cu:461-477 does), round the f32 queries to f16 (the precision of the f16-query entry points;
  * outputs stay within max-abs 2e-3 of the f32-query result) and run the tcgen05 decode kernel, one token = one
  * dense sequence (decode, MTP verify, and prefill chunks whose lists are short, i.e. sparse attention).  Every other
- * call (Q8 cache, more tokens, longer lists) runs the CUDA-core kernel as before. */
+ * call (more tokens, longer lists) runs the CUDA-core kernel as before. */
 int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows);
 int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream);
 

@@ -214,3 +214,20 @@ def test_gs_mla_attn_tensor_path_falls_back_when_the_call_does_not_fit(pkg, cuda
         pkg.mla_attn_scratch_off()
     assert L.gs_mla_attn_scratch_bytes(513, 64, 100) == 0 and L.gs_mla_attn_scratch_bytes(4, 72, 100) == 0 and L.gs_mla_attn_scratch_bytes(4, 64, 100) > 0
     assert L.gs_mla_attn_set_scratch(1 << 8, 16, 1, 64, 100, None) != 0  # too small
+
+
+@pytest.mark.parametrize("T,H,n", [(1, 64, 2052), (2, 32, 700), (3, 16, 40)])
+def test_gs_mla_attn_tensor_path_q8_cache(pkg, cuda, oracle, T, H, n):
+    q, Cc, sel, cnt = _legacy_inputs(T * 13 + n, T, H, n, n + 3000, False)
+    cq, cs = oracle.quant_q8_rows(Cc.astype(np.float32))
+    L = pkg._lib.load()
+    scratch = pkg.mla_attn_scratch(4, H, sel.shape[1] + 5)
+    try:
+        fast = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, 4, scales=cs)
+        cuda.cuda.synchronize()
+        assert int(scratch[:4].view(cuda.int32)[0]) == 0
+    finally:
+        pkg.mla_attn_scratch_off()
+    want = oracle.mla_attn_ref(q, oracle.dequant_q8(cq, cs), sel, cnt, 1 / 16)
+    check_close(fast, want, "tensor-core path, q8 cache")
+    check_not_degenerate(fast[-1], "tensor-core path, q8 cache")
