@@ -22,6 +22,10 @@ queries, N(0,0.5) cache).
             oracle) on the host cores; the reference has no CPU implementation of this path and
             its CUDA kernel rejects these shapes (R != 512 or H % 16 != 0).
 
+  others    the remaining configurations: the 128K-row decode, the paged 64-sequence batch, the 8192-token
+            prefill, the reference kernel's twin shapes (R = 512, 32 and 64 heads), and the engine's own sparse
+            decode shape through the reference's entry point gs_mla_attn (CUDA-core kernel and tensor-core path).
+
 With --gpus N > 1 (launched by torchrun) every rank runs its own independent copy of the workload
 (sequences are independent units: weak scaling, no collective on the data path); the "others"
 object carries the 128K-context decode sharded by sequence over the N GPUs, the paged 64-sequence
