@@ -57,46 +57,54 @@ __device__ __forceinline__ SegRange combine_locate(const CombinePlan &C, int row
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // The attention kernel caps every length at what the cache can hold and lets its running sum of units
-    // saturate at 2^29; capped non-negative terms make that sum min(plain sum, 2^29), recomputed here in 64 bits.
-    constexpr long long kUnitCap = 1ll << 29;
-    auto units_of = [&](int i) -> long long {
-        const long long len = min((long long) max(__ldg(C.seq_lens + i / (C.seq_div > 1 ? C.seq_div : 1)), 0), (long long) C.len_cap);
-        return (len + C.unit_rows - 1) / C.unit_rows;
+    // saturate at 2^29; capped non-negative terms make that sum min(plain sum, 2^29).  The terms fit an int
+    // (a length below 2^31 is at most 2^27 units of 16 rows); only the sums are kept in 64 bits, and the
+    // divisions below run on the saturated 32-bit values.  unit_rows is 16 or 64: a shift.
+    constexpr int kUnitCap = 1 << 29;
+    const int shift = __ffs(C.unit_rows) - 1, div = C.seq_div > 1 ? C.seq_div : 1;
+    const int len_cap = (int) min(C.len_cap, (int64_t) 0x7fffffff - 64);
+    auto units_of = [&](int i) -> int {
+        const int len = min(max(__ldg(C.seq_lens + (div == 1 ? i : i / div)), 0), len_cap);
+        return (len + C.unit_rows - 1) >> shift;
     };
-    long long before = 0, total = 0;
+    long long before64 = 0, total64 = 0;
     for (int i = tid; i < C.n_seq; i += CB_NT) {
-        const long long u = units_of(i);
-        total += u;
-        if (i < b) before += u;
+        const int u = units_of(i);
+        total64 += u;
+        if (i < b) before64 += u;
     }
+    if (C.n_seq > 1) {  // one sequence: thread 0 alone holds the (single) term, nothing to add up
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        total += __shfl_xor_sync(0xffffffffu, total, o);
-        before += __shfl_xor_sync(0xffffffffu, before, o);
-    }
-    if (lane == 0) {
-        S.lred2[0][warp] = total;
-        S.lred2[1][warp] = before;
-    }
-    __syncthreads();
-    total = before = 0;
+        for (int o = 16; o > 0; o >>= 1) {
+            total64 += __shfl_xor_sync(0xffffffffu, total64, o);
+            before64 += __shfl_xor_sync(0xffffffffu, before64, o);
+        }
+        if (lane == 0) {
+            S.lred2[0][warp] = total64;
+            S.lred2[1][warp] = before64;
+        }
+        __syncthreads();
+        total64 = before64 = 0;
 #pragma unroll
-    for (int w = 0; w < CB_NT / 32; w++) {
-        total += S.lred2[0][w];
-        before += S.lred2[1][w];
+        for (int w = 0; w < CB_NT / 32; w++) {
+            total64 += S.lred2[0][w];
+            before64 += S.lred2[1][w];
+        }
     }
-    const long long mine = units_of(b);
-    const long long after = min(before + mine, kUnitCap);  // saturated running sums, as the kernel holds them
-    before = min(before, kUnitCap);
-    total = min(total, kUnitCap);
-    const long long chunk = max(1ll, (total + C.n_ctas - 1) / C.n_ctas);
+    const int mine = units_of(b);
+    if (C.n_seq == 1) total64 = mine;
+    const int after = (int) min(before64 + mine, (long long) kUnitCap);  // saturated running sums, as the kernel holds them
+    const int before = (int) min(before64, (long long) kUnitCap);
+    const int total = (int) min(total64, (long long) kUnitCap);
+    const int chunk = max(1, (total + C.n_ctas - 1) / C.n_ctas);
     r.first = b;
     r.nseg = 0;
     if (after > before) {
-        const long long c_first = before / chunk, c_last = (after - 1) / chunk;
+        const int c_first = before / chunk, c_last = (after - 1) / chunk;
         // CTA indices are below n_ctas by construction; the clamp only keeps absurd inputs inside the workspace
-        r.first = (int) min(c_first, (long long) C.n_ctas - 1) + b;
-        r.nseg = (int) min(c_last - c_first + 1, (long long) C.n_ctas - min(c_first, (long long) C.n_ctas - 1));
+        const int cf = min(c_first, C.n_ctas - 1);
+        r.first = cf + b;
+        r.nseg = min(c_last - c_first + 1, C.n_ctas - cf);
     }
     return r;
 }

@@ -276,7 +276,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             // A length is taken as at most what the cache (or the sequence's row of the page table) can hold,
             // and the running sum below saturates: whatever the arrays contain - they are read once before they
             // are final - the schedule stays monotone and every index derived from it stays in range.
-            const int64_t len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
+            const int64_t len_cap = min(P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows,
+                                        (int64_t) 0x7fffffff - 64);  // the rounding up to units below stays in an int
             for (int b = tid; b < P.n_seq; b += NTHREADS) {
                 const int len = (int) min((int64_t) max(ld_global_hint(P.seq_lens + b / P.seq_div, pol_keep), 0), len_cap);
                 M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b / P.seq_div, pol_keep) : 0;
