@@ -227,8 +227,8 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
         p.d_qk = R;
         p.d_v = R;
         p.max_seq_len = sel_stride;
-        // a few thousand rows: one CTA per 128 rows keeps the partial records (and the combine) small
-        const int64_t want = ((int64_t) T * n_groups * sel_stride + 127) / 128;
+        // a few thousand rows: one CTA per 64-row tile (the shortest chain per CTA) while that leaves SMs free
+        const int64_t want = ((int64_t) T * n_groups * sel_stride + 63) / 64;
         p.max_ctas = (int) (want < 1 ? 1 : want > p.sm_count ? p.sm_count : want);
         const char *why = "";
         if (decode_umma_supported(p, &why)) return launch_decode_umma(p, (cudaStream_t) stream);
