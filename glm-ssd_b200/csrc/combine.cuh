@@ -222,6 +222,18 @@ __device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, const
     return holds;
 }
 
+// Output row of record row `row` = (sequence b, token t, head h of the records).  The records may cover a group of
+// the output's heads (h0), or - seq_div > 1 - sequence b of the records is head group b % seq_div of caller
+// sequence b / seq_div.
+__device__ __forceinline__ int64_t combine_out_row(const CombinePlan &C, int row, int &H_out) {
+    H_out = C.H_out > 0 ? C.H_out : C.H;
+    if (C.seq_div > 1) {
+        const int h = row % C.H, t = (row / C.H) % C.T, b = row / (C.H * C.T);
+        return ((int64_t) (b / C.seq_div) * C.T + t) * H_out + (b % C.seq_div) * C.H + h;
+    }
+    return (int64_t) (row / C.H) * H_out + C.h0 + row % C.H;
+}
+
 // Merge one item and write it: normalised output and/or the merged record.
 __device__ __forceinline__ void combine_item(const CombinePlan &C, const SegRange &R, int row, int col0, CombineSmem &S) {
     float4 a;
@@ -229,10 +241,10 @@ __device__ __forceinline__ void combine_item(const CombinePlan &C, const SegRang
     int col;
     if (combine_item_compute(C, R, col0, S, a, M, L, col)) {
         // the records may cover a group of the output's heads: row (b, t, h) of the group is row (b, t, h0 + h) there
-        const int H_out = C.H_out > 0 ? C.H_out : C.H;
-        const int64_t orow = (int64_t) (row / C.H) * H_out + C.h0 + row % C.H;
+        int H_out;
+        const int64_t orow = combine_out_row(C, row, H_out);
         if (C.part_out) {
-            const int64_t rows_total = (int64_t) C.n_seq * C.T * H_out;
+            const int64_t rows_total = (int64_t) (C.seq_div > 1 ? C.n_seq / C.seq_div : C.n_seq) * C.T * H_out;
             *reinterpret_cast<float4 *>(C.part_out + orow * C.d_v + col) = a;
             if (col == 0) {
                 C.part_out[rows_total * C.d_v + orow * 2] = M;

@@ -249,9 +249,9 @@ __global__ void __launch_bounds__(128) k_combine_rows(const CombinePlan C) {
     const float *ml0 = C.ml + (int64_t) first * C.seg_stride_ml + row_in_seg * 2;
     float M = -INFINITY;
     for (int s = 0; s < nseg; s++) M = fmaxf(M, __ldcg(ml0 + (int64_t) s * C.seg_stride_ml));
-    const int H_out = C.H_out > 0 ? C.H_out : C.H;
-    const int64_t orow = (int64_t) (row / C.H) * H_out + C.h0 + row % C.H;
-    const int64_t rows_total = (int64_t) C.n_seq * C.T * H_out;
+    int H_out;
+    const int64_t orow = combine_out_row(C, row, H_out);
+    const int64_t rows_total = (int64_t) (C.seq_div > 1 ? C.n_seq / C.seq_div : C.n_seq) * C.T * H_out;
     for (int col = threadIdx.x * 4; col < C.d_v; col += blockDim.x * 4) {
         const float *acc0 = C.acc + (int64_t) first * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);

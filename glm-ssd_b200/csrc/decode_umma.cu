@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #pragma unroll
                                 for (int k = 0; k < NBLK; k++)
                                     tma_load_2d(q_smem + k * NQ * 128 + t * P.H * 128, &P.tm_q, &B.q_full, k * 64,
-                                                (sg.b * P.T + t) * P.H_full + P.h0);
+                                                ((sg.b / P.seq_div) * P.T + t) * P.H_full + P.h0 + (sg.b % P.seq_div) * P.H);
                             }
                         }
                     }
@@ -813,11 +813,18 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         const int hg_max = (48 / p.T) & ~7;          // a multiple of 8 heads
         n_groups = (p.H + hg_max - 1) / hg_max;
         Hg = (((p.H + n_groups - 1) / n_groups) + 7) & ~7;  // balanced, rounded up to 8
-        // One query token and equal groups: q [n_seq][H][d] is [n_seq * groups][Hg][d] as it lies (and so is o), so the
-        // groups of a sequence can be sequences of their own over the same rows - one launch instead of one per group.
-        if (p.T == 1 && Hg * n_groups == p.H && n_groups <= 8 && (int64_t) p.n_seq * n_groups <= MAX_SEQ) {
-            seq_div = n_groups;
-            n_groups = 1;
+        // Equal groups can run as sequences of their own over the same rows - kernel sequence b is head group
+        // b % groups of caller sequence b / groups - so that one launch covers them.  Take the group count that
+        // divides the heads into multiples of 8 if it is the minimum or one more (each group reads the cache again).
+        for (int n = n_groups; n <= n_groups + 1 && n <= 8; n++) {
+            if (p.H % n == 0 && (p.H / n) % 8 == 0 && p.T * (p.H / n) <= 48) {
+                if ((int64_t) p.n_seq * n <= MAX_SEQ) {
+                    seq_div = n;
+                    Hg = p.H / n;
+                    n_groups = 1;
+                }
+                break;
+            }
         }
     }
     const int n_seq_k = p.n_seq * seq_div;  // sequences as the kernel sees them
@@ -841,7 +848,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     P.status = p.status;
     P.n_seq = n_seq_k;
     P.T = p.T;
-    P.H_full = seq_div > 1 ? Hg : p.H;
+    P.H_full = (seq_div > 1 && p.T == 1) ? Hg : p.H;  // one token: the groups' query rows are contiguous, no per-token boxes
     P.seq_div = seq_div;
     P.d_v = p.d_v;
     P.cache_rows = p.cache_rows;
@@ -859,7 +866,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         const int NQ = rows_q <= 32 ? 32 : 48;
         // one box of NQ rows when the rows of a sequence are contiguous, else one box of hg rows per token
         if (int e = encode_tmap_2d_f16(&P.tm_q, p.q, (uint64_t) p.n_seq * p.T * p.H, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
-                                       (uint32_t) (n_groups == 1 ? NQ : hg), 64, kSw128)) return e;
+                                       (uint32_t) (P.H_full == hg ? NQ : hg), 64, kSw128)) return e;
         P.H = hg;
         P.h0 = h0;
         P.rows_q = rows_q;
@@ -873,7 +880,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.n_seq = n_seq_k;
         c.T = p.T;
         c.H = hg;
-        c.H_out = seq_div > 1 ? hg : p.H;
+        c.H_out = p.H;
         c.h0 = h0;
         c.seq_div = seq_div;
         c.d_v = p.d_v;
