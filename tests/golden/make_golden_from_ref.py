@@ -1,10 +1,10 @@
 """Generate the golden fixtures that pin the CPU oracle: outputs of the reference engine's own CUDA
-kernels (gs_mla_attn, gs_f32_to_f16), compiled unmodified into oracle/_ref/libglmssd_ref.so by
+kernels (gs_mla_attn, gs_f32_to_f16, gs_quant_q8_rows), compiled unmodified into oracle/_ref/libglmssd_ref.so by
 oracle/build.py and run on a GPU.
 
     python tests/golden/make_golden_from_ref.py <out_dir>
 
-writes ref_*.npz into <out_dir>; the committed copies live beside this script.  Inputs are seeded
+writes ref_*.npz and refq8_cache.npz into <out_dir>; the committed copies live beside this script.  Inputs are seeded
 (numpy default_rng) so the run is reproducible.  Needs a CUDA device; not used at test time.
 """
 import ctypes as C
@@ -61,6 +61,32 @@ def main(out_dir: str) -> None:
                             scale=np.float32(1 / 16), o=o.cpu().numpy(), splits=np.int32(splits), append_x=x,
                             append_y=yd.cpu().numpy().view(np.uint16))
         print("wrote", name)
+    # Q8 latent cache: the reference's quantiser and its attention over (int8 rows, f16 scales)
+    ref.gs_quant_q8_rows.restype = i32
+    ref.gs_quant_q8_rows.argtypes = [vp, vp, vp, C.c_int64, vp]
+    rng = np.random.default_rng(201)
+    T, H, n, ctx, splits = 2, 16, 90, 128, 4
+    x = rng.standard_normal((ctx, 512), dtype=np.float32) * np.float32(0.5)
+    x[3] = 0.0
+    q = rng.standard_normal((T, H, 512), dtype=np.float32)
+    sel = np.zeros((T, n + 4), np.int32)
+    cnt = np.array([n - 1, n], np.int32)
+    for t in range(T):
+        sel[t, :cnt[t]] = rng.permutation(ctx)[:cnt[t]]
+    xd = torch.from_numpy(x).cuda()
+    c8 = torch.zeros((ctx, 512), dtype=torch.int8, device="cuda")
+    cs = torch.zeros((ctx, 16), dtype=torch.float16, device="cuda")
+    assert ref.gs_quant_q8_rows(xd.data_ptr(), c8.data_ptr(), cs.data_ptr(), ctx * 512, None) == 0
+    qd, sd, nd = torch.from_numpy(q).cuda(), torch.from_numpy(sel).cuda(), torch.from_numpy(cnt).cuda()
+    o = torch.zeros((T, H, 512), dtype=torch.float32, device="cuda")
+    part = torch.zeros(T * (H // 16) * splits * (16 * 512 + 32), dtype=torch.float32, device="cuda")
+    assert ref.gs_mla_attn(qd.data_ptr(), c8.data_ptr(), cs.data_ptr(), sd.data_ptr(), n + 4, nd.data_ptr(), 1 / 16,
+                           o.data_ptr(), part.data_ptr(), T, H, 512, splits, None) == 0
+    torch.cuda.synchronize()
+    np.savez_compressed(os.path.join(out_dir, "refq8_cache.npz"), x=x, q8=c8.cpu().numpy(),
+                        d=cs.cpu().numpy().view(np.uint16), q=q, sel=sel, cnt=cnt, scale=np.float32(1 / 16),
+                        o=o.cpu().numpy())
+    print("wrote q8_cache")
 
 
 if __name__ == "__main__":

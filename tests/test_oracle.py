@@ -203,3 +203,20 @@ def test_q8_round_trip_error_is_half_a_step(oracle):
     back = oracle.dequant_q8(q, d).astype(np.float32)
     step = np.repeat(d.astype(np.float32), 32, axis=1)
     assert np.all(np.abs(back - x) <= 0.5 * step * 1.01 + 2e-3 * np.abs(x))
+
+
+def test_q8_golden_vectors_from_reference_kernels(oracle):
+    """Outputs of the reference's own Q8 quantiser and Q8 attention branch (compiled unmodified, run on a B200) pin
+    the oracle's Q8 functions.  The reference is built with fast-math: its scale may differ by one f16 ulp and a value
+    on a rounding boundary by one step; the attention is compared over the reference's own (q8, scale) bytes."""
+    path = os.path.join(HERE, "golden", "refq8_cache.npz")
+    if not os.path.exists(path):
+        pytest.skip("no Q8 golden fixture committed yet")
+    g = np.load(path)
+    oq, od = oracle.quant_q8_rows(g["x"])
+    assert np.abs(oq.astype(np.int32) - g["q8"].astype(np.int32)).max() <= 1
+    assert (oq != g["q8"]).mean() < 1e-3
+    assert np.abs(od.view(np.uint16).astype(np.int32) - g["d"].astype(np.int32)).max() <= 1
+    rows = oracle.dequant_q8(g["q8"], g["d"].view(np.float16))
+    o = oracle.mla_attn_ref(g["q"], rows, g["sel"], g["cnt"], float(g["scale"]))
+    check_close(o, g["o"], "oracle vs reference Q8 attention", 2e-5, 2e-6)
