@@ -247,7 +247,7 @@ def _sparse_list_shape(torch, dev, fn, label, scratch=None):
     ctx, n, Hh = 32768, 2052, 64
     caches = [(torch.randn((ctx, 512), device=dev) * 0.5).half() for _ in range(6)]
     st = torch.cuda.current_stream().cuda_stream
-    for T, splits in ((1, 16), (2, 4)):
+    for T, splits in ((1, 16), (2, 4), (256, 1)):  # decode, MTP verify, a prefill chunk (forward.rs:898-901)
         q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
         sel = torch.stack([torch.randperm(ctx, device=dev)[:n].sort().values for _ in range(T)]).int().contiguous()
         cnt = torch.full((T,), n, dtype=torch.int32, device=dev)
@@ -263,12 +263,13 @@ def _sparse_list_shape(torch, dev, fn, label, scratch=None):
             call(i)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 30 if T <= 4 else 6
         e0.record()
-        for i in range(30):
+        for i in range(reps):
             call(i)
         e1.record()
         torch.cuda.synchronize()
-        res[f"sparse2052_T{T}_H64_{label}"] = {"us_per_call": e0.elapsed_time(e1) * 1e3 / 30, "splits": splits}
+        res[f"sparse2052_T{T}_H64_{label}"] = {"us_per_call": e0.elapsed_time(e1) * 1e3 / reps, "splits": splits}
     return res
 
 
@@ -594,7 +595,7 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     try:
         fn = pkg._lib.load().gs_mla_attn
         sp = _sparse_list_shape(torch, dev, fn, "cuda_core")
-        scratch = pkg.mla_attn_scratch(4, 64, 2060, dev)
+        scratch = pkg.mla_attn_scratch(256, 64, 2060, dev)
         try:
             sp.update(_sparse_list_shape(torch, dev, fn, "tensor_path"))
             torch.cuda.synchronize()

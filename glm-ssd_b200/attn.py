@@ -51,7 +51,7 @@ def mla_attn_scratch(t_max: int, H: int, max_rows: int, device=None):
     L = _lib.load()
     n = int(L.gs_mla_attn_scratch_bytes(t_max, H, max_rows))
     if n <= 0:
-        raise ValueError("t_max must be 1..4, H and max_rows positive")
+        raise ValueError("sizes outside the tensor-core path (1 <= t_max <= 512, heads in groups of 8..48)")
     buf = torch.zeros(n, dtype=torch.uint8, device=device or torch.cuda.current_device())
     _lib.check(L.gs_mla_attn_set_scratch(buf.data_ptr(), n, t_max, H, max_rows, _stream()), "gs_mla_attn_set_scratch")
     return buf
