@@ -2,6 +2,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "internal.cuh"
 
 namespace gs {
@@ -128,6 +130,7 @@ struct AttnScratch {
     int t_max, h, max_rows;
 };
 static AttnScratch g_attn_scratch[64] = {};
+static std::mutex g_attn_scratch_mutex;  // the registry is the library's only mutable global besides the error text
 static constexpr int kAttnTensorTmax = 512;  // query tokens per call (decode, MTP verify, a prefill chunk)
 
 // Head groups per token, each a "sequence" of the dense kernel: groups of at most 48 heads, a multiple of 8 each;
@@ -159,6 +162,7 @@ GS_EXPORT int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, i
     GS_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail_invalid("gs_mla_attn_set_scratch: device index beyond 63");
     if (!scratch) {
+        std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
         g_attn_scratch[dev] = AttnScratch{};
         return 0;
     }
@@ -169,6 +173,7 @@ GS_EXPORT int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, i
         return (int) cudaErrorInvalidValue;
     }
     GS_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes, (cudaStream_t) stream));  // sticky status block starts clean
+    std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
     g_attn_scratch[dev] = AttnScratch{scratch, bytes, t_max, H, max_rows};
     return 0;
 }
@@ -189,7 +194,11 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     // "sequence" of the tcgen05 kernel.  (A decode or MTP-verify call: few tokens, a few thousand rows each.)
     int dev = 0;
     GS_TRY(cudaGetDevice(&dev));
-    const AttnScratch sc = (dev >= 0 && dev < 64) ? g_attn_scratch[dev] : AttnScratch{};
+    AttnScratch sc{};
+    if (dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
+        sc = g_attn_scratch[dev];
+    }
     if (sc.ptr && T <= sc.t_max && H == sc.h && sel_stride > 0 && sel_stride <= sc.max_rows && scale > 0.f &&
         !(reinterpret_cast<uintptr_t>(C) & 15)) {
         int64_t off_lens, off_q, off_rows;

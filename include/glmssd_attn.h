@@ -43,7 +43,8 @@ int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *
  *   gs_mla_attn_set_scratch(scratch, bytes, t_max, H, max_rows, stream): registers it for the current device
  *     (256-byte aligned; NULL switches the path off again).  The buffer stays the caller's; it must outlive the
  *     calls, and only one gs_mla_attn call per device may be in flight at a time while it is registered (the
- *     engine issues its forward pass on one stream).
+ *     engine issues its forward pass on one stream).  A device reset (the engine's idle unload, runtime.cu:51-53)
+ *     frees the buffer with everything else: register a new one afterwards, or NULL.
  * While a scratch is registered, gs_mla_attn calls that fit it gather the listed rows of every query token into
  * contiguous f16 rows (a Q8 cache is dequantised on the way, row by row as ops.cu:461-477 does), round the f32 queries to f16 (the precision of the f16-query entry points;
  * outputs stay within max-abs 2e-3 of the f32-query result) and run the tcgen05 decode kernel, one token = one
