@@ -206,7 +206,8 @@ def reference_cuda_twin():
         torch.cuda.set_device(0)
         out = {}
         for name, n, T, Hh, splits in (("ctx32k_T2_H32", 32768, 2, 32, 4), ("ctx32k_T1_H32", 32768, 1, 32, 16),
-                                       ("ctx128k_T1_H32", 131072, 1, 32, 16), ("ctx32k_T1_H64", 32768, 1, 64, 16)):
+                                       ("ctx128k_T1_H32", 131072, 1, 32, 16), ("ctx32k_T1_H64", 32768, 1, 64, 16),
+                                       ("ctx4k_T1_H32", 4096, 1, 32, 16)):
             n_copies = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
             caches = [(torch.randn((n, 512), device=dev) * 0.5).half() for _ in range(n_copies)]
             q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
@@ -577,7 +578,8 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     # (more than 48 packed query rows run as head groups, one pass over the cache per group)
     twin = {}
     for name, n, T, Ht in (("ctx32k_T2_H32", 32768, 2, 32), ("ctx32k_T1_H32", 32768, 1, 32),
-                           ("ctx128k_T1_H32", 131072, 1, 32), ("ctx32k_T1_H64", 32768, 1, 64)):
+                           ("ctx128k_T1_H32", 131072, 1, 32), ("ctx32k_T1_H64", 32768, 1, 64),
+                           ("ctx4k_T1_H32", 4096, 1, 32)):
         nc = max(2, -(-2 * L2_BYTES // (n * 1024)) + 1)
         cs = [randn_f16((n, 512), 0.5) for _ in range(nc)]
         qt = randn_f16((1, T, Ht, 512))
