@@ -57,6 +57,7 @@ SIGNATURES = {
     "gs_peer_close": (i32, [vp]),
     "gs_prefill_attn": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]),
     "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),
+    "gs_norm_rope_kv_append_at": (i32, [vp, vp, f32, vp, i64, i32, i32, i32, f32, vp]),
     "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "gs_rope_f16_inplace": (i32, [vp, i32, i32, i32, i32, i64, f32, vp]),
     "gs_mla_layer_step_host": (i32, [C.POINTER(LayerStep), vp]),

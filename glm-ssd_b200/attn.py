@@ -177,6 +177,21 @@ def rope_kv_append_at(kv, cache, pos0, *, d_rope=64, rope_base=10000.0):
                "gs_rope_kv_append_at")
 
 
+def norm_rope_kv_append_at(kv, cache, pos0, *, weight=None, eps=1e-6, d_rope=64, rope_base=10000.0):
+    """The same with the latent RMSNorm folded in (forward.rs:850): the first d_row - d_rope columns are normalised
+    (``weight`` f32 [d_row - d_rope] or None), the rest rotated, all appended as f16."""
+    _need(kv, torch.float32, "kv")
+    _need(cache, torch.float16, "cache")
+    T, d_row = kv.shape
+    if pos0 + T > cache.shape[0]:
+        raise ValueError(f"context full ({cache.shape[0]} rows)")
+    if weight is not None:
+        _need(weight, torch.float32, "weight")
+    row0 = cache.data_ptr() + pos0 * d_row * 2
+    _lib.check(_lib.load().gs_norm_rope_kv_append_at(kv.data_ptr(), _ptr(weight), eps, row0, pos0, T, d_row, d_rope,
+                                                     rope_base, _stream()), "gs_norm_rope_kv_append_at")
+
+
 def rope_kv_append(kv, cache, pos0, *, seq_base=None, page_table=None, page_rows=64, d_rope=64, rope_base=10000.0):
     """Batched append: kv f32 [n_seq,T,d_row]; pos0 i32 [n_seq] on the device."""
     _need(kv, torch.float32, "kv")

@@ -102,6 +102,40 @@ __global__ void k_rope_append(const AppendParams P) {
     }
 }
 
+// RMSNorm of the latent columns fused into the append: y[c] = x[c] * rsqrt(mean(x[0..d0)^2) + eps) * w[c] for the
+// first d0 = d_row - d_rope columns (the reference runs gs_rmsnorm over the new latent rows and then appends them,
+// forward.rs:850 then :857-860; ops.cu:43-50), the last d_rope columns rotated at position pos0 + t; everything
+// rounded to f16.  One block of 128 threads per row; division and square root are IEEE (no fast-math in this file).
+__global__ void __launch_bounds__(128) k_norm_rope_append(const AppendParams P, const float *__restrict__ w, float eps) {
+    __shared__ float red[4];
+    const int t = blockIdx.x;
+    const int64_t pos = P.pos0_host + t;
+    const float *src = P.kv + (int64_t) t * P.d_row;
+    __half *dst = P.cache + (int64_t) t * P.d_row;
+    const int d0 = P.d_row - P.d_rope;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d0; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float tot = (red[0] + red[1]) + (red[2] + red[3]);
+    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float) d0), eps)));
+    for (int j = threadIdx.x; j < P.d_row / 2; j += blockDim.x) {
+        const int c = 2 * j;
+        float2 v = *reinterpret_cast<const float2 *>(src + c);
+        if (c >= d0) {
+            const float ang = (float) pos * P.tab.inv_freq[(c - d0) >> 1];
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            v = rotate(v, cs, sn);
+        } else {
+            v.x = __fmul_rn(__fmul_rn(v.x, r), w ? w[c] : 1.f);
+            v.y = __fmul_rn(__fmul_rn(v.y, r), w ? w[c + 1] : 1.f);
+        }
+        *reinterpret_cast<__half2 *>(dst + c) = __floats2half2_rn(v.x, v.y);
+    }
+}
+
 // First kernel of a replayed step.  Block 0 reads the position from a page-locked host word (so the launch
 // itself carries no per-step argument and can be replayed from a CUDA graph), appends the T rows of one
 // dense sequence there and leaves the new length in *len_dev for the attention kernel.  A step that would
@@ -237,6 +271,27 @@ GS_EXPORT int gs_rope_kv_append_at(const float *kv, void *cache_row0, int64_t po
     P.d_rope = d_rope;
     fill_table(P.tab, d_rope, rope_base);
     k_rope_append<<<dim3(T, 1), 128, 0, (cudaStream_t) stream>>>(P);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_norm_rope_kv_append_at(const float *kv, const float *w, float eps, void *cache_row0, int64_t pos0, int T,
+                                        int d_row, int d_rope, float rope_base, void *stream) {
+    if (int e = check_rope(d_row, d_rope)) return e;
+    if (T <= 0) return 0;
+    if (pos0 < 0) return fail_invalid("append: pos0 < 0");
+    if ((d_row - d_rope) % 2 != 0 || d_row == d_rope) return fail_invalid("append: need an even, non-empty run of latent columns");
+    if (!(eps >= 0.f)) return fail_invalid("append: eps must be non-negative");
+    AppendParams P{};
+    P.kv = kv;
+    P.cache = (__half *) cache_row0;
+    P.pos0_host = pos0;
+    P.page_rows = 1;
+    P.T = T;
+    P.d_row = d_row;
+    P.d_rope = d_rope;
+    fill_table(P.tab, d_rope, rope_base);
+    k_norm_rope_append<<<T, 128, 0, (cudaStream_t) stream>>>(P, w, eps);
     GS_TRY(cudaGetLastError());
     return 0;
 }

@@ -188,6 +188,11 @@ int gs_prefill_attn(const void *q, const void *k, const void *v, void *o, int o_
 int gs_rope_kv_append_at(const float *kv, void *cache_row0, int64_t pos0, int T, int d_row, int d_rope,
                          float rope_base, void *stream);
 /* Batched, positions on the device: pos0[b] is the position of sequence b's first new row. */
+/* The same append with the latent RMSNorm in front of it folded in (the reference runs gs_rmsnorm over the new
+ * rows, forward.rs:850 / ops.cu:43-50, and then appends them, :857-860): the first d_row - d_rope columns become
+ * x * rsqrt(mean(x^2) + eps) * w (w may be NULL = all ones), the last d_rope columns are rotated, all rounded to f16. */
+int gs_norm_rope_kv_append_at(const float *kv, const float *w, float eps, void *cache_row0, int64_t pos0, int T,
+                              int d_row, int d_rope, float rope_base, void *stream);
 int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos0, const int32_t *seq_base,
                       const int32_t *page_table, int page_table_stride, int page_rows, int n_seq, int T, int d_row,
                       int d_rope, float rope_base, void *stream);

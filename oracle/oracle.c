@@ -460,6 +460,26 @@ void oracle_rope_append(const float *x, uint16_t *y, int T, int d_row, int d_rop
     }
 }
 
+/* Latent RMSNorm (crates/cuda/kernels/ops.cu:43-50, called at forward.rs:850) followed by the fused RoPE + append:
+ * the first d_row - d_rope columns become x * rsqrt(mean(x^2) + eps) * w (w may be NULL), then the row goes through
+ * oracle_rope_append.  The sum of squares is accumulated in double, so this is the reference for any summation
+ * order. */
+void oracle_norm_rope_append(const float *x, const float *w, float eps, uint16_t *y, int T, int d_row, int d_rope,
+                             int64_t pos0, double base) {
+    const int d0 = d_row - d_rope;
+    float *tmp = (float *) malloc((size_t) d_row * sizeof(float));
+    for (int t = 0; t < T; t++) {
+        const float *xr = x + (int64_t) t * d_row;
+        double ss = 0.0;
+        for (int c = 0; c < d0; c++) ss += (double) xr[c] * xr[c];
+        const float r = (float) (1.0 / sqrt(ss / d0 + (double) eps));
+        for (int c = 0; c < d0; c++) tmp[c] = xr[c] * r * (w ? w[c] : 1.f);
+        for (int c = d0; c < d_row; c++) tmp[c] = xr[c];
+        oracle_rope_append(tmp, y + (int64_t) t * d_row, 1, d_row, d_rope, pos0 + t, base);
+    }
+    free(tmp);
+}
+
 /* RoPE in place on f16 rows [S][H][d] (prefill Q and K): last d_rope columns of every head at
  * position pos0 + s; computed in f32 and rounded back to f16. */
 void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base) {

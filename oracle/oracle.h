@@ -30,6 +30,8 @@ void oracle_quant_q8_rows(const float *x, int8_t *q, uint16_t *d, int64_t n_bloc
 void oracle_dequant_q8(const int8_t *q, const uint16_t *d, uint16_t *out, int64_t n_blocks);
 void oracle_rope_inv_freq(float *inv_freq, int d_rope, double base);
 void oracle_rope_append(const float *x, uint16_t *y, int T, int d_row, int d_rope, int64_t pos0, double base);
+void oracle_norm_rope_append(const float *x, const float *w, float eps, uint16_t *y, int T, int d_row, int d_rope,
+                             int64_t pos0, double base);
 void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base);
 
 #ifdef __cplusplus

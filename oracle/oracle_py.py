@@ -43,6 +43,7 @@ def lib() -> C.CDLL:
     L.oracle_dequant_q8.argtypes = [vp, vp, vp, i64]
     L.oracle_rope_inv_freq.argtypes = [vp, i32, C.c_double]
     L.oracle_rope_append.argtypes = [vp, vp, i32, i32, i32, i64, C.c_double]
+    L.oracle_norm_rope_append.argtypes = [vp, vp, f32, vp, i32, i32, i32, i64, C.c_double]
     L.oracle_rope_f16.argtypes = [vp, i32, i32, i32, i32, i64, C.c_double]
     _lib = L
     return L
@@ -148,6 +149,17 @@ def rope_append(x, pos0, d_rope=64, base=10000.0) -> np.ndarray:
     T, d_row = x.shape
     y = np.empty((T, d_row), np.uint16)
     lib().oracle_rope_append(_p(x), _p(y), T, d_row, d_rope, pos0, base)
+    return y.view(np.float16)
+
+
+def norm_rope_append(x, pos0, weight=None, eps=1e-6, d_rope=64, base=10000.0) -> np.ndarray:
+    """x f32 [T,d_row] -> f16 [T,d_row]: RMSNorm (weights ``weight`` or ones) on the first d_row - d_rope columns,
+    RoPE on the rest at positions pos0+t."""
+    x = _c(x, np.float32)
+    T, d_row = x.shape
+    w = None if weight is None else _c(weight, np.float32)
+    y = np.empty((T, d_row), np.uint16)
+    lib().oracle_norm_rope_append(_p(x), _p(w), eps, _p(y), T, d_row, d_rope, pos0, base)
     return y.view(np.float16)
 
 

@@ -220,3 +220,16 @@ def test_q8_golden_vectors_from_reference_kernels(oracle):
     rows = oracle.dequant_q8(g["q8"], g["d"].view(np.float16))
     o = oracle.mla_attn_ref(g["q"], rows, g["sel"], g["cnt"], float(g["scale"]))
     check_close(o, g["o"], "oracle vs reference Q8 attention", 2e-5, 2e-6)
+
+
+def test_norm_rope_append_matches_float64_numpy(oracle):
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((5, 576)).astype(np.float32) * np.float32(2.0)
+    w = (1.0 + 0.1 * rng.standard_normal(512)).astype(np.float32)
+    got = oracle.norm_rope_append(x, 100, weight=w, eps=1e-6).astype(np.float64)
+    lat = x[:, :512].astype(np.float64)
+    want_lat = lat / np.sqrt((lat ** 2).mean(1, keepdims=True) + 1e-6) * w
+    assert np.abs(got[:, :512] - want_lat).max() <= 2e-3 * np.abs(want_lat).max()
+    # the rotated columns are those of the plain RoPE append
+    plain = oracle.rope_append(x, 100).astype(np.float64)
+    assert np.array_equal(got[:, 512:], plain[:, 512:])

@@ -186,3 +186,22 @@ def test_decode_layer_graph_refuses_to_run_past_the_cache(pkg, cuda):
     assert L.gs_mla_layer_graph_step(h, ctx - 1, layer._graph_stream.cuda_stream, 1) != 0
     assert b"context full" in L.gs_attn_last_error_string()
     assert L.gs_mla_layer_graph_step(None, 0, layer._graph_stream.cuda_stream, 1) != 0
+
+
+@pytest.mark.parametrize("d_row,d_rope,with_w", [(576, 64, True), (512, 0, True), (576, 64, False), (128, 32, True)])
+def test_norm_rope_append_vs_oracle(pkg, cuda, oracle, d_row, d_rope, with_w):
+    rng = np.random.default_rng(d_row + d_rope)
+    T, pos0 = 3, 41
+    x = rng.standard_normal((T, d_row)).astype(np.float32) * np.float32(3.0)
+    w = (1.0 + 0.2 * rng.standard_normal(d_row - d_rope)).astype(np.float32) if with_w else None
+    cache = cuda.zeros((pos0 + T + 2, d_row), dtype=cuda.float16, device="cuda")
+    pkg.norm_rope_kv_append_at(cuda.from_numpy(x).cuda(), cache, pos0, weight=None if w is None else cuda.from_numpy(w).cuda(),
+                               eps=1e-6, d_rope=d_rope)
+    cuda.cuda.synchronize()
+    got = cache.cpu().numpy()
+    want = oracle.norm_rope_append(x, pos0, weight=w, eps=1e-6, d_rope=d_rope)
+    assert (got[:pos0] == 0).all() and (got[pos0 + T:] == 0).all()
+    g, v = got[pos0:pos0 + T].astype(np.float32), want.astype(np.float32)
+    # the sum of squares is added up in another order than the oracle's: at most one f16 step apart
+    ulp = np.maximum(np.abs(v), 2.0 ** -14) * 2.0 ** -10
+    assert np.all(np.abs(g - v) <= ulp + 4e-3 * (np.arange(d_row) >= d_row - d_rope))
