@@ -133,16 +133,27 @@ def cpu_decode_baseline(n_rows: int, T: int, budget_s: float, max_reps: int = 50
     rng = np.random.default_rng(0)
     q = rng.standard_normal((1, T, H, D_QK), dtype=np.float32).astype(np.float16)
     cache = (rng.standard_normal((n_rows, D_QK), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
-    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True)  # warm-up, page in
+    ks = cpu_key_splits(T)
+    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True, key_splits=ks)  # warm-up, page in
     t0 = time.perf_counter()
     reps = 0
     while reps < max_reps and (time.perf_counter() - t0 < budget_s or reps == 0):
-        O.mla_decode(q, cache, [n_rows], SCALE)
+        O.mla_decode(q, cache, [n_rows], SCALE, key_splits=ks)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     return {"value": algorithmic_bytes(n_rows, T) / dt / 1e9, "unit": "GB/s", "cores": int(used), "kind": "port",
-            "sample": f"full workload ({n_rows} rows, T={T}, H={H}), {reps} passes, {dt * 1e3:.1f} ms each",
+            "sample": f"full workload ({n_rows} rows, T={T}, H={H}), {reps} passes, {dt * 1e3:.1f} ms each; "
+                      f"{T * H * ks} work items = {T * H} (token, head) rows x {ks} key ranges",
             "seconds_per_pass": dt}
+
+
+def cpu_key_splits(T: int) -> int:
+    """Key ranges per (token, head) row so that every host core has several work items."""
+    from oracle import oracle_py as O
+    return max(1, -(-4 * O.host_cores() // (T * H)))
+
+
+WORKLOAD = "mtp_verify_32k: batch 1, T=2 causal, H=20, d_qk=576, d_v=512, ctx=32768, scale=1/16"
 
 
 def run_reference(args) -> None:
@@ -155,27 +166,29 @@ def run_reference(args) -> None:
     rng = np.random.default_rng(0)
     q = rng.standard_normal((1, T, H, D_QK), dtype=np.float32).astype(np.float16)
     cache = (rng.standard_normal((n_rows, D_QK), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
-    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True)
+    ks = cpu_key_splits(T)
+    _, used = O.mla_decode(q, cache, [n_rows], SCALE, return_threads=True, key_splits=ks)
     t0 = time.perf_counter()
-    O.mla_decode(q, cache, [n_rows], SCALE)
+    O.mla_decode(q, cache, [n_rows], SCALE, key_splits=ks)
     t_full = time.perf_counter() - t0
     # bound the whole run to about two minutes: shorten each step to a prefix of the cache if needed
     total = (args.steps + args.warmup) * t_full
     rows = n_rows if total <= 120.0 else max(1024, int(n_rows * 120.0 / total) // 64 * 64)
     for _ in range(args.warmup):
-        O.mla_decode(q, cache[:rows], [rows], SCALE)
+        O.mla_decode(q, cache[:rows], [rows], SCALE, key_splits=ks)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        O.mla_decode(q, cache[:rows], [rows], SCALE)
+        O.mla_decode(q, cache[:rows], [rows], SCALE, key_splits=ks)
     dt = (time.perf_counter() - t0) / max(1, args.steps)
     val = algorithmic_bytes(rows, T) / dt / 1e9
     sample = f"{rows} of {n_rows} cache rows per step" if rows != n_rows else "full workload per step"
+    sample += f"; {T * H * ks} work items = {T * H} (token, head) rows x {ks} key ranges"
     line = {
         "impl": "reference", "metric": "MLA decode-attention HBM GB/s (MTP verify, 32K ctx)", "value": val,
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "mtp_verify_32k: batch 1, T=2 causal, H=20, d_qk=576, d_v=512, ctx=32768, scale=1/16"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": int(used), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -323,44 +336,79 @@ def run_ours(args) -> None:
             flat[i:i + n] = (torch.randn(n, generator=gen, device=dev, dtype=torch.float32) * sigma).to(torch.float16)
         return out
 
-    def time_loop(fn, steps, warmup, period=1, use_graph=True):
+    def time_loop(fn, steps, warmup, period=1, use_graph=True, repeats=1, spread=None):
         """Device time of `steps` calls of fn(i) after `warmup` calls: barrier + sync on both sides,
-        CUDA events on the launching stream, max over ranks.  Returns seconds per step.
+        CUDA events on the launching stream, max over ranks.  Returns seconds per step.  With
+        `repeats` > 1 the timed region (the same `steps` calls, bracketed the same way) is run that many
+        times and the median is returned; `spread` receives min / median / max and the region's length.
 
         `period` consecutive calls (one pass over the rotating buffers) are captured once into a CUDA
         graph and replayed, so the figure is the device's, not the Python caller's launch rate."""
         for i in range(min(warmup, 3)):
             fn(i)
         torch.cuda.synchronize()
-        graph = None
+        graph = rem_graph = None
+        rem = steps % period if steps >= period else 0
+        if steps < period:
+            period, rem = steps, 0
+
+        def capture(n_calls, first):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(n_calls):
+                        fn(first + i)
+            torch.cuda.current_stream().wait_stream(side)
+            return g
+
         if use_graph:
             try:
-                side = torch.cuda.Stream()
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side):
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, stream=side):
-                        for i in range(period):
-                            fn(i)
-                torch.cuda.current_stream().wait_stream(side)
+                graph = capture(period, 0)
+                if rem:
+                    rem_graph = capture(rem, 0)  # the last `rem` of exactly `steps` timed calls
             except Exception:
-                graph = None
+                graph = rem_graph = None
                 torch.cuda.synchronize()
         if graph is None:
-            call, n_timed, n_warm, per = fn, steps, warmup, 1
+            n_steps = steps
+
+            def run_timed():
+                for i in range(steps):
+                    fn(warmup + i)
+
+            for i in range(warmup):
+                fn(i)
         else:
-            call, per = (lambda i: graph.replay()), period
-            n_timed, n_warm = max(1, -(-steps // period)), max(1, -(-warmup // period))
-        for i in range(n_warm):
-            call(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(n_timed):
-            call(n_warm + i)
-        e1.record()
-        barrier()
-        return max_over_ranks(e0.elapsed_time(e1) * 1e-3) / (n_timed * per)
+            n_full = steps // period
+            n_steps = n_full * period + rem  # == steps
+
+            def run_timed():
+                for _ in range(n_full):
+                    graph.replay()
+                if rem_graph is not None:
+                    rem_graph.replay()
+
+            for _ in range(max(1, -(-warmup // period))):
+                graph.replay()
+            if rem_graph is not None:
+                rem_graph.replay()
+        per_step = []
+        for _ in range(max(1, repeats)):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run_timed()
+            e1.record()
+            barrier()
+            per_step.append(max_over_ranks(e0.elapsed_time(e1) * 1e-3) / n_steps)
+        med = statistics.median(per_step)
+        if spread is not None:
+            spread.update({"repeats": len(per_step), "steps_per_repeat": n_steps, "us_min": min(per_step) * 1e6,
+                           "us_median": med * 1e6, "us_max": max(per_step) * 1e6,
+                           "timed_region_ms": med * n_steps * 1e3})
+        return med
 
     sampler = ClockSampler(local_rank)
 
@@ -378,14 +426,15 @@ def run_ours(args) -> None:
         pkg.mla_decode(q, caches[i % n_copies], seq_len, out=out, workspace=ws, max_seq_len=n_rows, ev_after_main=ev)
 
     sampler.start()
-    sec = time_loop(step, args.steps, args.warmup, period=n_copies)
+    spread = {}
+    sec = time_loop(step, args.steps, args.warmup, period=n_copies, repeats=args.repeats, spread=spread)
     value = world * bytes_step / sec / 1e9
 
     # ---- roofline pass: the attention kernel alone (combine skipped), same rotation, same graph replay ----
     def step_kernel_only(i):
         pkg.mla_decode(q, caches[i % n_copies], seq_len, out=out, workspace=ws, max_seq_len=n_rows, no_combine=True)
 
-    kern_sec = time_loop(step_kernel_only, min(args.steps, 2000), args.warmup, period=n_copies)
+    kern_sec = time_loop(step_kernel_only, min(args.steps, 2000), args.warmup, period=n_copies, repeats=args.repeats)
     achieved = bytes_step / kern_sec / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -419,17 +468,22 @@ def run_ours(args) -> None:
         lay.step(q_host, kv_host)
 
     e2e_steps = min(args.steps, 500)
-    for i in range(min(args.warmup, 20)):
+    # every layer records its graph on its first step: all of that happens here, before anything is timed
+    for i in range(max(2 * n_layers, min(args.warmup, 20))):
         e2e_step(i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    e2e_sec = max_over_ranks((time.perf_counter() - t0)) / e2e_steps
+    e2e_runs = []
+    for _ in range(max(1, args.repeats)):
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        torch.cuda.synchronize()
+        e2e_runs.append(max_over_ranks((time.perf_counter() - t0)) / e2e_steps)
+    e2e_sec = statistics.median(e2e_runs)
     clocks = sampler.stop()
     e2e = {"value": world * bytes_step / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "us_per_step": e2e_sec * 1e6, "steps": e2e_steps}
+           "d2h_bytes_per_step": d2h, "us_per_step": e2e_sec * 1e6, "steps": e2e_steps, "repeats": len(e2e_runs),
+           "us_min": min(e2e_runs) * 1e6, "us_max": max(e2e_runs) * 1e6}
     del layers
     torch.cuda.empty_cache()
 
@@ -452,12 +506,12 @@ def run_ours(args) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": "mtp_verify_32k: batch 1, T=2 causal, H=20, d_qk=576, d_v=512, ctx=32768, "
-                                   "scale=1/16; one independent sequence per GPU",
+            "config": {"workload": WORKLOAD, "replicas": "one independent sequence per GPU",
                        "launch": "one pass over the cache copies captured in a CUDA graph and replayed",
                        "l2": f"rotates over {n_copies} distinct cache copies ({n_copies * n_rows * D_QK * 2 >> 20} MiB "
                              "> 2 x L2)"},
             "e2e": e2e, "gpu_launches": 2 * args.steps, "launches_per_step": {"value": 2, "e2e": 3},
+            "timing": spread,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "others": others,
         }
         print(json.dumps(line), flush=True)
@@ -673,6 +727,8 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--repeats", type=int, default=15,
+                    help="how often the timed region of --steps steps is repeated (the median is reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the 128K / paged / prefill extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

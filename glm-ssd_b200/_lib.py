@@ -48,6 +48,7 @@ SIGNATURES = {
     "gs_mla_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
     "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_decode_static": (i32, [C.POINTER(DecodeArgs), vp]),
+    "gs_mla_decode_static_status": (i32, [C.POINTER(C.c_int32), vp]),
     "gs_mla_combine_parts": (i32, [vp, i32, i64, i32, i32, vp, vp]),
     "gs_shard_exchange_bytes": (i64, [i32, i32, i32]),
     "gs_peer_alloc": (i32, [C.POINTER(vp), i64]),
@@ -59,6 +60,8 @@ SIGNATURES = {
     "gs_rope_kv_append_at": (i32, [vp, vp, i64, i32, i32, i32, f32, vp]),
     "gs_norm_rope_kv_append_at": (i32, [vp, vp, f32, vp, i64, i32, i32, i32, f32, vp]),
     "gs_rope_kv_append": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "gs_prefill_attn_checked": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]),
+    "gs_rope_kv_append_checked": (i32, [vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp]),
     "gs_rope_f16_inplace": (i32, [vp, i32, i32, i32, i32, i64, f32, vp]),
     "gs_mla_layer_step_host": (i32, [C.POINTER(LayerStep), vp]),
     "gs_mla_layer_graph_create": (i32, [C.POINTER(LayerStep), vp, C.POINTER(vp)]),

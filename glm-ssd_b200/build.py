@@ -46,29 +46,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_host_check(force: bool = False) -> str:
-    """Compile the C++ host mirror's test driver (tests/host_check.cpp) against the library and the oracle."""
-    root = os.path.dirname(HERE)
-    exe = os.path.join(root, "tests", "host_check")
-    src = os.path.join(root, "tests", "host_check.cpp")
-    deps = [src, os.path.join(HERE, "host", "glmssd_host.hpp"), os.path.join(root, "include", "glmssd_attn.h")]
-    if not force and os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
-        return exe
-    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    if not os.path.exists(nvcc):
-        if os.path.exists(exe):
-            return exe
-        raise RuntimeError("nvcc not found; cannot build tests/host_check")
-    build()
-    sys.path.insert(0, root)
-    from oracle import build as obuild
-    obuild.build_oracle()
-    cmd = [nvcc, "-O2", "-std=c++17", "-x", "cu", "-o", exe, src, "-L" + HERE, "-lglmssd_attn",
-           "-L" + os.path.join(root, "oracle"), "-loracle",
-           "-Xlinker", "-rpath," + HERE, "-Xlinker", "-rpath," + os.path.join(root, "oracle")]
-    subprocess.check_call(cmd)
-    return exe
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

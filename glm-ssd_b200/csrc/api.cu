@@ -2,6 +2,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "internal.cuh"
@@ -130,7 +131,8 @@ struct AttnScratch {
     int t_max, h, max_rows;
 };
 static AttnScratch g_attn_scratch[64] = {};
-static std::mutex g_attn_scratch_mutex;  // the registry is the library's only mutable global besides the error text
+static std::mutex g_attn_scratch_mutex;  // guards the registry (the other mutable globals: the per-thread error text and
+                                          // the atomically cached addresses of the built-in scratch array further down)
 static constexpr int kAttnTensorTmax = 512;  // query tokens per call (decode, MTP verify, a prefill chunk)
 
 // Head groups per token, each a "sequence" of the dense kernel: groups of at most 48 heads, a multiple of 8 each;
@@ -186,7 +188,6 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     if (T <= 0 || H <= 0) return 0;
     if (!q || !C || !sel || !cnt || !o) return fail_invalid("gs_mla_attn: null pointer");
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
-    if (splits == 1 && !part) return fail_invalid("gs_mla_attn: this implementation needs `part` (T*H*(R+2) floats) also for splits == 1");
     DecodeProblem p{};
     if (int e = device_sm_count(&p.sm_count)) return e;
     // Tensor-core path, only when the caller registered a scratch for this device: the listed rows of every query
@@ -257,9 +258,10 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     p.tail_causal = 0;
     p.o = o;
     p.part_out = nullptr;
-    // caller's `part`: T*H*splits*(R+2) floats, used as [T*splits*H][R] accumulators then [T*splits*H][2] (m, l)
-    p.ws_acc = part;
-    p.ws_ml = part + (int64_t) T * splits * H * R;
+    // caller's `part`: T*H*splits*(R+2) floats (the size of ops.cu:578), used as [T*splits*H][R] accumulators then
+    // [T*splits*H][2] (m, l).  With splits == 1 it is never touched and may be NULL (ops.cu:531-538).
+    p.ws_acc = splits > 1 ? part : nullptr;
+    p.ws_ml = splits > 1 ? part + (int64_t) T * splits * H * R : nullptr;
     p.max_segments = (int64_t) T * splits;
     p.n_seq = 1;
     p.T = T;
@@ -295,8 +297,8 @@ GS_EXPORT int gs_mla_combine_parts(const float *parts, int n_parts, int64_t part
     return launch_combine(c, (cudaStream_t) stream);
 }
 
-GS_EXPORT int gs_prefill_attn(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d,
-                              int p0, float scale, int impl, void *stream) {
+static int prefill_attn(const char *who, const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d,
+                        int p0, float scale, int impl, int32_t *status, void *stream) {
     if (S < 0 || H < 0 || p0 < 0) return fail_invalid("gs_prefill_attn: negative size");
     if (S == 0 || H == 0) return 0;
     if (!q || !k || !v || !o) return fail_invalid("gs_prefill_attn: null pointer");
@@ -304,14 +306,25 @@ GS_EXPORT int gs_prefill_attn(const void *q, const void *k, const void *v, void 
     const char *why = "";
     const bool umma_ok = prefill_umma_supported(S, H, d, p0, &why);
     if (impl == 2 && !umma_ok) {
-        set_error("gs_prefill_attn: tcgen05 kernel does not take this shape: %s", why);
+        set_error("%s: tcgen05 kernel does not take this shape: %s", who, why);
         return (int) cudaErrorInvalidValue;
     }
     if (umma_ok && impl != 1)
         return launch_prefill_umma((const __half *) q, (const __half *) k, (const __half *) v, o, o_f16, S, H, d, p0,
-                                   scale, (cudaStream_t) stream);
+                                   scale, status, (cudaStream_t) stream);
     return launch_prefill_simt((const __half *) q, (const __half *) k, (const __half *) v, o, o_f16, S, H, d, p0, scale,
                                (cudaStream_t) stream);
+}
+
+GS_EXPORT int gs_prefill_attn(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d,
+                              int p0, float scale, int impl, void *stream) {
+    return prefill_attn("gs_prefill_attn", q, k, v, o, o_f16, S, H, d, p0, scale, impl, nullptr, stream);
+}
+
+GS_EXPORT int gs_prefill_attn_checked(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d,
+                                      int p0, float scale, int impl, int32_t *status, void *stream) {
+    if (!status) return fail_invalid("gs_prefill_attn_checked: status (device) is required");
+    return prefill_attn("gs_prefill_attn_checked", q, k, v, o, o_f16, S, H, d, p0, scale, impl, status, stream);
 }
 
 GS_EXPORT int gs_mla_decode_status(const void *workspace, int32_t *status_out, void *stream) {
@@ -332,7 +345,25 @@ GS_EXPORT int gs_mla_decode_status(const void *workspace, int32_t *status_out, v
 // the process exits.  In host code `g_static_scratch` is only a handle for the symbol, not a device
 // address; the address comes from cudaGetSymbolAddress, once per device, with that device current.
 static __device__ __align__(256) unsigned char g_static_scratch[GS_MLA_DECODE_STATIC_SCRATCH_BYTES];
-static void *g_static_scratch_ptr[64] = {nullptr};
+static std::atomic<void *> g_static_scratch_ptr[64];  // zero-initialised; racing first calls store the same address
+
+// Device address of the built-in array on the current device (looked up once per device).
+static int static_scratch_address(void **out, const char *who) {
+    int dev = 0;
+    GS_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("%s: device index beyond 63", who);
+        return (int) cudaErrorInvalidValue;
+    }
+    void *scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
+        // first call on this device (it is the current one): resolve the symbol to its device address
+        GS_TRY(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        g_static_scratch_ptr[dev].store(scratch, std::memory_order_release);
+    }
+    *out = scratch;
+    return 0;
+}
 
 GS_EXPORT int gs_mla_decode_static(const gs_mla_decode_args *a, void *stream) {
     if (!a) return fail_invalid("gs_mla_decode_static: args == NULL");
@@ -345,19 +376,18 @@ GS_EXPORT int gs_mla_decode_static(const gs_mla_decode_args *a, void *stream) {
                   (long long) need, (long long) GS_MLA_DECODE_STATIC_SCRATCH_BYTES);
         return (int) cudaErrorInvalidValue;
     }
-    int dev = 0;
-    GS_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail_invalid("gs_mla_decode_static: device index beyond 63");
-    void *scratch = g_static_scratch_ptr[dev];
-    if (!scratch) {
-        // first call on this device (it is the current one): resolve the symbol to its device address
-        GS_TRY(cudaGetSymbolAddress(&scratch, g_static_scratch));
-        g_static_scratch_ptr[dev] = scratch;
-    }
+    void *scratch = nullptr;
+    if (int e = static_scratch_address(&scratch, "gs_mla_decode_static")) return e;
     // the status block must start at zero; the partial records are fully rewritten before they are read
     GS_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes, (cudaStream_t) stream));
     gs_mla_decode_args b = *a;
     b.workspace = scratch;
     b.workspace_bytes = GS_MLA_DECODE_STATIC_SCRATCH_BYTES;
     return gs_mla_decode(&b, stream);
+}
+
+GS_EXPORT int gs_mla_decode_static_status(int32_t *status_out, void *stream) {
+    void *scratch = nullptr;
+    if (int e = static_scratch_address(&scratch, "gs_mla_decode_static_status")) return e;
+    return gs_mla_decode_status(scratch, status_out, stream);
 }

@@ -31,6 +31,7 @@ struct SimtParams {
     float scale;
     int tail_causal;
     float *ws_acc, *ws_ml;
+    float *o_direct;            // splits == 1: the normalised output [groups][H][d_v] is stored here and no record is written
     int T, H, d_qk, d_v, splits;
 };
 
@@ -181,6 +182,21 @@ __global__ void __launch_bounds__(NT) k_decode_gather(const SimtParams P) {
         }
         __syncthreads();
     }
+    if (P.o_direct) {
+        // a single split needs no merge: normalise here and leave the workspace alone, as the reference does
+        // (crates/cuda/kernels/ops.cu:531-538; zeros for a query that attends nothing)
+#pragma unroll
+        for (int h = 0; h < HG; h++) {
+            if (h < nh) {
+                const float l = s_l[h];
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                float *dst = P.o_direct + ((int64_t) bt * P.H + h0 + h) * d_v;
+                if (tid < d_v) dst[tid] = acc[h][0] * inv;
+                if (tid + NT < d_v) dst[tid + NT] = acc[h][1] * inv;
+            }
+        }
+        return;
+    }
     // one (acc, m, l) record per (sequence, token, split, head)
     const int64_t seg = (int64_t) bt * P.splits + split;
 #pragma unroll
@@ -328,7 +344,10 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
         if (splits < 1) splits = 1;
         if (splits > kSimtMaxSplits) splits = kSimtMaxSplits;
     }
-    if ((int64_t) groups * splits > p.max_segments) return fail_invalid("decode: workspace too small for the splits");
+    // One split and a plain output wanted: the kernel normalises and stores o itself, no record, no combine launch.
+    const bool direct = splits == 1 && p.o && !p.part_out && !p.exchange && !p.no_combine;
+    if (!direct && (int64_t) groups * splits > p.max_segments) return fail_invalid("decode: workspace too small for the splits");
+    if (!direct && (!p.ws_acc || !p.ws_ml)) return fail_invalid("decode: a workspace for the split records is required");
     SimtParams P;
     P.q = p.q;
     P.cache = p.cache;
@@ -343,6 +362,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     P.tail_causal = p.tail_causal;
     P.ws_acc = p.ws_acc;
     P.ws_ml = p.ws_ml;
+    P.o_direct = direct ? p.o : nullptr;
     P.T = p.T;
     P.H = p.H;
     P.d_qk = p.d_qk;
@@ -374,7 +394,7 @@ int launch_decode_simt(const DecodeProblem &p, cudaStream_t st) {
     if (e) return e;
     GS_TRY(cudaGetLastError());
     if (p.ev_after_main) GS_TRY(cudaEventRecord(p.ev_after_main, st));
-    if (p.no_combine) return 0;
+    if (p.no_combine || direct) return 0;
     CombinePlan c{};
     c.acc = p.ws_acc;
     c.ml = p.ws_ml;

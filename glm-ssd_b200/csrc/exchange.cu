@@ -5,7 +5,7 @@
 // (crates/cuda/kernels/ops.cu:539-574) with "split" = GPU.  The reference itself is single-GPU; this
 // path has no counterpart there.
 //
-// The records travel as 8-byte words {value, epoch}: an 8-byte store arrives whole, so a reader that
+// The records travel as 8-byte words {value, epoch}, each written and read by one 64-bit access, so a reader that
 // sees the call's epoch in a word also sees its value, and no memory fence or separate flag is needed
 // (a system-scope fence after peer stores costs several microseconds - more than the whole transfer).
 //
@@ -53,13 +53,16 @@ struct ExchangeParams {
     int32_t *status;
 };
 
+// One 64-bit scalar access per word (value in the low half, epoch in the high half): a scalar access of a naturally
+// aligned 8-byte word is single-copy atomic, a two-element vector access is only a pair of 4-byte accesses.
 __device__ __forceinline__ void st_word(uint2 *p, float v, uint32_t epoch) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+    const uint64_t w = (uint64_t) __float_as_uint(v) | ((uint64_t) epoch << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_word(const uint2 *p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+    uint64_t w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((uint32_t) w, (uint32_t) (w >> 32));
 }
 
 // Leaves the launch: with device-kept epochs the last block to finish advances the counter.

@@ -75,6 +75,6 @@ int launch_prefill_simt(const __half *q, const __half *k, const __half *v, void 
                         int p0, float scale, cudaStream_t st);
 bool prefill_umma_supported(int S, int H, int d, int p0, const char **why);
 int launch_prefill_umma(const __half *q, const __half *k, const __half *v, void *o, int o_f16, int S, int H, int d,
-                        int p0, float scale, cudaStream_t st);
+                        int p0, float scale, int32_t *status, cudaStream_t st);
 
 }  // namespace gs

@@ -358,7 +358,7 @@ bool prefill_umma_supported(int S, int H, int d, int p0, const char **why) {
 }
 
 int launch_prefill_umma(const __half *q, const __half *k, const __half *v, void *o, int o_f16, int S, int H, int d,
-                        int p0, float scale, cudaStream_t st) {
+                        int p0, float scale, int32_t *status, cudaStream_t st) {
     if (!(scale > 0.f)) return fail_invalid("prefill: the tcgen05 kernel needs a positive softmax scale");
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(o)) & 15)
@@ -376,7 +376,7 @@ int launch_prefill_umma(const __half *q, const __half *k, const __half *v, void 
     P.H = H;
     P.p0 = p0;
     P.scale_log2 = scale * 1.4426950408889634f;
-    P.status = nullptr;
+    P.status = status;  // may be nullptr: a wait that gives up is then not reported
     GS_TRY(cudaFuncSetAttribute(k_prefill_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
     dim3 grid((S + BM - 1) / BM, H);
     k_prefill_umma<<<grid, PF_THREADS, PF_SMEM, st>>>(P);

@@ -69,6 +69,10 @@ struct AppendParams {
     int T, d_row, d_rope;
     int32_t *len_out;  // optional: receives len_val (the sequence length after the append), for the decode that follows
     int32_t len_val;
+    // checked form (cache_rows > 0): a position, page-table slot or cache row out of range is not followed; the row is
+    // skipped and bit 17 of *status is set
+    int64_t cache_rows;
+    int32_t *status;
     RopeTable tab;
 };
 
@@ -78,13 +82,24 @@ __global__ void k_rope_append(const AppendParams P) {
     if (P.len_out && t == 0 && b == 0 && threadIdx.x == 0) *P.len_out = P.len_val;
     const int64_t pos = (P.pos0 ? (int64_t) P.pos0[b] : P.pos0_host) + t;
     int64_t row;
+    const bool checked = P.cache_rows > 0;
+    bool bad = checked && pos < 0;
     if (P.page_table) {
-        row = (int64_t) P.page_table[(int64_t) b * P.page_table_stride + pos / P.page_rows] * P.page_rows +
-              pos % P.page_rows;
+        const int64_t slot = pos / P.page_rows;
+        if (checked && (bad || slot >= P.page_table_stride)) {
+            bad = true;
+            row = 0;
+        } else {
+            row = (int64_t) P.page_table[(int64_t) b * P.page_table_stride + slot] * P.page_rows + pos % P.page_rows;
+        }
     } else if (P.pos0) {
         row = (P.seq_base ? (int64_t) P.seq_base[b] : 0) + pos;
     } else {
         row = t;  // host-position form: `cache` already points at the first new row
+    }
+    if (checked && (bad || row < 0 || row >= P.cache_rows)) {
+        if (threadIdx.x == 0) atomicOr(P.status, 1 << 17);
+        return;
     }
     const float *src = P.kv + ((int64_t) b * P.T + t) * P.d_row;
     __half *dst = P.cache + row * P.d_row;
@@ -315,6 +330,35 @@ GS_EXPORT int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos
     P.T = T;
     P.d_row = d_row;
     P.d_rope = d_rope;
+    fill_table(P.tab, d_rope, rope_base);
+    k_rope_append<<<dim3(T, n_seq), 128, 0, (cudaStream_t) stream>>>(P);
+    GS_TRY(cudaGetLastError());
+    return 0;
+}
+
+GS_EXPORT int gs_rope_kv_append_checked(const float *kv, void *cache, int64_t cache_rows, const int32_t *pos0,
+                                        const int32_t *seq_base, const int32_t *page_table, int page_table_stride,
+                                        int page_rows, int n_seq, int T, int d_row, int d_rope, float rope_base,
+                                        int32_t *status, void *stream) {
+    if (int e = check_rope(d_row, d_rope)) return e;
+    if (n_seq <= 0 || T <= 0) return 0;
+    if (!pos0 || !status) return fail_invalid("append: pos0 and status (device) are required");
+    if (cache_rows <= 0) return fail_invalid("append: cache_rows <= 0");
+    if (page_table && (page_rows <= 0 || page_table_stride <= 0)) return fail_invalid("append: page_rows and page_table_stride must be positive");
+    if (n_seq > 65535) return fail_invalid("append: n_seq > 65535");
+    AppendParams P{};
+    P.kv = kv;
+    P.cache = (__half *) cache;
+    P.pos0 = pos0;
+    P.seq_base = seq_base;
+    P.page_table = page_table;
+    P.page_table_stride = page_table_stride;
+    P.page_rows = page_rows > 0 ? page_rows : 1;
+    P.T = T;
+    P.d_row = d_row;
+    P.d_rope = d_rope;
+    P.cache_rows = cache_rows;
+    P.status = status;
     fill_table(P.tab, d_rope, rope_base);
     k_rope_append<<<dim3(T, n_seq), 128, 0, (cudaStream_t) stream>>>(P);
     GS_TRY(cudaGetLastError());

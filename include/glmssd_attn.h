@@ -7,7 +7,13 @@
  *   - calls only enqueue work on the caller's stream (`void *stream` is a cudaStream_t) and never
  *     synchronise; results are valid in stream order;
  *   - the caller owns all device memory, including workspaces; the library allocates nothing and
- *     keeps no state between calls (safe across cudaDeviceReset, cf. ops.cu:583-587).
+ *     keeps no state between calls (safe across cudaDeviceReset, cf. ops.cu:583-587) - except where an
+ *     entry point says otherwise.  Those are: gs_peer_alloc / gs_peer_open (allocate or map an exchange
+ *     buffer), gs_mla_layer_graph_create (allocates a handle with a recorded graph), and
+ *     gs_mla_decode_static (keeps the device address of its built-in scratch array per device).  After a
+ *     cudaDeviceReset (the engine's idle unload, runtime.cu:51-53) a layer-graph handle and every peer
+ *     mapping are gone with the context and must be created again, and gs_mla_decode_static must not
+ *     be used in a process that resets the device.
  * All pointers are device pointers unless a comment says "host".
  */
 #ifndef GLMSSD_ATTN_H
@@ -77,9 +83,13 @@ int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream);
  * reference, which is single-GPU.  All ranks must make the same call with the same epoch. */
 typedef struct gs_shard_exchange {
     int32_t world, rank;       /* 2..8 ranks */
-    uint32_t epoch;            /* 1, 2, 3, ... : strictly increasing from call to call, equal on all ranks; or 0
-                                  on every call of every rank: the epoch is then kept in the exchange buffers
-                                  themselves, which lets the call be captured in a CUDA graph and replayed */
+    uint32_t epoch;            /* 1, 2, 3, ... : consecutive - every call's epoch is the previous call's plus one, on
+                                  every rank (the record slots alternate with the epoch's parity, so a skipped
+                                  value would reuse the slot a slower rank is still reading and end in a wait
+                                  that runs out); or 0 on every call of every rank: the epoch is then kept in
+                                  the exchange buffers themselves, which lets the call be captured in a CUDA
+                                  graph and replayed.  After a call whose wait ran out (status bit 16), all
+                                  ranks carry on with the next consecutive epoch */
     void *const *peer_bufs;    /* host array [world]: every rank's exchange buffer as mapped in THIS process
                                   (gs_peer_alloc / gs_peer_export / gs_peer_open); peer_bufs[rank] is local */
     int64_t buf_bytes;         /* size of each buffer, >= gs_shard_exchange_bytes() */
@@ -148,6 +158,11 @@ int gs_mla_decode(const gs_mla_decode_args *args /* host */, void *stream);
  *   - Calls neither cudaMalloc nor cudaFree nor any allocating library routine. */
 #define GS_MLA_DECODE_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
 int gs_mla_decode_static(const gs_mla_decode_args *args /* host */, void *stream);
+/* gs_mla_decode_status for the built-in array of the current device (its address is not exposed): synchronises
+ * `stream`, reads the status word the last gs_mla_decode_static call left there and returns cudaErrorLaunchTimeout
+ * when a bounded wait inside the kernels gave up (the output of that call is then not valid).  Read it before the
+ * next gs_mla_decode_static call on the device: every call starts by clearing the word.  Allocates nothing. */
+int gs_mla_decode_static_status(int32_t *status_out /* host, may be NULL */, void *stream);
 
 /* Bytes of one rank's exchange buffer for `rows` = n_seq*T*H query rows (host function). */
 int64_t gs_shard_exchange_bytes(int world, int rows, int d_v);
@@ -176,6 +191,11 @@ int gs_mla_combine_parts(const float *parts, int n_parts, int64_t part_stride, i
  * ---------------------------------------------------------------------------------------------- */
 int gs_prefill_attn(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d, int p0,
                     float scale, int impl, void *stream);
+/* The same call with a status word: `status` is one int32 on the device, zeroed by the caller once; when a bounded
+ * wait inside the tcgen05 kernel gives up (o is then not valid) the kernel ORs a code into it instead of failing
+ * silently.  Read it with gs_mla_decode_status(status, ...), which treats any device word that way. */
+int gs_prefill_attn_checked(const void *q, const void *k, const void *v, void *o, int o_f16, int S, int H, int d, int p0,
+                            float scale, int impl, int32_t *status, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Fused RoPE + KV-append: replaces the gs_f32_to_f16 call of forward.rs:857-860 when the cache row
@@ -196,6 +216,13 @@ int gs_norm_rope_kv_append_at(const float *kv, const float *w, float eps, void *
 int gs_rope_kv_append(const float *kv, void *cache, const int32_t *pos0, const int32_t *seq_base,
                       const int32_t *page_table, int page_table_stride, int page_rows, int n_seq, int T, int d_row,
                       int d_rope, float rope_base, void *stream);
+/* gs_rope_kv_append that never follows a bad index: a negative position, a position beyond the sequence's
+ * page_table_stride * page_rows rows, or a cache row outside [0, cache_rows) writes nothing for that row and sets
+ * bit 17 of *status (one int32 on the device, zeroed by the caller once; read it with gs_mla_decode_status).
+ * gs_rope_kv_append itself trusts pos0, seq_base and the page table, as the reference trusts p0 (forward.rs:858). */
+int gs_rope_kv_append_checked(const float *kv, void *cache, int64_t cache_rows, const int32_t *pos0,
+                              const int32_t *seq_base, const int32_t *page_table, int page_table_stride, int page_rows,
+                              int n_seq, int T, int d_row, int d_rope, float rope_base, int32_t *status, void *stream);
 /* RoPE in place on f16 rows x [S][H][d] (prefill Q and K): last d_rope columns of every head at
  * position pos0 + s. */
 int gs_rope_f16_inplace(void *x, int S, int H, int d, int d_rope, int64_t pos0, float rope_base, void *stream);

@@ -382,6 +382,67 @@ int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const in
     return run_pool(dec_item, &c, (int64_t) n_seq * T * H, threads);
 }
 
+/* The same decode with the attended rows of every (sequence, token, head) cut into `key_splits` ranges by the
+ * reference's split rule (per = ceil(n / splits), ops.cu:447-449), one work item per range, merged by
+ * oracle_combine (ops.cu:558-573): the form that keeps every host core busy when n_seq*T*H is small.
+ * `scratch` holds n_seq*T*H*key_splits*(d_v+2) floats. */
+typedef struct {
+    dec_ctx_t d;
+    int key_splits;
+    float *scratch;
+} dec_split_ctx_t;
+
+static void dec_split_item(void *vctx, int64_t item) {
+    dec_split_ctx_t *sc = (dec_split_ctx_t *) vctx;
+    const dec_ctx_t *c = &sc->d;
+    const int ks = sc->key_splits;
+    const int64_t row_item = item / ks;
+    const int split = (int) (item % ks);
+    const int h = (int) (row_item % c->H);
+    const int t = (int) ((row_item / c->H) % c->T);
+    const int b = (int) (row_item / ((int64_t) c->H * c->T));
+    int64_t n = (int64_t) c->seq_lens[b] - (c->T - 1 - t);
+    if (n < 0) n = 0;
+    const int64_t per = (n + ks - 1) / ks;
+    const int64_t lo = split * per < n ? split * per : n;
+    const int64_t hi = lo + per < n ? lo + per : n;
+    const int64_t cnt = hi - lo;
+    float *qf = (float *) malloc(sizeof(float) * (size_t) c->d_qk);
+    oracle_f16_to_f32_array(c->q + (((int64_t) b * c->T + t) * c->H + h) * c->d_qk, qf, c->d_qk);
+    float *buf = (float *) malloc(sizeof(float) * (size_t) (cnt > 0 ? cnt : 1));
+    int32_t *rows = NULL;
+    int64_t row0 = 0;
+    if (c->page_table) {
+        rows = (int32_t *) malloc(sizeof(int32_t) * (size_t) (cnt > 0 ? cnt : 1));
+        const int32_t *pt = c->page_table + (int64_t) b * c->page_table_stride;
+        for (int64_t i = 0; i < cnt; i++) {
+            const int64_t pos = lo + i;
+            rows[i] = pt[pos / c->page_rows] * c->page_rows + (int32_t) (pos % c->page_rows);
+        }
+    } else {
+        row0 = (c->seq_base ? (int64_t) c->seq_base[b] : 0) + lo;
+    }
+    float *rec = sc->scratch + (row_item * ks + split) * (c->d_v + 2);
+    attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 0, rec,
+               rec + c->d_v, rec + c->d_v + 1, buf);
+    free(rows);
+    free(buf);
+    free(qf);
+}
+
+int oracle_mla_decode_split(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens, const int32_t *seq_base,
+                            const int32_t *page_table, int page_table_stride, int page_rows, float scale, float *o,
+                            int n_seq, int T, int H, int d_qk, int d_v, int key_splits, float *scratch, int threads) {
+    if (key_splits < 1) key_splits = 1;
+    dec_split_ctx_t c = {{q, cache, seq_lens, seq_base, page_table, page_table_stride, page_rows, scale, NULL, NULL, 0,
+                          0, n_seq, T, H, d_qk, d_v},
+                         key_splits, scratch};
+    const int64_t n_rows = (int64_t) n_seq * T * H;
+    const int used = run_pool(dec_split_item, &c, n_rows * key_splits, threads);
+    oracle_combine(scratch, n_rows, key_splits, d_v, o);
+    return used;
+}
+
 /* ------------------------------------------------------------------------------------------
  * Causal prefill attention, non-absorbed form.  The reference runs prefill through the same
  * absorbed kernel with T <= 256 queries and splits = 1 (forward.rs:61, :898-908); with
@@ -522,5 +583,130 @@ void oracle_dequant_q8(const int8_t *q, const uint16_t *d, uint16_t *out, int64_
     for (int64_t b = 0; b < n_blocks; b++) {
         const float dd = oracle_f16_to_f32(d[b]);
         for (int i = 0; i < 32; i++) out[b * 32 + i] = oracle_f32_to_f16(dd * (float) q[b * 32 + i]);
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * DSA k-pool indexer (crates/cuda/kernels/ops.cu:619-791): the kernels that produce the position
+ * lists (sel, cnt) the attention call consumes beyond top_k positions of context
+ * (crates/engine/src/forward.rs:864-895).
+ *
+ * oracle_idx_pool (ops.cu:622-672): raw indexer keys kc / gates gc of the chunk's T positions
+ * p0..p0+T-1, [T][Dk] f32; older positions of an unfinished pool live in the rings rk / rg
+ * ([kpool][Dk], row pos % kpool).  For every pool j of kpool positions that completes inside
+ * [p0, p0+T):  P[j][c] = sum_m softmax_m(gate[m][c] + ape[m][c]) * key[m][c]  (softmax over the pool's
+ * kpool positions, per column c); afterwards the rows of the trailing incomplete pool are copied
+ * into the rings.
+ * ------------------------------------------------------------------------------------------ */
+static inline const float *idx_row_cpu(const float *chunk, const float *ring, int64_t pos, int p0, int Dk, int kpool) {
+    return pos >= p0 ? chunk + (pos - p0) * Dk : ring + (pos % kpool) * Dk; /* ops.cu:622-625 */
+}
+
+void oracle_idx_pool(const float *kc, const float *gc, float *rk, float *rg, const float *ape, float *P, int p0, int T,
+                     int Dk, int kpool) {
+    const int end = p0 + T;
+    const int jf = p0 / kpool, jl = end / kpool; /* ops.cu:656-657 */
+    for (int64_t j = jf; j < jl; j++) {
+        for (int c = 0; c < Dk; c++) {
+            float mx = -INFINITY;
+            for (int m = 0; m < kpool; m++) {
+                const int64_t pos = j * kpool + m;
+                mx = fmaxf(mx, idx_row_cpu(gc, rg, pos, p0, Dk, kpool)[c] + ape[m * Dk + c]);
+            }
+            float sum = 0.f, acc = 0.f;
+            for (int m = 0; m < kpool; m++) {
+                const int64_t pos = j * kpool + m;
+                const float e = expf(idx_row_cpu(gc, rg, pos, p0, Dk, kpool)[c] + ape[m * Dk + c] - mx);
+                sum += e;
+                acc += e * idx_row_cpu(kc, rk, pos, p0, Dk, kpool)[c];
+            }
+            P[j * Dk + c] = acc / sum;
+        }
+    }
+    const int first = p0 > jl * kpool ? p0 : jl * kpool; /* ops.cu:662-666 */
+    for (int64_t pos = first; pos < end; pos++) {
+        for (int c = 0; c < Dk; c++) {
+            rk[(pos % kpool) * Dk + c] = kc[(pos - p0) * Dk + c];
+            rg[(pos % kpool) * Dk + c] = gc[(pos - p0) * Dk + c];
+        }
+    }
+}
+
+/* oracle_idx_score (ops.cu:675-712): score[t][p] = sum_h w[t][h] * relu(scale * q[t][h] . P[p]) for the
+ * p < (pos0 + t + 1) / kpool pools complete at query position pos0 + t; other entries are left alone. */
+void oracle_idx_score(const float *q, const float *w, const float *P, float *score, int64_t score_stride, int pos0, int T,
+                      int kpool, int Hq, int Dk, float scale) {
+    for (int t = 0; t < T; t++) {
+        const int n_pool = (pos0 + t + 1) / kpool;
+        for (int p = 0; p < n_pool; p++) {
+            float total = 0.f;
+            for (int h = 0; h < Hq; h++) {
+                const float *qh = q + ((int64_t) t * Hq + h) * Dk;
+                float d = 0.f;
+                for (int c = 0; c < Dk; c++) d += qh[c] * P[(int64_t) p * Dk + c];
+                total += w[(int64_t) t * Hq + h] * fmaxf(d * scale, 0.f);
+            }
+            score[(int64_t) t * score_stride + p] = total;
+        }
+    }
+}
+
+/* oracle_idx_select (ops.cu:714-791): the attended position list of query t (position pos = pos0 + t).
+ *   n_pool = (pos+1)/kpool <= top_k : every position 0..pos, cnt = pos + 1            (ops.cu:728-731)
+ *   else: the kpool positions of each of the top_k highest-scoring pools, then the positions of the
+ *         incomplete tail pool n_pool*kpool..pos; cnt = top_k*kpool + (pos + 1 - n_pool*kpool).
+ * Top-k is exact on the order-preserving uint32 image of the scores (ops.cu:718-721), i.e. all pools
+ * above the k-th largest value and as many of the pools equal to it as are still needed (ops.cu:770-777).
+ * The reference fills the slots in the order its threads reach an atomic counter, so neither the order of
+ * the pools inside the list nor which of several equal-valued pools are taken is fixed there; this
+ * restatement fixes both: pools in ascending index, ties to the lowest indices. */
+static inline uint32_t f2ord_cpu(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+static int cmp_u32_desc(const void *a, const void *b) {
+    const uint32_t x = *(const uint32_t *) a, y = *(const uint32_t *) b;
+    return x < y ? 1 : x > y ? -1 : 0;
+}
+
+void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T, int kpool, int top_k, int32_t *sel,
+                       int sel_stride, int32_t *cnt) {
+    for (int t = 0; t < T; t++) {
+        const int pos = pos0 + t;
+        const int n_pool = (pos + 1) / kpool;
+        int32_t *out = sel + (int64_t) t * sel_stride;
+        if (n_pool <= top_k) {
+            for (int i = 0; i <= pos; i++) out[i] = i;
+            cnt[t] = pos + 1;
+            continue;
+        }
+        const float *sc = score + (int64_t) t * score_stride;
+        uint32_t *ord = (uint32_t *) malloc(sizeof(uint32_t) * (size_t) n_pool);
+        for (int p = 0; p < n_pool; p++) ord[p] = f2ord_cpu(sc[p]);
+        uint32_t *sorted = (uint32_t *) malloc(sizeof(uint32_t) * (size_t) n_pool);
+        memcpy(sorted, ord, sizeof(uint32_t) * (size_t) n_pool);
+        qsort(sorted, (size_t) n_pool, sizeof(uint32_t), cmp_u32_desc);
+        const uint32_t U = sorted[top_k - 1]; /* the k-th largest value */
+        int above = 0;
+        for (int p = 0; p < n_pool; p++) above += ord[p] > U;
+        int need_eq = top_k - above, slot = 0;
+        for (int p = 0; p < n_pool; p++) {
+            int take = ord[p] > U;
+            if (ord[p] == U && need_eq > 0) {
+                take = 1;
+                need_eq--;
+            }
+            if (take) {
+                for (int m = 0; m < kpool; m++) out[slot * kpool + m] = p * kpool + m;
+                slot++;
+            }
+        }
+        const int base = top_k * kpool, tail0 = n_pool * kpool;
+        for (int i = 0; tail0 + i <= pos; i++) out[base + i] = tail0 + i;
+        cnt[t] = base + (pos + 1 - tail0);
+        free(sorted);
+        free(ord);
     }
 }

@@ -20,6 +20,11 @@ void oracle_combine(const float *part, int64_t n_rows, int n_parts, int d_v, flo
 int oracle_mla_decode(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens, const int32_t *seq_base,
                       const int32_t *page_table, int page_table_stride, int page_rows, float scale, float *o,
                       int n_seq, int T, int H, int d_qk, int d_v, int threads);
+/* oracle_mla_decode with every row's attended range cut into key_splits work items (all host cores busy); scratch:
+ * n_seq*T*H*key_splits*(d_v+2) floats */
+int oracle_mla_decode_split(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens, const int32_t *seq_base,
+                            const int32_t *page_table, int page_table_stride, int page_rows, float scale, float *o,
+                            int n_seq, int T, int H, int d_qk, int d_v, int key_splits, float *scratch, int threads);
 int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const int32_t *seq_lens,
                               const int32_t *seq_base, const int32_t *page_table, int page_table_stride,
                               int page_rows, float scale, float *parts, int64_t part_lo, int64_t part_hi, int n_seq,
@@ -33,6 +38,14 @@ void oracle_rope_append(const float *x, uint16_t *y, int T, int d_row, int d_rop
 void oracle_norm_rope_append(const float *x, const float *w, float eps, uint16_t *y, int T, int d_row, int d_rope,
                              int64_t pos0, double base);
 void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base);
+
+/* DSA k-pool indexer (ops.cu:619-791) */
+void oracle_idx_pool(const float *kc, const float *gc, float *rk, float *rg, const float *ape, float *P, int p0, int T,
+                     int Dk, int kpool);
+void oracle_idx_score(const float *q, const float *w, const float *P, float *score, int64_t score_stride, int pos0, int T,
+                      int kpool, int Hq, int Dk, float scale);
+void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T, int kpool, int top_k, int32_t *sel,
+                       int sel_stride, int32_t *cnt);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,8 @@ def lib() -> C.CDLL:
     L.oracle_combine.argtypes = [vp, i64, i32, i32, vp]
     L.oracle_mla_decode.restype = i32
     L.oracle_mla_decode.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp, i32, i32, i32, i32, i32, i32]
+    L.oracle_mla_decode_split.restype = i32
+    L.oracle_mla_decode_split.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp, i32, i32, i32, i32, i32, i32, vp, i32]
     L.oracle_mla_decode_partial.restype = i32
     L.oracle_mla_decode_partial.argtypes = [vp, vp, vp, vp, vp, i32, i32, f32, vp, i64, i64, i32, i32, i32, i32, i32,
                                             i32]
@@ -102,9 +104,11 @@ def combine(parts: np.ndarray) -> np.ndarray:
 
 
 def mla_decode(q, cache, seq_lens, scale, d_v=512, seq_base=None, page_table=None, page_rows=64, threads=0,
-               part_range=None, return_threads=False):
+               part_range=None, return_threads=False, key_splits=0):
     """q f16 [n_seq,T,H,d_qk]; cache f16 [rows,d_qk].  Returns o f32 [n_seq,T,H,d_v], or with
-    ``part_range=(lo, hi)`` the unnormalised records f32 [n_seq,T,H,d_v+2] over rows lo..hi."""
+    ``part_range=(lo, hi)`` the unnormalised records f32 [n_seq,T,H,d_v+2] over rows lo..hi.
+    ``key_splits > 1`` cuts every row's attended range into that many work items (merged by the reference's
+    combine arithmetic), so that all host cores work when n_seq*T*H is small."""
     qb = f16_bits(q)
     n_seq, T, H, d_qk = qb.shape
     cb = f16_bits(cache)
@@ -112,7 +116,12 @@ def mla_decode(q, cache, seq_lens, scale, d_v=512, seq_base=None, page_table=Non
     sb = None if seq_base is None else _c(seq_base, np.int32)
     pt = None if page_table is None else _c(page_table, np.int32)
     pts = 0 if pt is None else pt.shape[1]
-    if part_range is None:
+    if part_range is None and key_splits > 1:
+        o = np.empty((n_seq, T, H, d_v), np.float32)
+        scratch = np.empty((n_seq * T * H * key_splits, d_v + 2), np.float32)
+        used = lib().oracle_mla_decode_split(_p(qb), _p(cb), _p(seq_lens), _p(sb), _p(pt), pts, page_rows, scale, _p(o),
+                                             n_seq, T, H, d_qk, d_v, key_splits, _p(scratch), threads)
+    elif part_range is None:
         o = np.empty((n_seq, T, H, d_v), np.float32)
         used = lib().oracle_mla_decode(_p(qb), _p(cb), _p(seq_lens), _p(sb), _p(pt), pts, page_rows, scale, _p(o),
                                        n_seq, T, H, d_qk, d_v, threads)

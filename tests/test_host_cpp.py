@@ -10,8 +10,8 @@ BIN = os.path.join(ROOT, "tests", "host_check")
 
 
 def _build():
-    import importlib
-    return importlib.import_module("glm-ssd_b200.build").build_host_check()
+    from build_host_check import build_host_check
+    return build_host_check()
 
 
 def test_host_mirror_compiles_and_checks_arguments():

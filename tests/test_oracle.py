@@ -233,3 +233,15 @@ def test_norm_rope_append_matches_float64_numpy(oracle):
     # the rotated columns are those of the plain RoPE append
     plain = oracle.rope_append(x, 100).astype(np.float64)
     assert np.array_equal(got[:, 512:], plain[:, 512:])
+
+
+def test_decode_cut_into_key_ranges_equals_the_plain_decode(oracle):
+    """oracle_mla_decode_split (every row's attended range cut by the reference's split rule, ops.cu:447-449, and
+    merged by its combine arithmetic, ops.cu:558-573) against the single-pass decode: same result to rounding."""
+    rng = np.random.default_rng(17)
+    for n, T, ks in ((1000, 2, 7), (64, 1, 3), (5, 2, 8), (0, 1, 4)):
+        q = rng.standard_normal((1, T, 3, 576), dtype=np.float32).astype(np.float16)
+        cache = (rng.standard_normal((max(n, 1), 576), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+        a = oracle.mla_decode(q, cache, [n], 1 / 16)
+        b = oracle.mla_decode(q, cache, [n], 1 / 16, key_splits=ks)
+        assert np.abs(a - b).max() <= 2e-6, (n, T, ks, np.abs(a - b).max())

@@ -66,6 +66,48 @@ def test_gs_mla_attn_prefill_shape(pkg, cuda, oracle):
     check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "prefill via gs_mla_attn")
 
 
+ENGINE_PART_FLOATS = 128 * (16 * 512 + 32)  # the engine's `part` allocation (crates/engine/src/forward.rs:498)
+
+
+@pytest.mark.parametrize("T,H,splits", [(256, 64, 1), (8, 64, 4), (1, 64, 16), (2, 64, 4)])
+def test_gs_mla_attn_stays_inside_the_engines_part_buffer(pkg, cuda, oracle, T, H, splits):
+    """The engine passes one `part` buffer of 128 * (16*512 + 32) floats to every call: decode (T = 1, 16 splits),
+    MTP verify (T = 2, 4 splits), chunks of up to 8 tokens with 4 splits, and prefill chunks of up to 256 tokens
+    with splits = 1, where the reference never touches it (ops.cu:531-538).  A canary tail behind the usable part
+    of the allocation must come back unchanged, and with splits = 1 the buffer itself too."""
+    torch = cuda
+    n = 300
+    q, Cc, sel, cnt = _legacy_inputs(T + 31 * splits, T, H, n, n + 50, dense=False)
+    qd, cd, sd, nd = to_dev(torch, q), to_dev(torch, Cc), to_dev(torch, sel), to_dev(torch, cnt)
+    o = torch.zeros((T, H, 512), dtype=torch.float32, device="cuda")
+    tail = 1 << 16
+    part = torch.full((ENGINE_PART_FLOATS + tail,), -7.25, dtype=torch.float32, device="cuda")
+    rc = pkg._lib.load().gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16,
+                                     o.data_ptr(), part.data_ptr(), T, H, 512, splits, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert bool((part[ENGINE_PART_FLOATS:] == -7.25).all()), "gs_mla_attn wrote past the engine's part buffer"
+    if splits == 1:
+        assert bool((part == -7.25).all()), "part must not be touched when splits == 1"
+    check_close(o.cpu().numpy(), oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "gs_mla_attn (engine part buffer)")
+
+
+def test_gs_mla_attn_single_split_takes_null_part(pkg, cuda, oracle):
+    torch = cuda
+    T, H, n = 40, 16, 120
+    q, Cc, sel, cnt = _legacy_inputs(3, T, H, n, n + 9, dense=True)
+    qd, cd, sd, nd = to_dev(torch, q), to_dev(torch, Cc), to_dev(torch, sel), to_dev(torch, cnt)
+    o = torch.zeros((T, H, 512), dtype=torch.float32, device="cuda")
+    L = pkg._lib.load()
+    assert L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16, o.data_ptr(),
+                         None, T, H, 512, 1, None) == 0
+    torch.cuda.synchronize()
+    check_close(o.cpu().numpy(), oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "gs_mla_attn, part == NULL")
+    # more than one split still needs the buffer
+    assert L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16, o.data_ptr(),
+                         None, T, H, 512, 4, None) == 1
+
+
 def test_gs_f32_to_f16_bit_exact(pkg, cuda, oracle):
     rng = np.random.default_rng(2)
     x = np.concatenate([rng.standard_normal(512 * 5 + 3).astype(np.float32) * s for s in (1e-7, 1.0, 1e3)])

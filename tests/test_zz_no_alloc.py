@@ -47,6 +47,12 @@ def test_static_scratch_matches_workspace_entry_point_twice(pkg, cuda, oracle):
         rc = L.gs_mla_decode_static(C.byref(_args(pkg, cuda, qd, cd, lens, o_static)), None)
         assert rc == 0, L.gs_attn_last_error_string()
         assert cuda.cuda.memory_allocated() == before  # nothing went through torch's allocator either
+        # the built-in array's address is not exposed: its status word is read through an accessor of its own,
+        # before the next call clears it
+        st = C.c_int32(-1)
+        assert L.gs_mla_decode_static_status(C.byref(st), None) == 0, L.gs_attn_last_error_string()
+        assert st.value == 0
+        assert cuda.cuda.memory_allocated() == before
         rc = L.gs_mla_decode(C.byref(_args(pkg, cuda, qd, cd, lens, o_ws, ws)), None)
         assert rc == 0, L.gs_attn_last_error_string()
         cuda.cuda.synchronize()
