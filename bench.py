@@ -266,7 +266,7 @@ def _sparse_list_shape(torch, dev, fn, label, scratch=None):
         sel = torch.stack([torch.randperm(ctx, device=dev)[:n].sort().values for _ in range(T)]).int().contiguous()
         cnt = torch.full((T,), n, dtype=torch.int32, device=dev)
         o = torch.empty((T, Hh, 512), dtype=torch.float32, device=dev)
-        part = torch.empty(T * Hh * splits * 514 + 1024, dtype=torch.float32, device=dev)
+        part = torch.empty(T * Hh * splits * 514, dtype=torch.float32, device=dev)  # the reference's size (ops.cu:578)
 
         def call(i):
             rc = fn(q.data_ptr(), caches[i % 6].data_ptr(), None, sel.data_ptr(), n, cnt.data_ptr(), SCALE, o.data_ptr(),
@@ -514,6 +514,17 @@ def run_ours(args) -> None:
             "timing": spread,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "others": others,
         }
+        # the sharded configurations once more, short and at the very end of the line
+        if isinstance(others, dict) and "ctx128k_T1" in others:
+            c3, p5 = others["ctx128k_T1"], others.get("paged64", {})
+            line["sharded"] = {
+                "n_gpus": world, "ctx128k_us": round(c3["us_per_step"], 2),
+                "ctx128k_frac_per_gpu": round(c3["frac_of_hbm_per_gpu"], 3),
+                "ctx128k_nccl_us": round(others["ctx128k_T1_nccl"]["us_per_step"], 2) if "ctx128k_T1_nccl" in others else None,
+                "paged64_us": round(p5.get("us_per_step", 0.0), 2), "paged64_frac_per_gpu": round(p5.get("frac_of_hbm_per_gpu", 0.0), 3),
+                "exchange": "none" if world == 1 else ("p2p" if "ctx128k_T1_p2p_error" not in others else "nccl"),
+                "max_abs_vs_1gpu": others.get("sharded_max_abs_vs_1gpu"),
+            }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -532,6 +543,8 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     n_copies = min(n_copies, 24)
     shards = [randn_f16((max(rows_local, 1), D_QK), 0.5) for _ in range(n_copies)]
     q1 = randn_f16((1, 1, H, D_QK))
+    if world > 1:
+        dist.broadcast(q1, src=0)  # one query for the whole sharded context
     lens = torch.tensor([rows_local], dtype=torch.int32, device=dev)
     ws = pkg.new_workspace(1, 1, H, D_V, dev)
     rows_q = H
@@ -564,8 +577,33 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
             if int(ok.item()) != 1:
                 raise RuntimeError("a rank reported an exchange time-out")
             exchange = "peer-to-peer stores of the (acc, m, l) records as {value, epoch} words, merged in one kernel (CUDA graph)"
+            # Outside the timed region: one more exchanged step on the first shard copies, checked on EVERY rank against
+            # the single-GPU decode of the concatenated shards (all-gathered once for the check)
+            o1.zero_()
+            xk = ex.next(device_epoch=True)
+            pkg.mla_decode(q1, shards[0], lens, tail_causal=(rank == world - 1), out=o1, workspace=ws, max_seq_len=rows_local, exchange=xk)
+            torch.cuda.synchronize()
+            if pkg.decode_status(ws) != 0:
+                raise RuntimeError("exchange time-out in the checked step")
+            sizes = [pkg.shard_rows(n_total, world, r, 16) for r in range(world)]
+            if len({hi_ - lo_ for lo_, hi_ in sizes}) != 1:
+                raise RuntimeError("shards of unequal size: the check gathers equal shards")
+            whole = torch.empty((n_total, D_QK), dtype=torch.float16, device=dev)
+            dist.all_gather_into_tensor(whole, shards[0])
+            o_one = torch.empty_like(o1)
+            pkg.mla_decode(q1, whole, torch.tensor([n_total], dtype=torch.int32, device=dev), out=o_one,
+                           workspace=pkg.new_workspace(1, 1, H, D_V, dev), max_seq_len=n_total)
+            torch.cuda.synchronize()
+            err = (o1 - o_one).abs().max().reshape(1).double()
+            dist.all_reduce(err, op=dist.ReduceOp.MAX)
+            res["sharded_max_abs_vs_1gpu"] = float(err.item())
+            del whole
             dist.barrier()
             ex.close()
+            if not (float(err.item()) <= 2e-3):
+                print(json.dumps({"error": f"sharded 128K decode differs from the single-GPU result by {float(err.item()):.3e} (> 2e-3)"}),
+                      flush=True)
+                raise SystemExit(1)
         except Exception as exc:
             res["ctx128k_T1_p2p_error"] = f"{type(exc).__name__}: {exc}"
             sec = None
@@ -583,6 +621,12 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
         sec_nccl = time_loop(sharded_step, steps, warm, period=n_copies)
         res["ctx128k_T1_nccl"] = {"us_per_step": sec_nccl * 1e6, "value": total_bytes / sec_nccl / 1e9,
                                   "exchange": "nccl all_gather of (acc, m, l) records + local combine (CUDA graph)"}
+        if sec is not None:  # both paths on the first shard copies: the all-gather path against the checked peer-to-peer result
+            sharded_step(0)
+            torch.cuda.synchronize()
+            d = (o2.view(-1) - o1.view(-1)).abs().max().reshape(1).double()
+            dist.all_reduce(d, op=dist.ReduceOp.MAX)
+            res["ctx128k_T1_nccl"]["max_abs_vs_p2p"] = float(d.item())
         if sec is None:
             sec, exchange = sec_nccl, res["ctx128k_T1_nccl"]["exchange"]
     gbs = total_bytes / sec / 1e9
@@ -647,17 +691,18 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
         torch.cuda.empty_cache()
     res["twin_R512"] = twin
 
-    # -- the engine's sparse decode shape through gs_mla_attn: CUDA-core kernel, then the tensor-core path -----
+    # -- the engine's sparse decode shape through gs_mla_attn: CUDA-core kernel, then the automatic choice (tcgen05 kernel
+    #    fed from the position lists by gather copies; nothing beyond the reference's own arguments) -------------------
     try:
         fn = pkg._lib.load().gs_mla_attn
-        sp = _sparse_list_shape(torch, dev, fn, "cuda_core")
-        scratch = pkg.mla_attn_scratch(256, 64, 2060, dev)
+        pkg.mla_attn_impl(1)
         try:
-            sp.update(_sparse_list_shape(torch, dev, fn, "tensor_path"))
-            torch.cuda.synchronize()
+            sp = _sparse_list_shape(torch, dev, fn, "cuda_core")
         finally:
-            pkg.mla_attn_scratch_off()
-        del scratch
+            pkg.mla_attn_impl(0)
+        sp.update(_sparse_list_shape(torch, dev, fn, "tensor_path"))
+        torch.cuda.synchronize()
+        sp["tensor_path_status"] = pkg.mla_attn_status()
         res["gs_mla_attn_sparse"] = sp
     except Exception as exc:
         res["gs_mla_attn_sparse"] = {"error": f"{type(exc).__name__}: {exc}"}
@@ -712,6 +757,10 @@ def run_profile_case(name: str) -> None:
         for i in range(4):
             pkg.mla_decode(q, pool, torch.from_numpy(lens_h.astype(np.int32)).to(dev), page_table=torch.from_numpy(pt).to(dev),
                            out=out, workspace=ws, max_seq_len=int(lens_h.max()))
+    elif name == "sparse":
+        # the engine's sparse decode shape through the reference's entry point: 64 heads, 2052 listed rows per token
+        fn = pkg._lib.load().gs_mla_attn
+        _sparse_list_shape(torch, dev, fn, "profile")
     else:
         S, Hh = 4096, 8
         Q, K, V = (torch.randn((S, Hh, 256), device=dev).half() for _ in range(3))
@@ -732,7 +781,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the 128K / paged / prefill extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["decode32k", "decode128k", "paged", "prefill"],
+    ap.add_argument("--profile-case", default=None, choices=["decode32k", "decode128k", "paged", "prefill", "sparse"],
                     help="run a handful of eager launches of one kernel on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.warmup < 3:

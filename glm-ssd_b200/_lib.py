@@ -39,15 +39,29 @@ class DecodeArgs(C.Structure):
 
 
 # name -> (restype, argtypes); every symbol include/glmssd_attn.h declares
+class FusedArgs(C.Structure):
+    """gs_mla_fused_args of include/glmssd_attn.h."""
+    _fields_ = [("q", vp), ("k_b", vp), ("v_b", vp), ("cache", vp), ("cache_rows", i64), ("seq_len", vp), ("scale", f32),
+                ("ov", vp), ("workspace", vp), ("workspace_bytes", i64), ("T", i32), ("H", i32), ("d_q", i32), ("d_lat", i32),
+                ("d_out", i32)]
+
+
 SIGNATURES = {
     "gs_mla_attn": (i32, [vp, vp, vp, vp, i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]),
     "gs_f32_to_f16": (i32, [vp, vp, i64, vp]),
     "gs_quant_q8_rows": (i32, [vp, vp, vp, i64, vp]),
-    "gs_mla_attn_scratch_bytes": (i64, [i32, i32, i32]),
-    "gs_mla_attn_set_scratch": (i32, [vp, i64, i32, i32, i32, vp]),
+    "gs_idx_pool": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "gs_idx_score": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp]),
+    "gs_idx_select": (i32, [vp, i64, i32, i32, i32, i32, vp, i32, vp, vp]),
+    "gs_cache_export_rows": (i32, [vp, i64, vp, i32, i32, i64, i64, i32, vp, vp, vp]),
+    "gs_cache_import_rows": (i32, [vp, i64, vp, i32, i32, i64, i64, i32, vp, vp, vp]),
+    "gs_mla_attn_set_impl": (i32, [i32]),
+    "gs_mla_attn_status": (i32, [C.POINTER(C.c_int32), vp]),
     "gs_mla_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
     "gs_mla_decode": (i32, [C.POINTER(DecodeArgs), vp]),
     "gs_mla_decode_static": (i32, [C.POINTER(DecodeArgs), vp]),
+    "gs_mla_fused_workspace_bytes": (i64, [i32, i32]),
+    "gs_mla_decode_fused": (i32, [C.POINTER(FusedArgs), vp]),
     "gs_mla_decode_static_status": (i32, [C.POINTER(C.c_int32), vp]),
     "gs_mla_combine_parts": (i32, [vp, i32, i64, i32, i32, vp, vp]),
     "gs_shard_exchange_bytes": (i64, [i32, i32, i32]),

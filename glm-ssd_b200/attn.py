@@ -45,20 +45,16 @@ def mla_attn(q, C_latent, C_scales, sel, sel_stride, cnt, scale, o, part, T, H, 
                              _ptr(o), _ptr(part), T, H, R, splits, _stream()), "gs_mla_attn")
 
 
-def mla_attn_scratch(t_max: int, H: int, max_rows: int, device=None):
-    """Allocates and registers the scratch that switches ``gs_mla_attn`` to its tensor-core path on the current
-    device; returns the tensor (keep it alive).  ``mla_attn_scratch_off()`` unregisters."""
-    L = _lib.load()
-    n = int(L.gs_mla_attn_scratch_bytes(t_max, H, max_rows))
-    if n <= 0:
-        raise ValueError("sizes outside the tensor-core path (1 <= t_max <= 512, heads in groups of 8..48)")
-    buf = torch.zeros(n, dtype=torch.uint8, device=device or torch.cuda.current_device())
-    _lib.check(L.gs_mla_attn_set_scratch(buf.data_ptr(), n, t_max, H, max_rows, _stream()), "gs_mla_attn_set_scratch")
-    return buf
+def mla_attn_impl(impl: int) -> None:
+    """Kernel choice of ``gs_mla_attn``: 0 automatic, 1 CUDA-core kernel (f32 queries stay f32), 2 tcgen05 kernel or error."""
+    _lib.check(_lib.load().gs_mla_attn_set_impl(impl), "gs_mla_attn_set_impl")
 
 
-def mla_attn_scratch_off():
-    _lib.check(_lib.load().gs_mla_attn_set_scratch(None, 0, 0, 0, 0, _stream()), "gs_mla_attn_set_scratch")
+def mla_attn_status() -> int:
+    """Synchronises and returns the sticky status word of the tcgen05 path of ``gs_mla_attn`` (0 = ok)."""
+    st = C.c_int32(0)
+    _lib.load().gs_mla_attn_status(C.byref(st), _stream())
+    return int(st.value)
 
 
 def f32_to_f16(x, y, n):

@@ -122,61 +122,26 @@ GS_EXPORT int gs_mla_decode(const gs_mla_decode_args *a, void *stream) {
     return launch_decode_simt(p, (cudaStream_t) stream);
 }
 
-// ---- optional tensor-core path of the reference-compatible entry point ------------------------------------
-// Scratch registered by the caller, per device (G = head groups per token): [workspace of a decode with
-// n_seq = G T_max, T = 1, H/G heads][lens G T_max][bases G T_max][queries f16 T_max*H*512][rows T_max*max_rows*512 f16].
-struct AttnScratch {
-    void *ptr;
-    int64_t bytes;
-    int t_max, h, max_rows;
-};
-static AttnScratch g_attn_scratch[64] = {};
-static std::mutex g_attn_scratch_mutex;  // guards the registry (the other mutable globals: the per-thread error text and
-                                          // the atomically cached addresses of the built-in scratch array further down)
-static constexpr int kAttnTensorTmax = 512;  // query tokens per call (decode, MTP verify, a prefill chunk)
+// ---- kernel choice of the reference-compatible entry point ---------------------------------------------------
+// 0 = automatic (the tcgen05 kernel whenever it takes the shape), 1 = always the CUDA-core kernel (bit-level second
+// opinion: f32 queries stay f32), 2 = the tcgen05 kernel or an error.  A process-wide setting, read once per call.
+static std::atomic<int> g_attn_impl{0};
 
-// Head groups per token, each a "sequence" of the dense kernel: groups of at most 48 heads, a multiple of 8 each;
-// 0 when the head count cannot be cut that way.
-static int attn_head_groups(int H) {
-    const int n = (H + 47) / 48;
-    return (n > 0 && H % n == 0 && (H / n) % 8 == 0) ? n : 0;
+GS_EXPORT int gs_mla_attn_set_impl(int impl) {
+    if (impl < 0 || impl > 2) return fail_invalid("gs_mla_attn_set_impl: impl must be 0, 1 or 2");
+    g_attn_impl.store(impl, std::memory_order_relaxed);
+    return 0;
 }
 
-static int64_t attn_scratch_layout(int t_max, int H, int max_rows, int64_t *off_lens, int64_t *off_q, int64_t *off_rows) {
-    const int ng = attn_head_groups(H) > 0 ? attn_head_groups(H) : 1;
-    const int64_t ws = ws_layout(t_max * ng, 1, H / ng, 512).total;
-    const int64_t lens = ws, q16 = align_up(lens + 2 * (int64_t) t_max * ng * 4, 256);
-    const int64_t rows = align_up(q16 + (int64_t) t_max * H * 512 * 2, 256);
-    if (off_lens) *off_lens = lens;
-    if (off_q) *off_q = q16;
-    if (off_rows) *off_rows = rows;
-    return align_up(rows + (int64_t) t_max * max_rows * 512 * 2, 256);
-}
-
-GS_EXPORT int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows) {
-    if (t_max <= 0 || t_max > kAttnTensorTmax || H <= 0 || max_rows <= 0 || attn_head_groups(H) == 0) return 0;
-    if ((int64_t) t_max * attn_head_groups(H) > 1024 || (int64_t) t_max * max_rows >= (1ll << 31)) return 0;
-    return attn_scratch_layout(t_max, H, max_rows, nullptr, nullptr, nullptr);
-}
-
-GS_EXPORT int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream) {
-    int dev = 0;
-    GS_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail_invalid("gs_mla_attn_set_scratch: device index beyond 63");
-    if (!scratch) {
-        std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
-        g_attn_scratch[dev] = AttnScratch{};
-        return 0;
+GS_EXPORT int gs_mla_attn_status(int32_t *status_out, void *stream) {
+    GS_TRY(cudaStreamSynchronize((cudaStream_t) stream));
+    int32_t st = 0;
+    if (int e = read_list_status(&st)) return e;
+    if (status_out) *status_out = st;
+    if (st != 0) {
+        set_error("gs_mla_attn: a bounded wait inside the tcgen05 kernel gave up (status 0x%x)", st);
+        return (int) cudaErrorLaunchTimeout;
     }
-    const int64_t need = gs_mla_attn_scratch_bytes(t_max, H, max_rows);
-    if (need <= 0 || bytes < need || (reinterpret_cast<uintptr_t>(scratch) & 255)) {
-        set_error("gs_mla_attn_set_scratch: need %lld bytes, 256-byte aligned, 1 <= t_max <= %d, H in groups of 8..48 heads (given %lld)", (long long) need,
-                  kAttnTensorTmax, (long long) bytes);
-        return (int) cudaErrorInvalidValue;
-    }
-    GS_TRY(cudaMemsetAsync(scratch, 0, kStatusBytes, (cudaStream_t) stream));  // sticky status block starts clean
-    std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
-    g_attn_scratch[dev] = AttnScratch{scratch, bytes, t_max, H, max_rows};
     return 0;
 }
 
@@ -190,61 +155,16 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
     DecodeProblem p{};
     if (int e = device_sm_count(&p.sm_count)) return e;
-    // Tensor-core path, only when the caller registered a scratch for this device: the listed rows of every query
-    // token are gathered into contiguous rows and the queries rounded to f16, then each token is one dense
-    // "sequence" of the tcgen05 kernel.  (A decode or MTP-verify call: few tokens, a few thousand rows each.)
-    int dev = 0;
-    GS_TRY(cudaGetDevice(&dev));
-    AttnScratch sc{};
-    if (dev >= 0 && dev < 64) {
-        std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
-        sc = g_attn_scratch[dev];
+    // f16 cache: the tcgen05 kernel reads the listed rows four at a time with gather copies and rounds the queries to
+    // f16 itself; it needs nothing beyond the reference's own arguments.  Q8 caches and shapes it does not take run on
+    // the CUDA-core kernel below.
+    const int impl = g_attn_impl.load(std::memory_order_relaxed);
+    if (!C_scales && impl != 1) {
+        const int e = launch_decode_umma_list(q, (const __half *) C, sel, sel_stride, cnt, scale, o, part, T, H, R, splits,
+                                              p.sm_count, (cudaStream_t) stream);
+        if (e >= 0) return e;
     }
-    if (sc.ptr && T <= sc.t_max && H == sc.h && sel_stride > 0 && sel_stride <= sc.max_rows && scale > 0.f &&
-        !(reinterpret_cast<uintptr_t>(C) & 15)) {
-        int64_t off_lens, off_q, off_rows;
-        attn_scratch_layout(sc.t_max, sc.h, sc.max_rows, &off_lens, &off_q, &off_rows);
-        char *base = (char *) sc.ptr;
-        const int n_groups = attn_head_groups(H);  // > 0: checked when the scratch was registered
-        int32_t *lens = (int32_t *) (base + off_lens), *bases = lens + sc.t_max * n_groups;
-        __half *q16 = (__half *) (base + off_q), *rows = (__half *) (base + off_rows);
-        // More than 48 heads: every group of Hg heads of a token becomes a sequence of its own over the same rows
-        // (q [T][H][R] and o [T][H][R] are [T * groups][Hg][R] as they lie), so one launch covers all of them.
-        const int Hg = H / n_groups;
-        if (int e = launch_gather_rows((const __half *) C, (const __half *) C_scales, sel, sel_stride, cnt, T, sc.max_rows, R, n_groups, rows, lens, bases,
-                                       q, q16, (int64_t) T * H * R, (cudaStream_t) stream))
-            return e;
-        const WsLayout w = ws_layout(sc.t_max * n_groups, 1, Hg, R);
-        p.q = q16;
-        p.q_is_f32 = false;
-        p.cache = rows;
-        p.cache_rows = (int64_t) sc.t_max * sc.max_rows;
-        p.seq_lens = lens;
-        p.seq_base = bases;
-        p.page_rows = 64;
-        p.scale = scale;
-        p.tail_causal = 0;
-        p.o = o;
-        p.status = (int32_t *) base;
-        p.ws_desc = (int2 *) (base + w.off_desc);
-        p.ws_acc = (float *) (base + w.off_acc);
-        p.ws_ml = (float *) (base + w.off_ml);
-        p.max_segments = w.max_segments;
-        p.max_record_rows = w.record_rows;
-        p.n_seq = T * n_groups;
-        p.T = 1;
-        p.H = Hg;
-        p.d_qk = R;
-        p.d_v = R;
-        p.max_seq_len = sel_stride;
-        // a few thousand rows: one CTA per 64-row tile (the shortest chain per CTA) while that leaves SMs free
-        const int64_t want = ((int64_t) T * n_groups * sel_stride + 63) / 64;
-        p.max_ctas = (int) (want < 1 ? 1 : want > p.sm_count ? p.sm_count : want);
-        const char *why = "";
-        if (decode_umma_supported(p, &why)) return launch_decode_umma(p, (cudaStream_t) stream);
-        p = DecodeProblem{};
-        if (int e = device_sm_count(&p.sm_count)) return e;
-    }
+    if (impl == 2) return fail_invalid("gs_mla_attn: the tcgen05 kernel does not take this call (Q8 cache, head count, alignment or scale)");
     p.q = q;
     p.q_is_f32 = true;
     p.cache = (const __half *) C;

@@ -25,6 +25,19 @@ struct CombineSmem {
     float4 part[CB_LANES][CB_COLS / 4];
 };
 
+// Address helpers of the generalised record layout (see CombinePlan).
+__device__ __forceinline__ int64_t combine_row_stride_acc(const CombinePlan &C) { return C.row_stride_acc ? C.row_stride_acc : C.d_v; }
+__device__ __forceinline__ int64_t combine_chunk_stride_acc(const CombinePlan &C) { return C.chunk_stride_acc ? C.chunk_stride_acc : CB_COLS; }
+__device__ __forceinline__ int64_t combine_row_stride_ml(const CombinePlan &C) { return C.row_stride_ml ? C.row_stride_ml : 2; }
+// column `col` of row `row_in_seg` of segment `seg`
+__device__ __forceinline__ const float *combine_acc_ptr(const CombinePlan &C, int64_t seg, int row_in_seg, int col) {
+    return C.acc + seg * C.seg_stride_acc + (int64_t) row_in_seg * combine_row_stride_acc(C) +
+           (int64_t) (col / CB_COLS) * combine_chunk_stride_acc(C) + (col % CB_COLS);
+}
+__device__ __forceinline__ const float *combine_ml_ptr(const CombinePlan &C, int64_t seg, int row_in_seg) {
+    return C.ml + seg * C.seg_stride_ml + (int64_t) row_in_seg * combine_row_stride_ml(C);
+}
+
 // Where the segments of output row `row` lie.
 struct SegRange {
     int first, nseg, row_in_seg;
@@ -118,8 +131,8 @@ __device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, const
     const int col = col0 + quad * 4;
     const int first = R.first, row_in_seg = R.row_in_seg;
     const int nseg = min(R.nseg, CB_MAX_SEG);
-    const float *acc0 = C.acc + (int64_t) first * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col;
-    const float *ml0 = C.ml + (int64_t) first * C.seg_stride_ml + row_in_seg * 2;
+    const float *acc0 = combine_acc_ptr(C, first, row_in_seg, col < C.d_v ? col : 0);
+    const float *ml0 = combine_ml_ptr(C, first, row_in_seg);
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     float M, L;
     if (nseg <= CB_LANES * CB_REG_SEG) {

@@ -241,6 +241,107 @@ __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
     if (prof) prof[2] = sm100::global_timer_ns();
 }
 
+// Combine of records kept as [row][128-column chunk][segment][128] (the tcgen05 kernel's layout): everything an
+// item needs is one contiguous run of nseg x 512 bytes, fetched by a single bulk copy into shared memory while the
+// threads fetch the (m, l) pairs and form the weights; the copy engine keeps the L2 read at full rate with no
+// address arithmetic in the threads.  One item = (output row, 128 columns), at most CB_NT segments.
+constexpr int32_t ST_COMBINE = 1 << 18;  // status bit: the bulk copy of the records did not complete in time
+__global__ void __launch_bounds__(CB_NT) k_combine_bulk(const CombinePlan C) {
+    extern __shared__ __align__(128) unsigned char bulk_raw[];
+    float4 *tile = reinterpret_cast<float4 *>(bulk_raw);  // [nseg][32] column quads
+    __shared__ CombineSmem S;
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    long long *prof = nullptr;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (C.status && C.status[1] != 0 && cta < 256 && tid == 0)
+        prof = reinterpret_cast<long long *>(const_cast<char *>(reinterpret_cast<const char *>(C.status)) + kCombineProfOffsetBytes) + cta * 8;
+    if (prof) prof[0] = sm100::global_timer_ns();
+    cudaTriggerProgrammaticLaunchCompletion();
+    if (tid == 0) {
+        sm100::mbar_init(&bar, 1);
+        sm100::fence_barrier_init();
+        s_abort = 0;
+    }
+    const int row = blockIdx.x, col0 = blockIdx.y * CB_COLS;
+    const SegRange R = combine_locate(C, row, S);  // from the sequence lengths only: nothing the kernel in front writes
+    __syncthreads();
+    cudaGridDependencySynchronize();  // the records are written by the preceding kernel
+    if (prof) prof[1] = sm100::global_timer_ns();
+    const int nseg = min(R.nseg, CB_NT);
+    if (nseg > 0) {
+        if (C.seg_stride_acc == CB_COLS) {  // the item's segments lie back to back: one copy
+            if (tid == 0) {
+                sm100::mbar_arrive_expect_tx(&bar, (uint32_t) nseg * CB_COLS * 4);
+                sm100::bulk_load(tile, combine_acc_ptr(C, R.first, R.row_in_seg, col0), (uint32_t) nseg * CB_COLS * 4, &bar);
+            }
+        } else if (warp == 0) {  // one 512-byte copy per segment, issued by the lanes of a warp
+            if (lane == 0) sm100::mbar_arrive_expect_tx(&bar, (uint32_t) nseg * CB_COLS * 4);
+            __syncwarp();
+            for (int s = lane; s < nseg; s += 32)
+                sm100::bulk_load(tile + s * (CB_COLS / 4), combine_acc_ptr(C, R.first + s, R.row_in_seg, col0), CB_COLS * 4, &bar);
+        }
+    }
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (tid < nseg) ml = __ldcg(reinterpret_cast<const float2 *>(combine_ml_ptr(C, R.first + tid, R.row_in_seg)));
+    const float mx = warp_max(ml.x);
+    if (lane == 0) S.red[warp] = mx;
+    __syncthreads();
+    float M = S.red[0];
+#pragma unroll
+    for (int w = 1; w < CB_NT / 32; w++) M = fmaxf(M, S.red[w]);
+    const float wgt = ml.x == -INFINITY ? 0.f : expf(ml.x - M);
+    S.m[tid] = wgt;
+    const float ls = warp_sum(ml.y * wgt);
+    if (lane == 0) S.lred[warp] = ls;
+    if (nseg > 0 && !sm100::mbar_wait(&bar, 0, &s_abort, const_cast<int32_t *>(C.status), ST_COMBINE)) s_abort = 1;
+    __syncthreads();
+    if (s_abort) return;  // the status word says why; nothing is written
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < CB_NT / 32; w++) L += S.lred[w];
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = warp; s < nseg; s += CB_LANES) {
+        const float w = S.m[s];
+        if (w != 0.f) {  // an empty segment's accumulator never enters the sum
+            const float4 u = tile[s * (CB_COLS / 4) + lane];
+            a.x = fmaf(u.x, w, a.x);
+            a.y = fmaf(u.y, w, a.y);
+            a.z = fmaf(u.z, w, a.z);
+            a.w = fmaf(u.w, w, a.w);
+        }
+    }
+    S.part[warp][lane] = a;
+    __syncthreads();
+    const int col = col0 + lane * 4;
+    if (warp == 0 && col < C.d_v) {
+#pragma unroll
+        for (int j = 1; j < CB_LANES; j++) {
+            const float4 u = S.part[j][lane];
+            a.x += u.x;
+            a.y += u.y;
+            a.z += u.z;
+            a.w += u.w;
+        }
+        int H_out;
+        const int64_t orow = combine_out_row(C, row, H_out);
+        if (C.part_out) {
+            const int64_t rows_total = (int64_t) (C.seq_div > 1 ? C.n_seq / C.seq_div : C.n_seq) * C.T * H_out;
+            *reinterpret_cast<float4 *>(C.part_out + orow * C.d_v + col) = a;
+            if (col == 0) {
+                C.part_out[rows_total * C.d_v + orow * 2] = M;
+                C.part_out[rows_total * C.d_v + orow * 2 + 1] = L;
+            }
+        }
+        if (C.o) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            *reinterpret_cast<float4 *>(C.o + orow * C.d_v + col) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
+    }
+    if (prof) prof[2] = sm100::global_timer_ns();
+}
+
 // Combine for large batches: a sequence then has only a few segments (about n_ctas / n_seq + 1), and one CTA per
 // (row, 128 columns) with block-wide reductions costs far more than the merge itself.  Here one thread owns four
 // columns of one output row and walks the row's segments; (m, l) loads are the same for the whole block.
@@ -262,14 +363,14 @@ __global__ void __launch_bounds__(128) k_combine_rows(const CombinePlan C) {
         nseg = C.regular_segments;
         row_in_seg = h;
     }
-    const float *ml0 = C.ml + (int64_t) first * C.seg_stride_ml + row_in_seg * 2;
+    const float *ml0 = combine_ml_ptr(C, first, row_in_seg);
     float M = -INFINITY;
     for (int s = 0; s < nseg; s++) M = fmaxf(M, __ldcg(ml0 + (int64_t) s * C.seg_stride_ml));
     int H_out;
     const int64_t orow = combine_out_row(C, row, H_out);
     const int64_t rows_total = (int64_t) (C.seq_div > 1 ? C.n_seq / C.seq_div : C.n_seq) * C.T * H_out;
     for (int col = threadIdx.x * 4; col < C.d_v; col += blockDim.x * 4) {
-        const float *acc0 = C.acc + (int64_t) first * C.seg_stride_acc + (int64_t) row_in_seg * C.d_v + col;
+        const float *acc0 = combine_acc_ptr(C, first, row_in_seg, col);
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         float L = 0.f;
         for (int s = 0; s < nseg; s++) {
@@ -316,8 +417,20 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (by_rows) GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_rows, c));
-    else GS_TRY(cudaLaunchKernelEx(&cfg, k_combine, c));
+    // records of the tcgen05 kernel ([row][chunk][segment][128], at most one segment per CTA and sequence): bulk copy
+    const bool bulk = c.bulk && !by_rows && c.desc != nullptr && c.seq_lens != nullptr && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
+                      c.d_v % CB_COLS == 0 && c.seg_stride_acc % 4 == 0 && !(reinterpret_cast<uintptr_t>(c.acc) & 15);
+    if (bulk) {
+        const int smem = c.n_ctas * CB_COLS * 4;
+        // attributes are set on every call: a cached flag would go stale across a device reset
+        GS_TRY(cudaFuncSetAttribute(k_combine_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        cfg.dynamicSmemBytes = smem;
+        GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_bulk, c));
+    } else if (by_rows) {
+        GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_rows, c));
+    } else {
+        GS_TRY(cudaLaunchKernelEx(&cfg, k_combine, c));
+    }
     return 0;
 }
 

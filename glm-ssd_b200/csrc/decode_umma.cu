@@ -28,6 +28,7 @@
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status word and leaves
 // through the common exit, which frees tensor memory.
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -78,6 +79,12 @@ constexpr int BLK_BYTES = TILE * 128;    // one 64-column block of a tile: 64 ro
 constexpr int NBLK_MAX = 9;              // 576 / 64
 constexpr int STAGE_BYTES = NBLK_MAX * BLK_BYTES;
 constexpr int STAGES = 2;
+// A tile's blocks may complete separate barriers (groups of GRP blocks) so that the score MMAs of a group are issued as
+// soon as it has landed.  Measured on the B200 with three groups of three: the boxes of a tile are requested together and
+// land together, nothing starts earlier, and the extra barrier traffic costs 0.6 us per step at 32K rows (2.5 us at 128K).
+// One group per tile it is.
+constexpr int GRP = NBLK_MAX;
+constexpr int NGRP = (NBLK_MAX + GRP - 1) / GRP;
 constexpr int AHEAD = 2;                 // tiles of a CTA's range asked into L2 before the inputs are final (1-3 measured: 2 best)
 constexpr int N_MMA_WARPS = 3;           // concurrently issuing MMA warps
 constexpr int NTHREADS = 32 * (1 + N_MMA_WARPS + 4);  // warp 0 producer, warps 1-3 MMA, warps 4-7 softmax group
@@ -97,6 +104,9 @@ enum { ST_PRODUCER = 1, ST_MMA = 2, ST_SOFTMAX = 4 };
 enum { PF_LOAD_ISSUE = 0, PF_KV_FULL = 1, PF_S_ISSUED = 2, PF_S_FULL = 3, PF_S_LOADED = 4, PF_VOTED = 5,
        PF_P_WRITTEN = 6, PF_P_FULL_SEEN = 7, PF_PV_ISSUED = 8, PF_SLOW_PATH = 9 };
 
+// Sticky status word of the position-list form: the reference's entry point has no workspace that could carry one.
+__device__ int32_t g_list_status[2];
+
 struct UmmaParams {
     CUtensorMap tm_kv64, tm_kv16, tm_q;
     const int32_t *seq_lens, *seq_base, *page_table;
@@ -108,13 +118,28 @@ struct UmmaParams {
     int32_t *status;
     int n_seq, T, H, rows_q, d_v;  // H: heads handled by this launch (a group of the H_full heads of q)
     int H_full, h0;                // q holds H_full heads per token; this launch takes heads h0 .. h0+H-1
+    // position-list form (the reference's sel / cnt): kernel sequence b attends rows sel[(b / seq_div) * sel_stride + i],
+    // i < seq_lens[b / seq_div]; the rows are fetched four at a time with gather copies through tm_kv1
+    CUtensorMap tm_kv1;
+    const int32_t *sel;
+    int sel_stride;
+    const float *q_f32;            // list form: f32 queries [tokens][H_full][d_qk], rounded to f16 inside the kernel
+    int whole_seq;                 // list form: every sequence is attended by one CTA, which normalises and stores o itself
+    float *o;                      // whole_seq: output f32 [tokens][H_out][d_v]
+    int H_out;
+    int seg_cap;                   // segments the record arrays are laid out for: acc [row][4 chunks][seg_cap][128], ml [row][seg_cap][2]
+    // record addressing: column c of query row q of segment s at ws_acc + s*acc_seg + q*acc_row + (c/128)*acc_chunk + c%128,
+    // its (m, l) pair at ws_ml + s*ml_seg + q*ml_row
+    // (element strides; the record arrays hold fewer than 2^31 floats, so offsets are formed in 32 bits)
+    int acc_seg, acc_row, acc_chunk, ml_seg, ml_row;
+    int tune;                      // tuning switches of the record path, see launch_decode_umma
     int seq_div;                   // >= 1: kernel sequence b reads the length / base / pages of caller sequence b / seq_div
                                    // (T = 1 only: the head groups of a sequence as sequences of their own)
     int64_t cache_rows;
 };
 
 struct Barriers {
-    uint64_t kv_full[STAGES], kv_empty[STAGES];
+    uint64_t kv_full[STAGES][NGRP], kv_empty[STAGES];
     uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
     uint64_t q_full, q_empty, o_full, o_empty;
 };
@@ -147,10 +172,43 @@ struct Segment {
     int b, r0, r1, len, n_tiles, seg_id;
 };
 
+// The schedule as every thread holds it.  With one sequence (the decode and MTP-verify calls) it lives in registers:
+// no shared-memory arrays, no scan, no search and no block barrier between reading the length and the first copy.
+struct Sched {
+    int total, chunk, start, end, b0;
+    int len0, base0;  // single sequence: its (capped) length and first row
+    bool single;
+    bool whole;       // sequences are not cut: CTA c attends sequences c, c + grid, ... from their first row to their last
+};
+
 // Walks the segments of this CTA's unit range [pos, end); `b` is a cursor over sequences.
 __device__ __forceinline__ bool next_segment(int &pos, int &b, int end, const int *cum, int unit_rows,
-                                             const int *seq_lens, Segment &sg) {
+                                             const int *seq_lens, Segment &sg, const Sched &sc) {
+    if (sc.whole) {
+        // `b` walks this CTA's sequences; empty ones yield no segment (their output rows are zeroed up front)
+        int len = 0;
+        while (b < sc.total && (len = sc.single ? sc.len0 : seq_lens[b]) <= 0) b += (int) gridDim.x;
+        if (b >= sc.total) return false;
+        sg.b = b;
+        sg.len = len;
+        sg.r0 = 0;
+        sg.r1 = len;
+        sg.n_tiles = (len + TILE - 1) / TILE;
+        sg.seg_id = 0;
+        b += (int) gridDim.x;
+        return true;
+    }
     if (pos >= end) return false;
+    if (sc.single) {
+        sg.b = 0;
+        sg.len = sc.len0;
+        sg.r0 = pos * unit_rows;
+        sg.r1 = min(sc.len0, end * unit_rows);
+        sg.n_tiles = (sg.r1 - sg.r0 + TILE - 1) / TILE;
+        sg.seg_id = blockIdx.x;
+        pos = end;
+        return true;
+    }
     while (cum[b + 1] <= pos) b++;
     const int u_lo = pos - cum[b];
     const int u_hi = min(end, cum[b + 1]) - cum[b];
@@ -203,7 +261,7 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t 
     }
 }
 
-template <int NQ, int NBLK>
+template <int NQ, int NBLK, bool LIST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
     using SM = Smem<NQ>;
     extern __shared__ uint8_t smem_raw[];
@@ -217,10 +275,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit_rows = P.paged ? TILE : 16;
+    int32_t *const status_w = LIST ? g_list_status : P.status;  // where a wait that gives up leaves its code
 
     // optional clock stamps of CTA 0's first tiles
     long long *prof = nullptr;
-    if (blockIdx.x == 0 && P.status[1] != 0)
+    if (blockIdx.x == 0 && P.status && P.status[1] != 0)
         prof = reinterpret_cast<long long *>(reinterpret_cast<char *>(P.status) + kProfOffsetBytes);
 #define GS_STAMP(tile, slot)                                                                     \
     do {                                                                                         \
@@ -228,7 +287,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     } while (0)
 
     long long *cta_prof = nullptr;  // wall-clock stamps of every CTA
-    if (P.status[1] != 0)
+    if (P.status && P.status[1] != 0)
         cta_prof = reinterpret_cast<long long *>(reinterpret_cast<char *>(P.status) + kCtaProfOffsetBytes) + blockIdx.x * 8;
 #define GS_CTA_STAMP(slot)                              \
     do {                                                \
@@ -244,8 +303,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tma_prefetch_desc(&P.tm_kv64);
         tma_prefetch_desc(&P.tm_kv16);
         tma_prefetch_desc(&P.tm_q);
+        if (LIST) tma_prefetch_desc(&P.tm_kv1);
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&B.kv_full[s], 1);
+            for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], 1);
             mbar_init(&B.kv_empty[s], N_MMA_WARPS);
         }
         for (int s = 0; s < 2; s++) {
@@ -254,7 +314,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             mbar_init(&B.p_full[s], 4);
             mbar_init(&B.p_empty[s], N_MMA_WARPS);
         }
-        mbar_init(&B.q_full, 1);
+        mbar_init(&B.q_full, (LIST && P.q_f32) ? 4 : 1);  // f32 queries are converted by the four softmax warps
         mbar_init(&B.q_empty, N_MMA_WARPS);
         mbar_init(&B.o_full, N_MMA_WARPS);
         mbar_init(&B.o_empty, 4);
@@ -268,53 +328,72 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tmem_relinquish();
     }
     // The schedule: units per sequence, their running sum, this CTA's chunk and the sequence it starts in.
-    int total = 0, chunk = 1, start = 0, end = 0, b_cur = 0;
+    Sched sc;
+    sc.single = P.n_seq == 1;
+    sc.whole = LIST && P.whole_seq;
+    sc.total = 0;
+    sc.chunk = 1;
+    sc.start = sc.end = sc.b0 = 0;
+    sc.len0 = sc.base0 = 0;
     auto build_schedule = [&]() {
-        {
-            // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
-            const uint64_t pol_keep = l2_policy_evict_last();
-            // A length is taken as at most what the cache (or the sequence's row of the page table) can hold,
-            // and the running sum below saturates: whatever the arrays contain - they are read once before they
-            // are final - the schedule stays monotone and every index derived from it stays in range.
-            const int64_t len_cap = min(P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows,
-                                        (int64_t) 0x7fffffff - 64);  // the rounding up to units below stays in an int
+        // the small per-sequence inputs are read by every CTA on every call: ask L2 to keep them
+        const uint64_t pol_keep = l2_policy_evict_last();
+        // A length is taken as at most what the cache (or the sequence's row of the page table) can hold,
+        // and the running sum below saturates: whatever the arrays contain - they are read once before they
+        // are final - the schedule stays monotone and every index derived from it stays in range.
+        const int64_t len_cap = min(P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows,
+                                    (int64_t) 0x7fffffff - 64);  // the rounding up to units below stays in an int
+        if (sc.single) {
+            // one sequence: every thread reads the one length word itself and derives its CTA's range in registers
+            sc.len0 = (int) min((int64_t) max(ld_global_hint(P.seq_lens, pol_keep), 0), len_cap);
+            sc.base0 = P.seq_base ? ld_global_hint(P.seq_base, pol_keep) : 0;
+            sc.total = (sc.len0 + unit_rows - 1) / unit_rows;
+        } else {
             for (int b = tid; b < P.n_seq; b += NTHREADS) {
                 const int len = (int) min((int64_t) max(ld_global_hint(P.seq_lens + b / P.seq_div, pol_keep), 0), len_cap);
                 M.base[b] = P.seq_base ? ld_global_hint(P.seq_base + b / P.seq_div, pol_keep) : 0;
                 M.len[b] = len;
                 M.cum[b + 1] = (len + unit_rows - 1) / unit_rows;  // < 2^27
             }
-        }
-        tc_fence_before();
-        __syncthreads();
-        if (warp == 0 && P.n_seq > 1) {  // inclusive scan of cum[1..n_seq], 32 entries per step
-            int carry = 0;
-            for (int base = 1; base <= P.n_seq; base += 32) {
-                const int i = base + lane;
-                int v = i <= P.n_seq ? M.cum[i] : 0;
+            tc_fence_before();
+            __syncthreads();
+            if (warp == 0) {  // inclusive scan of cum[1..n_seq], 32 entries per step
+                int carry = 0;
+                for (int base = 1; base <= P.n_seq; base += 32) {
+                    const int i = base + lane;
+                    int v = i <= P.n_seq ? M.cum[i] : 0;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int u = __shfl_up_sync(0xffffffffu, v, o);
-                    if (lane >= o) v = min(v + u, UNIT_CAP);
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int u = __shfl_up_sync(0xffffffffu, v, o);
+                        if (lane >= o) v = min(v + u, UNIT_CAP);
+                    }
+                    v = min(v + carry, UNIT_CAP);
+                    if (i <= P.n_seq) M.cum[i] = v;
+                    carry = __shfl_sync(0xffffffffu, v, 31);
                 }
-                v = min(v + carry, UNIT_CAP);
-                if (i <= P.n_seq) M.cum[i] = v;
-                carry = __shfl_sync(0xffffffffu, v, 31);
             }
+            __syncthreads();
+            tc_fence_after();
+            sc.total = M.cum[P.n_seq];
         }
-        if (P.n_seq > 1) __syncthreads();
-        tc_fence_after();
-        total = M.cum[P.n_seq];
-        chunk = max(1, (total + (int) gridDim.x - 1) / (int) gridDim.x);
-        start = min(total, (int) blockIdx.x * chunk);
-        end = min(total, start + chunk);
-        // first sequence of this CTA's range (binary search: largest b with cum[b] <= start)
-        int lo = 0, hi = P.n_seq - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (M.cum[mid] <= start) lo = mid; else hi = mid - 1;
+        sc.chunk = max(1, (sc.total + (int) gridDim.x - 1) / (int) gridDim.x);
+        sc.start = min(sc.total, (int) blockIdx.x * sc.chunk);
+        sc.end = min(sc.total, sc.start + sc.chunk);
+        sc.b0 = 0;
+        if (sc.whole) {  // sequences dealt round-robin; `total` counts sequences, the cursor starts at this CTA's first
+            sc.total = P.n_seq;
+            sc.b0 = (int) blockIdx.x;
+            return;
         }
-        b_cur = lo;
+        if (!sc.single) {
+            // first sequence of this CTA's range (binary search: largest b with cum[b] <= start)
+            int lo = 0, hi = P.n_seq - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (M.cum[mid] <= sc.start) lo = mid; else hi = mid - 1;
+            }
+            sc.b0 = lo;
+        }
     };
     // Everything above touched only this CTA's own resources.  While the kernel in front of this one is still
     // running (programmatic dependent launch), the schedule is built once from whatever the length / base /
@@ -322,14 +401,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     // them - and the first tiles of this CTA's range are asked into L2.  Nothing read here is used for a
     // result: a stale value costs a useless prefetch, and every index is checked before it is followed.
     build_schedule();
-    if (warp == 0) {
-        int pp = start, bb = b_cur, asked = 0;
+    if (!LIST && warp == 0) {
+        int pp = sc.start, bb = sc.b0, asked = 0;
         Segment s2;
-        while (asked < AHEAD && next_segment(pp, bb, end, M.cum, unit_rows, M.len, s2)) {
+        while (asked < AHEAD && next_segment(pp, bb, sc.end, M.cum, unit_rows, M.len, s2, sc)) {
             for (int j = 0; j < s2.n_tiles && asked < AHEAD; j++, asked++) {
                 const int row = s2.r0 + j * TILE;
                 int64_t grow = -1;
-                if (!P.paged) grow = (int64_t) M.base[s2.b] + row;
+                if (!P.paged) grow = (int64_t) (sc.single ? sc.base0 : M.base[s2.b]) + row;
                 else if (row >= 0 && row / TILE < P.page_table_stride)
                     grow = (int64_t) P.page_table[(int64_t) (s2.b / P.seq_div) * P.page_table_stride + row / TILE] * TILE;
                 if (grow >= 0 && grow < P.cache_rows && elect_one()) {
@@ -340,25 +419,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             }
         }
     }
-    __syncthreads();  // the arrays are rebuilt below
+    // barrier initialisation and the tensor-memory address become visible to every warp here; with several
+    // sequences it is also the barrier in front of rebuilding the shared-memory arrays
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
     griddep_wait();
     if (tid == 0) GS_CTA_STAMP(1);
     build_schedule();
     const uint32_t tmem = M.tmem_base;
-    if (blockIdx.x == 0) {  // where the combine kernel finds each sequence's segments
-        for (int b = tid; b < P.n_seq; b += NTHREADS) {
-            const int u0 = M.cum[b], u1 = M.cum[b + 1];
-            int2 d = make_int2(0, 0);
-            if (u1 > u0) {
-                const int c_first = u0 / chunk, c_last = (u1 - 1) / chunk;
-                d = make_int2(c_first + b, c_last - c_first + 1);
+    if (blockIdx.x == 0 && P.ws_desc && !sc.whole) {  // where the combine kernel finds each sequence's segments
+        if (sc.single) {
+            if (tid == 0) P.ws_desc[0] = sc.total > 0 ? make_int2(0, (sc.total - 1) / sc.chunk + 1) : make_int2(0, 0);
+        } else {
+            for (int b = tid; b < P.n_seq; b += NTHREADS) {
+                const int u0 = M.cum[b], u1 = M.cum[b + 1];
+                int2 d = make_int2(0, 0);
+                if (u1 > u0) {
+                    const int c_first = u0 / sc.chunk, c_last = (u1 - 1) / sc.chunk;
+                    d = make_int2(c_first + b, c_last - c_first + 1);
+                }
+                P.ws_desc[b] = d;
             }
-            P.ws_desc[b] = d;
         }
     }
     griddep_launch_dependents();
     if (tid == 0) GS_STAMP(kProfTiles - 1, 1);
-    int pos = start;
+    int pos = sc.start, b_cur = sc.b0;
+    const int end = sc.end;
     uint32_t it = 0, sgc = 0;  // running tile and segment counters (identical in every role)
     Segment sg;
 
@@ -367,41 +455,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         // The whole warp runs the loop (uniform control flow); one elected lane issues each copy.
         bool ok = true;
         const uint64_t pol_stream = l2_policy_evict_first();  // every cache row is read once per step
-        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
-            const int64_t base_row = M.base[sg.b];
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg, sc)) {
+            const int64_t base_row = sc.single ? sc.base0 : M.base[sg.b];
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
-                ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+                ok = mbar_wait(&B.kv_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, status_w, ST_PRODUCER);
                 if (!ok) break;
                 if (lane == 0) GS_STAMP(it, PF_LOAD_ISSUE);
                 if (lane == 0 && it == 0) GS_CTA_STAMP(7);
                 const int row = sg.r0 + j * TILE;
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
-                if (P.paged || valid == TILE) {
+                if (LIST) {
+                    // Rows named by the position list: lane l fetches the four indices of row quad l % 16 once and issues the
+                    // gather copies of that quad for the column blocks l / 16, l / 16 + 2, ...  An index past the list's end
+                    // repeats the quad's first row (the copy always moves four rows); those rows are masked in the scores.
+                    const int nq4 = (valid + 3) >> 2;
+                    if (elect_one()) {
+#pragma unroll
+                        for (int g = 0; g < NGRP; g++) {
+                            const int k_lo = g * GRP, k_hi = min(NBLK, g * GRP + GRP);
+                            mbar_arrive_expect_tx(&B.kv_full[s][g], (uint32_t) (nq4 * (k_hi - k_lo) * 512));
+                        }
+                    }
+                    __syncwarp();
+                    const int quad = lane & 15;
+                    if (quad < nq4) {
+                        const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row + quad * 4;
+                        const int left = valid - quad * 4;  // >= 1
+                        const int r0 = lp[0];
+                        const int r1 = left > 1 ? lp[1] : r0, r2 = left > 2 ? lp[2] : r0, r3 = left > 3 ? lp[3] : r0;
+                        for (int k = lane >> 4; k < NBLK; k += 2)
+                            tma_gather4_hint(dst + k * BLK_BYTES + quad * 512, &P.tm_kv1, &B.kv_full[s][k / GRP], k * 64, r0, r1, r2, r3, pol_stream);
+                    }
+                    __syncwarp();
+                } else if (P.paged || valid == TILE) {
                     const int grow = P.paged ? P.page_table[(int64_t) (sg.b / P.seq_div) * P.page_table_stride +
                                                             min(max(row / TILE, 0), P.page_table_stride - 1)] * TILE
                                              : (int) (base_row + row);
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (NBLK * BLK_BYTES));
 #pragma unroll
-                        for (int k = 0; k < NBLK; k++)
-                            tma_load_2d_hint(dst + k * BLK_BYTES, &P.tm_kv64, &B.kv_full[s], k * 64, grow, pol_stream);
+                        for (int g = 0; g < NGRP; g++) {
+                            const int k_lo = g * GRP, k_hi = min(NBLK, g * GRP + GRP);
+                            mbar_arrive_expect_tx(&B.kv_full[s][g], (uint32_t) ((k_hi - k_lo) * BLK_BYTES));
+#pragma unroll
+                            for (int k = 0; k < GRP; k++)
+                                if (k_lo + k < k_hi)
+                                    tma_load_2d_hint(dst + (k_lo + k) * BLK_BYTES, &P.tm_kv64, &B.kv_full[s][g], (k_lo + k) * 64, grow, pol_stream);
+                        }
                     }
                 } else {
                     const int ng = (valid + 15) >> 4;
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(&B.kv_full[s], (uint32_t) (ng * NBLK * 2048));
-                        for (int g = 0; g < ng; g++) {
 #pragma unroll
-                            for (int k = 0; k < NBLK; k++)
-                                tma_load_2d_hint(dst + k * BLK_BYTES + g * 2048, &P.tm_kv16, &B.kv_full[s], k * 64,
-                                                 (int) (base_row + row + g * 16), pol_stream);
+                        for (int g = 0; g < NGRP; g++) {
+                            const int k_lo = g * GRP, k_hi = min(NBLK, g * GRP + GRP);
+                            mbar_arrive_expect_tx(&B.kv_full[s][g], (uint32_t) (ng * (k_hi - k_lo) * 2048));
+                            for (int r = 0; r < ng; r++) {
+#pragma unroll
+                                for (int k = 0; k < GRP; k++)
+                                    if (k_lo + k < k_hi)
+                                        tma_load_2d_hint(dst + (k_lo + k) * BLK_BYTES + r * 2048, &P.tm_kv16, &B.kv_full[s][g], (k_lo + k) * 64,
+                                                         (int) (base_row + row + r * 16), pol_stream);
+                            }
                         }
                     }
                 }
-                if (j == 0) {  // the query rows of this sequence, after the first (larger, farther) cache tile
-                    ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_PRODUCER);
+                if (j == 0 && !(LIST && P.q_f32)) {  // the query rows of this sequence, after the first (larger, farther) cache tile
+                    ok = mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, status_w, ST_PRODUCER);
                     if (!ok) break;
                     if (elect_one()) {
                         if (P.H_full == P.H) {  // the sequence's T*H query rows are contiguous: one box per block
@@ -435,13 +556,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 1);  // A (V^T) and B (P^T) MN-major
         constexpr int KSTEPS = NBLK * 4;
         constexpr int K_PER = (KSTEPS + N_MMA_WARPS - 1) / N_MMA_WARPS;
+        // the landing groups this warp's score k-steps read
+        const int g_lo = ((mw * K_PER) >> 2) / GRP, g_hi = ((min(KSTEPS, (mw + 1) * K_PER) - 1) >> 2) / GRP;
+        constexpr int g_all = NGRP;
         const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);         // cache tile / Q, K-major
         const uint64_t d_vt = make_smem_desc(0, BLK_BYTES, 1024, kSwizzle128B);    // cache tile, MN-major
         const uint64_t d_pt = make_smem_desc(0, 128, 1024, kSwizzleNone);          // P^T, MN-major
         const uint32_t q_lo = smem_u32(q_smem) >> 4, p_lo0 = smem_u32(p_smem) >> 4, kv_lo0 = smem_u32(kv_smem) >> 4;
         bool ok = true;
-        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
-            ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, P.status, ST_MMA);
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg, sc)) {
+            ok = mbar_wait(&B.q_full, sgc & 1, abort_flag, status_w, ST_MMA);
             // S of tile j+1 is issued ahead of P.V of tile j whenever its data has already landed, so it
             // runs on the tensor pipe while the softmax of tile j is computed.
             auto issue_s = [&](uint32_t i) {
@@ -468,8 +592,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const uint32_t ph = (it >> 1) & 1;
                 const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
                 if (!s_ahead) {
-                    ok = mbar_wait(&B.kv_full[s], ph, abort_flag, P.status, ST_MMA) &&
-                         mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, P.status, ST_MMA);
+                    ok = mbar_wait(&B.s_empty[s], ph ^ 1, abort_flag, status_w, ST_MMA);
+                    for (int g = g_lo; ok && g <= g_hi; g++) ok = mbar_wait(&B.kv_full[s][g], ph, abort_flag, status_w, ST_MMA);
                     if (!ok) break;
                     if (mw == 0 && lane == 0) GS_STAMP(it, PF_KV_FULL);
                     if (mw == 0 && lane == 0 && it == 0) GS_CTA_STAMP(2);
@@ -481,7 +605,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     const uint32_t i1 = it + 1;
                     const uint32_t ph1 = (i1 >> 1) & 1;
                     // uniform over the warp: every lane polls the same barriers
-                    const bool landed = mbar_test(&B.kv_full[i1 & 1], ph1) && mbar_test(&B.s_empty[i1 & 1], ph1 ^ 1);
+                    bool landed = mbar_test(&B.s_empty[i1 & 1], ph1 ^ 1);
+                    for (int g = g_lo; g <= g_hi; g++) landed = landed && mbar_test(&B.kv_full[i1 & 1][g], ph1);
                     if (__all_sync(0xffffffffu, landed)) {
                         if (mw == 0 && lane == 0) GS_STAMP(i1, PF_KV_FULL);
                         issue_s(i1);
@@ -490,8 +615,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     }
                 }
                 // ---- O^T[my tiles] += V^T . P^T ----
-                ok = mbar_wait(&B.p_full[s], ph, abort_flag, P.status, ST_MMA);
-                if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, P.status, ST_MMA);
+                ok = mbar_wait(&B.p_full[s], ph, abort_flag, status_w, ST_MMA);
+                // P.V reads every value block of the tile: all groups (they have landed: the scores the softmax
+                // just turned into P needed them; the waits return at once and make that landing visible here)
+                for (int g = 0; ok && g < g_all; g++) ok = mbar_wait(&B.kv_full[s][g], ph, abort_flag, status_w, ST_MMA);
+                if (ok && j == 0) ok = mbar_wait(&B.o_empty, (sgc & 1) ^ 1, abort_flag, status_w, ST_MMA);
                 if (!ok) break;
                 if (mw == 0 && lane == 0) GS_STAMP(it, PF_P_FULL_SEEN);
                 tc_fence_after();
@@ -532,7 +660,41 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         float l_part[HQ];                             // row sums of this thread's cache row, per query row
         float nm[HQ];                                 // minus the reference maximum (log2 units) per query row
         bool ok = true;
-        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg)) {
+        if (LIST && sc.whole) {
+            // a query that attends nothing gets zeros (crates/cuda/kernels/ops.cu:535); such sequences yield no segment
+            for (int b = (int) blockIdx.x; b < P.n_seq; b += (int) gridDim.x) {
+                if ((sc.single ? sc.len0 : M.len[b]) > 0) continue;
+                float *dst = P.o + ((int64_t) (b / P.seq_div) * P.H_out + (b % P.seq_div) * P.H) * P.d_v;
+                for (int i = wg_tid; i < P.rows_q * P.d_v; i += 128) dst[i] = 0.f;
+            }
+        }
+        while (ok && next_segment(pos, b_cur, end, M.cum, unit_rows, M.len, sg, sc)) {
+            if (LIST && P.q_f32) {
+                // f32 queries: the four warps round this sequence's rows to f16 straight into the operand layout the
+                // TMA would have produced (64-column blocks of [NQ rows][128 bytes], 16-byte chunk j of row r at chunk
+                // position j ^ (r % 8)), once the MMAs of the previous sequence have finished with the old rows
+                (void) mbar_wait(&B.q_empty, (sgc & 1) ^ 1, abort_flag, status_w, ST_SOFTMAX);
+                const float *qsrc = P.q_f32 + ((int64_t) (sg.b / P.seq_div) * P.H_full + (int64_t) (sg.b % P.seq_div) * P.H) * (NBLK * 64);
+                constexpr int CPR = NBLK * 8;  // 16-byte chunks (8 columns) per row
+                for (int i = wg_tid; i < NQ * CPR; i += 128) {
+                    const int r = i / CPR, cc = i - r * CPR;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (r < P.rows_q) {
+                        const float4 a = __ldg(reinterpret_cast<const float4 *>(qsrc + (int64_t) r * (NBLK * 64) + cc * 8));
+                        const float4 b4 = __ldg(reinterpret_cast<const float4 *>(qsrc + (int64_t) r * (NBLK * 64) + cc * 8 + 4));
+                        __half2 h;
+                        h = __floats2half2_rn(a.x, a.y); v.x = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(a.z, a.w); v.y = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(b4.x, b4.y); v.z = *reinterpret_cast<uint32_t *>(&h);
+                        h = __floats2half2_rn(b4.z, b4.w); v.w = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                    const int kb = cc >> 3, jj = cc & 7;
+                    *reinterpret_cast<uint4 *>(q_smem + kb * (NQ * 128) + r * 128 + ((jj ^ (r & 7)) << 4)) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&B.q_full);
+            }
             if (wg_tid < NQ) {
                 const int q = wg_tid, t = q / P.H;
                 int lim = 0;
@@ -551,7 +713,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                (void) mbar_wait(&B.s_full[s], ph, abort_flag, P.status, ST_SOFTMAX);
+                (void) mbar_wait(&B.s_full[s], ph, abort_flag, status_w, ST_SOFTMAX);
                 GS_STAMP(it, PF_S_FULL);
                 tc_fence_after();
                 const int row0 = sg.r0 + j * TILE;
@@ -636,7 +798,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         nm[i] = mr == -INFINITY ? UNSET : -mr;
                     }
                 }
-                (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, P.status, ST_SOFTMAX);
+                (void) mbar_wait(&B.p_empty[s], ph ^ 1, abort_flag, status_w, ST_SOFTMAX);
                 // probabilities: row sums in registers; P^T as f16, 8 query rows per 16-byte store, in the
                 // MN-major operand layout [q/8][row/8][row%8][q%8].  A masked score is -inf and gives 0; an
                 // unset column holds only masked scores.
@@ -659,7 +821,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 }
                 if (rescale) {
                     // S of this tile may have been issued ahead of P.V of the previous one: wait for that P.V
-                    (void) mbar_wait(&B.p_empty[s ^ 1], ((it - 1) >> 1) & 1, abort_flag, P.status, ST_SOFTMAX);
+                    (void) mbar_wait(&B.p_empty[s ^ 1], ((it - 1) >> 1) & 1, abort_flag, status_w, ST_SOFTMAX);
                     tc_fence_after();
 #pragma unroll 1
                     for (int mt = 0; mt < NVT; mt++) {
@@ -696,7 +858,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             }
             if (!ok) break;
             // ---- end of segment: drain the accumulators into this segment's partial record ----------------
-            (void) mbar_wait(&B.o_full, sgc & 1, abort_flag, P.status, ST_SOFTMAX);
+            (void) mbar_wait(&B.o_full, sgc & 1, abort_flag, status_w, ST_SOFTMAX);
             named_bar_sync(2, 128);
             if (*abort_flag) { ok = false; break; }
             tc_fence_after();
@@ -712,31 +874,94 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 if ((lane & 15) == 0) M.sl[qt][col0 + i] = v;
             }
             named_bar_sync(1, 128);
+            if (LIST && sc.whole) {
+                // the whole sequence was attended here: no record, no merge - normalise and store (ops.cu:531-538)
+                if (wg_tid < NQ) {
+                    const float l = (M.sl[0][wg_tid] + M.sl[1][wg_tid]) + (M.sl[2][wg_tid] + M.sl[3][wg_tid]);
+                    M.f[wg_tid] = l > 0.f ? 1.f / l : 0.f;
+                }
+                named_bar_sync(1, 128);
+                float *dst = P.o + ((int64_t) (sg.b / P.seq_div) * P.H_out + (sg.b % P.seq_div) * P.H) * P.d_v + qt * 32 + lane;
+#pragma unroll 1
+                for (int mt = 0; mt < NVT; mt++) {
+#pragma unroll
+                    for (int c = 0; c < NQ / 16; c++) {
+                        uint32_t r[16];
+                        tmem_ld16(tmem + lane_base + (O_SLOT0 + mt) * NQ + c * 16, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 16; i++)
+                            if (c * 16 + i < P.rows_q) dst[(int64_t) (c * 16 + i) * P.d_v + mt * 128] = __uint_as_float(r[i]) * M.f[c * 16 + i];
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&B.o_empty);
+                sgc++;
+                continue;
+            }
             if (wg_tid < P.rows_q) {
                 const int q = wg_tid;
                 const float m = M.mref[q];
-                float *ml = P.ws_ml + ((int64_t) sg.seg_id * P.rows_q + q) * 2;
+                float *ml = P.ws_ml + (sg.seg_id * P.ml_seg + q * P.ml_row);
                 ml[0] = m == -INFINITY ? -INFINITY : m * LN2;
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
-            float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
+            // records are kept as [query row][128-column chunk][segment][128]: what one (row, chunk) item of the combine
+            // kernel reads is then one contiguous run
+            float *acc = P.ws_acc + (sg.seg_id * P.acc_seg + qt * 32 + lane);
+            const int acc_row = P.acc_row, acc_chunk = P.acc_chunk;
             // one value tile (NQ columns of this lane's row) per step; the loads of the next tile are in flight
             // while the current one is stored
             uint32_t rbuf[2][NQ];
 #pragma unroll
             for (int c = 0; c < NQ / 16; c++) tmem_ld16(tmem + lane_base + O_SLOT0 * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
+            if (pos >= end && (P.tune & 1)) {
+                // The CTA's last segment: nothing will be loaded any more and every MMA that read the ring has
+                // completed, so the ring's first stage serves as a staging area [2][NQ][128] f32.  A thread holds one
+                // value column of all query rows; through the staging area a warp stores whole 512-byte pieces
+                // (one query row, 128 columns) with 16 bytes per lane - a quarter of the store instructions.
+                float *stg = reinterpret_cast<float *>(kv_smem);
+                // every CTA starts at another query row, so that at any moment the CTAs write to different parts of the arrays
+                const int rot = (int) (blockIdx.x % (NQ / 4));
+                float *piece0 = P.ws_acc + (sg.seg_id * P.acc_seg + lane * 4);
 #pragma unroll
-            for (int mt = 0; mt < NVT; mt++) {
-                tmem_wait_ld();
-                if (mt + 1 < NVT) {
+                for (int mt = 0; mt < NVT; mt++) {
+                    tmem_wait_ld();
+                    if (mt + 1 < NVT) {
 #pragma unroll
-                    for (int c = 0; c < NQ / 16; c++)
-                        tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
-                                  *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
+                        for (int c = 0; c < NQ / 16; c++)
+                            tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
+                                      *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
+                    }
+                    float *buf = stg + (mt & 1) * (NQ * 128);
+#pragma unroll
+                    for (int q = 0; q < NQ; q++)
+                        if (q < P.rows_q) buf[q * 128 + qt * 32 + lane] = __uint_as_float(rbuf[mt & 1][q]);
+                    named_bar_sync(1, 128);  // one barrier per value tile: the other buffer was last read before the previous one
+#pragma unroll
+                    for (int i = 0; i < NQ / 4; i++) {
+                        int ii = i + rot;
+                        if (ii >= NQ / 4) ii -= NQ / 4;
+                        const int q = qt + 4 * ii;
+                        if (q < P.rows_q)
+                            st_global_hint_v4(piece0 + (q * acc_row + mt * acc_chunk), *reinterpret_cast<const float4 *>(buf + q * 128 + lane * 4), pol_keep);
+                    }
                 }
+            } else {
 #pragma unroll
-                for (int q = 0; q < NQ; q++)
-                    if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(rbuf[mt & 1][q]), pol_keep);
+                for (int mt = 0; mt < NVT; mt++) {
+                    tmem_wait_ld();
+                    if (mt + 1 < NVT) {
+#pragma unroll
+                        for (int c = 0; c < NQ / 16; c++)
+                            tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
+                                      *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
+                    }
+#pragma unroll
+                    for (int q = 0; q < NQ; q++)
+                        if (q < P.rows_q) st_global_hint(acc + (q * acc_row + mt * acc_chunk), __uint_as_float(rbuf[mt & 1][q]), pol_keep);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -767,11 +992,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #undef GS_CTA_STAMP
 }
 
-template <int NQ, int NBLK>
+template <int NQ, int NBLK, bool LIST = false>
 int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
     const int smem = Smem<NQ>::TOTAL;
     // attributes are set on every call: a cached flag would go stale across a device reset
-    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK, LIST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NTHREADS);
@@ -783,11 +1008,123 @@ int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GS_TRY(cudaLaunchKernelEx(&cfg, k_decode_umma<NQ, NBLK>, P));
+    GS_TRY(cudaLaunchKernelEx(&cfg, k_decode_umma<NQ, NBLK, LIST>, P));
     return 0;
 }
 
 }  // namespace
+
+int read_list_status(int32_t *out) {
+    GS_TRY(cudaMemcpyFromSymbol(out, g_list_status, sizeof(int32_t)));
+    return 0;
+}
+
+// Position lists on the tensor cores.  Head groups of at most 48 heads (a multiple of 8 each): 0 = not cut that way.
+static int list_head_groups(int H) {
+    const int n = (H + 47) / 48;
+    return (n > 0 && H % n == 0 && (H / n) % 8 == 0) ? n : 0;
+}
+
+// Returns 0 when launched, -1 when the shape is not taken by the tcgen05 kernel (the caller then runs the CUDA-core
+// kernel), or a cudaError_t.  Every (token, head group) is a kernel sequence over the token's list.  With one split, or
+// when the caller's `part` cannot hold enough records, every sequence is attended by one CTA that stores o itself;
+// otherwise the rows are dealt to CTAs as in the dense form and the records live in `part`
+// (T*H*splits*(R+2) floats, crates/cuda/kernels/ops.cu:578), as [row][chunk][segment][128], then [row][segment][2], then
+// the per-sequence descriptors.
+int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
+                            float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st) {
+    const int n_groups = list_head_groups(H);
+    if (R != 512 || n_groups == 0 || sel_stride <= 0 || !(scale > 0.f)) return -1;
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(q) & 15)) return -1;
+    const int64_t n_seq_k = (int64_t) T * n_groups;
+    if (n_seq_k > MAX_SEQ) return -1;
+    const int Hg = H / n_groups;
+    UmmaParams P;
+    memset(&P, 0, sizeof(P));
+    // The entry point is not told how many rows the cache holds; the map spans the whole index range of a row
+    // coordinate, and the lists are trusted as the reference trusts them.
+    if (encode_tmap_2d_f16(&P.tm_kv1, C, (uint64_t) 0x7fffffff, (uint64_t) R, (uint64_t) R * 2, 1, 64, (int) CU_TENSOR_MAP_SWIZZLE_128B))
+        return -1;
+    P.tm_kv64 = P.tm_kv1;  // unused in this form; kept valid for the descriptor prefetches
+    P.tm_kv16 = P.tm_kv1;
+    P.tm_q = P.tm_kv1;
+    P.seq_lens = cnt;
+    P.sel = sel;
+    P.sel_stride = sel_stride;
+    P.q_f32 = q;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.tail_causal = 0;
+    P.n_seq = (int) n_seq_k;
+    P.T = 1;
+    P.H = Hg;
+    P.H_full = H;
+    P.H_out = H;
+    P.h0 = 0;
+    P.rows_q = Hg;
+    P.d_v = R;
+    P.seq_div = n_groups;
+    P.cache_rows = sel_stride;  // caps a length word: a list holds at most sel_stride entries
+    P.o = o;
+    P.status = nullptr;
+    int grid_max = sm_count < kMaxCtas ? sm_count : kMaxCtas;
+    if (grid_max < 1) grid_max = 1;
+    // records that fit the caller's buffer
+    int grid_rec = 0;
+    if (splits > 1 && part && !(reinterpret_cast<uintptr_t>(part) & 15)) {
+        const int64_t part_floats = (int64_t) T * H * splits * (R + 2);
+        const int64_t desc_floats = (n_seq_k * 2 + 3) / 4 * 4;
+        const int64_t segs = (part_floats - desc_floats) / ((int64_t) Hg * (R + 2));
+        const int64_t tiles = n_seq_k * ((sel_stride + TILE - 1) / TILE);
+        int64_t g = segs - n_seq_k;
+        if (g > grid_max) g = grid_max;
+        if (g > tiles) g = tiles;
+        grid_rec = (int) (g > 0 ? g : 0);
+    }
+    const int grid_whole = (int) (n_seq_k < grid_max ? n_seq_k : grid_max);
+    const bool whole = grid_rec <= grid_whole;
+    const int grid = whole ? grid_whole : grid_rec;
+    P.whole_seq = whole ? 1 : 0;
+    CombinePlan c{};
+    if (!whole) {
+        P.seg_cap = grid + (int) n_seq_k;
+        P.ws_acc = part;
+        P.ws_ml = part + (int64_t) Hg * NVT * P.seg_cap * 128;
+        P.ws_desc = reinterpret_cast<int2 *>(P.ws_ml + (int64_t) Hg * P.seg_cap * 2);
+        P.acc_seg = 128;
+        P.acc_chunk = P.seg_cap * 128;
+        P.acc_row = NVT * P.seg_cap * 128;
+        P.ml_seg = 2;
+        P.ml_row = P.seg_cap * 2;
+        c.acc = P.ws_acc;
+        c.ml = P.ws_ml;
+        c.desc = P.ws_desc;
+        c.seg_stride_acc = P.acc_seg;
+        c.row_stride_acc = P.acc_row;
+        c.chunk_stride_acc = P.acc_chunk;
+        c.seg_stride_ml = P.ml_seg;
+        c.row_stride_ml = P.ml_row;
+        c.n_seq = (int) n_seq_k;
+        c.T = 1;
+        c.H = Hg;
+        c.H_out = H;
+        c.h0 = 0;
+        c.seq_div = n_groups;
+        c.d_v = R;
+        c.o = o;
+        c.seq_lens = cnt;
+        c.unit_rows = 16;
+        c.n_ctas = grid;
+        c.len_cap = sel_stride;
+        c.bulk = true;
+        P.tune = 1;  // staged record stores
+    }
+    int e;
+    if (Hg <= 32) e = launch_cfg<32, 8, true>(P, grid, st);
+    else e = launch_cfg<48, 8, true>(P, grid, st);
+    if (e) return e;
+    if (!whole) return launch_combine(c, st);
+    return 0;
+}
 
 bool decode_umma_supported(const DecodeProblem &p, const char **why) {
     if (p.q_is_f32) { *why = "f32 queries"; return false; }
@@ -858,6 +1195,12 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     // every CTA and every sequence can add one segment, each with the query rows of one launch
     if (((int64_t) grid + n_seq_k) * p.T * (seq_div > 1 || n_groups > 1 ? Hg : p.H) > p.max_record_rows)
         return fail_invalid("decode: workspace too small for the segment records");
+    P.seg_cap = grid + n_seq_k;
+    // tuning switches (environment, read per call): bit 0 = staged 16-byte record stores on a CTA's last segment,
+    // bit 1 = records as [row][chunk][segment][128] instead of [segment][row][d_v], bit 2 = bulk-copy combine
+    P.tune = 7;
+    if (const char *e = getenv("GS_TUNE")) P.tune = atoi(e);
+    const bool seg_major = (P.tune & 2) == 0;
     for (int g = 0; g < n_groups; g++) {
         const int h0 = g * Hg;
         const int hg = p.H - h0 < Hg ? p.H - h0 : Hg;
@@ -875,8 +1218,24 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.ml = p.ws_ml;
         c.desc = p.ws_desc;
         c.regular_segments = 0;
-        c.seg_stride_acc = (int64_t) rows_q * p.d_v;
-        c.seg_stride_ml = (int64_t) rows_q * 2;
+        if (seg_major) {
+            c.seg_stride_acc = (int64_t) rows_q * p.d_v;
+            c.row_stride_acc = p.d_v;
+            c.chunk_stride_acc = 128;
+            c.seg_stride_ml = (int64_t) rows_q * 2;
+            c.row_stride_ml = 2;
+        } else {
+            c.seg_stride_acc = 128;  // [row][chunk][segment][128]
+            c.chunk_stride_acc = (int64_t) P.seg_cap * 128;
+            c.row_stride_acc = (int64_t) NVT * P.seg_cap * 128;
+            c.seg_stride_ml = 2;     // [row][segment][2]
+            c.row_stride_ml = (int64_t) P.seg_cap * 2;
+        }
+        P.acc_seg = (int) c.seg_stride_acc;
+        P.acc_row = (int) c.row_stride_acc;
+        P.acc_chunk = (int) c.chunk_stride_acc;
+        P.ml_seg = (int) c.seg_stride_ml;
+        P.ml_row = (int) c.row_stride_ml;
         c.n_seq = n_seq_k;
         c.T = p.T;
         c.H = hg;
@@ -891,6 +1250,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.unit_rows = P.paged ? TILE : 16;
         c.n_ctas = grid;
         c.len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
+        c.bulk = (P.tune & 4) != 0;
         int e;
         if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
         else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);

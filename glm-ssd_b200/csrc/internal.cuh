@@ -40,12 +40,18 @@ struct DecodeProblem {
 
 // Combine descriptor: how the segments of an output row are found.
 struct CombinePlan {
-    const float *acc;      // segment s, row r of the segment: acc + s*seg_stride_acc + r*d_v
-    const float *ml;       // segment s, row r of the segment: ml + s*seg_stride_ml + r*2
+    const float *acc;      // accumulators of the records (addressing below)
+    const float *ml;       // their (m, l) pairs
     const int2 *desc;      // per sequence (first_segment, n_segments), or nullptr => regular
     int regular_segments;  // desc == nullptr: segments per (sequence, token) group, consecutive
     int64_t seg_stride_acc;  // floats between the accumulator blocks of consecutive segments
     int64_t seg_stride_ml;   // floats between the (m, l) blocks of consecutive segments
+    // Generalised addressing (0 = the plain record layout [segment][row][d_v] / [segment][row][2]): column c of row r of
+    // segment s lies at acc + s*seg_stride_acc + r*row_stride_acc + (c/128)*chunk_stride_acc + c%128, its (m, l) pair at
+    // ml + s*seg_stride_ml + r*row_stride_ml.  The tcgen05 kernel keeps its records as [row][128-column chunk][segment][128],
+    // so that everything one (row, chunk) item of the combine needs is one contiguous run of memory.
+    int64_t row_stride_acc, chunk_stride_acc, row_stride_ml;
+    bool bulk;             // fetch an item's accumulators with bulk copies into shared memory (k_combine_bulk)
     int n_seq, T, H, d_v;  // H: heads in the records being merged
     int H_out, h0;         // the output has H_out heads per token and these are heads h0 .. h0+H-1 (0, 0: H_out = H)
     float *o;              // may be nullptr
@@ -60,15 +66,15 @@ struct CombinePlan {
 };
 
 int launch_decode_simt(const DecodeProblem &p, cudaStream_t st);
-// rows named by per-token position lists -> contiguous f16 rows, f32 queries -> f16, lengths and bases (gather.cu)
-int launch_gather_rows(const __half *C, const __half *C_scales, const int *sel, int sel_stride, const int *cnt, int T, int max_rows, int R, int n_groups,
-                       __half *rows_out, int32_t *lens_out, int32_t *base_out, const float *q, __half *q16, int64_t q_elems,
-                       cudaStream_t st);
 int launch_combine(const CombinePlan &c, cudaStream_t st);
 // local merge + peer-to-peer exchange of the merged records + final merge (exchange.cu)
 int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o, int32_t *status, int sm_count,
                             cudaStream_t st);
 bool decode_umma_supported(const DecodeProblem &p, const char **why);
+// position lists (the reference's sel / cnt) with f32 queries on the tcgen05 kernel: 0 launched, -1 shape not taken, else an error
+int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
+                            float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st);
+int read_list_status(int32_t *out);
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st);
 
 int launch_prefill_simt(const __half *q, const __half *k, const __half *v, void *o, int o_f16, int S, int H, int d,

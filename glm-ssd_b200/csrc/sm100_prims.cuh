@@ -118,6 +118,24 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, size a multiple of 16),
+// completion counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Four rows of a 2-D tensor, named one by one, into four consecutive rows of shared memory (the tensor map's box is
+// one row high; no multicast).  c0 is the column offset, r0..r3 the row indices.
+__device__ __forceinline__ void tma_gather4_hint(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int32_t c0, int32_t r0, int32_t r1,
+                                                 int32_t r2, int32_t r3, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
+        "l"(policy)
+        : "memory");
+}
 // L2 eviction policies: data streamed once (the latent cache) should leave L2 first, data another kernel
 // reads next (the partial records) last.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
@@ -144,6 +162,10 @@ __device__ __forceinline__ int ld_global_hint(const int *p, uint64_t policy) {
 }
 __device__ __forceinline__ void st_global_hint(float *p, float v, uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void st_global_hint_v4(float *p, float4 v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(policy)
+                 : "memory");
 }
 // Ask for one box of a tiled tensor to be brought into L2 (no destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int32_t c0, int32_t c1) {

@@ -41,23 +41,21 @@ extern "C" {
 int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride, const int *cnt,
                 float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
 
-/* Optional tensor-core path of gs_mla_attn (no counterpart in the reference).  The reference's only scratch,
- * `part`, is too small for it, so the caller lends the library one more device buffer per device:
- *   gs_mla_attn_scratch_bytes(t_max, H, max_rows): size for calls with T <= t_max (at most 512) query tokens, H heads
- *     and position lists of at most max_rows entries (sel_stride <= max_rows): about t_max * max_rows KB, since
- *     every token's rows are gathered separately; 0 if the sizes are not supported;
- *   gs_mla_attn_set_scratch(scratch, bytes, t_max, H, max_rows, stream): registers it for the current device
- *     (256-byte aligned; NULL switches the path off again).  The buffer stays the caller's; it must outlive the
- *     calls, and only one gs_mla_attn call per device may be in flight at a time while it is registered (the
- *     engine issues its forward pass on one stream).  A device reset (the engine's idle unload, runtime.cu:51-53)
- *     frees the buffer with everything else: register a new one afterwards, or NULL.
- * While a scratch is registered, gs_mla_attn calls that fit it gather the listed rows of every query token into
- * contiguous f16 rows (a Q8 cache is dequantised on the way, row by row as ops.cu:461-477 does), round the f32 queries to f16 (the precision of the f16-query entry points;
- * outputs stay within max-abs 2e-3 of the f32-query result) and run the tcgen05 decode kernel, one token = one
- * dense sequence (decode, MTP verify, and prefill chunks whose lists are short, i.e. sparse attention).  Every other
- * call (more tokens, longer lists) runs the CUDA-core kernel as before. */
-int64_t gs_mla_attn_scratch_bytes(int t_max, int H, int max_rows);
-int gs_mla_attn_set_scratch(void *scratch, int64_t bytes, int t_max, int H, int max_rows, void *stream);
+/* Which kernel gs_mla_attn runs (no counterpart in the reference).  With an f16 cache (C_scales == NULL) the call
+ * runs on the tcgen05 decode kernel whenever that kernel takes the shape: the rows a list names are fetched four at a
+ * time by gather copies straight from the cache, the f32 queries are rounded to f16 inside the kernel (the precision
+ * of the f16-query entry points; outputs stay within max-abs 2e-3 of the f32-query result), and nothing beyond the
+ * reference's own arguments is needed: with splits > 1 the split records live in `part` (as many segments as fit its
+ * T*H*splits*(R+2) floats), with splits == 1 every (token, head group) is attended by one CTA that stores o itself.
+ * Q8 caches, head counts that cannot be cut into groups of 8..48 heads and misaligned q / C run on the CUDA-core
+ * kernel, which keeps the queries in f32.
+ *   gs_mla_attn_set_impl(impl): 0 = automatic (default), 1 = always the CUDA-core kernel, 2 = the tcgen05 kernel or
+ *     cudaErrorInvalidValue.  A process-wide setting; it changes no result beyond the rounding described above.
+ *   gs_mla_attn_status(status_out, stream): synchronises `stream` and reads the sticky status word of the tcgen05
+ *     path (the reference's argument list has no workspace that could carry one): 0 = ok, else a bounded wait inside
+ *     the kernel gave up and cudaErrorLaunchTimeout is returned. */
+int gs_mla_attn_set_impl(int impl);
+int gs_mla_attn_status(int32_t *status_out /* host, may be NULL */, void *stream);
 
 /* Replaces gs_quant_q8_rows, crates/cuda/kernels/ops.cu:599-617 (Rust declaration crates/cuda/src/lib.rs:96;
  * caller crates/engine/src/forward.rs:852-856): the KV-append of the Q8 cache.  Per block of 32 values
@@ -68,6 +66,33 @@ int gs_quant_q8_rows(const float *x, void *q, void *d, int64_t n, void *stream);
  * caller crates/engine/src/forward.rs:857-860): y[i] = half_rn(x[i]) for i < n.  This is the reference's
  * KV-append. */
 int gs_f32_to_f16(const float *x, void *y, int64_t n, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * DSA k-pool indexer: produces the attended position lists (sel, cnt) gs_mla_attn consumes once the context is
+ * longer than top_k positions (caller crates/engine/src/forward.rs:864-895).  Same names, argument order and
+ * meaning as the reference.
+ * ---------------------------------------------------------------------------------------------- */
+/* Replaces gs_idx_pool, crates/cuda/kernels/ops.cu:627-672 (Rust declaration crates/cuda/src/lib.rs:101-104).
+ *   kc, gc f32 [T][Dk]   raw indexer keys / gates of positions p0 .. p0+T-1
+ *   rk, rg f32 [kpool][Dk] rings holding the rows of the pool that is still incomplete (row pos % kpool)
+ *   ape    f32 [kpool][Dk]  P f32 [pools][Dk]
+ * For every pool j of kpool positions completing inside the chunk: P[j][c] = sum_m softmax_m(gate + ape)[m][c] *
+ * key[m][c]; afterwards the rows of the trailing incomplete pool go to the rings.  One launch (the reference: two). */
+int gs_idx_pool(const float *kc, const float *gc, float *rk, float *rg, const float *ape, float *P, int p0, int T, int Dk,
+                int kpool, void *stream);
+/* Replaces gs_idx_score, ops.cu:675-712 (lib.rs:105-108): score[t][p] = sum_h w[t][h] * relu(scale * q[t][h] . P[p])
+ * for the p < (pos0 + t + 1) / kpool complete pools; q f32 [T][Hq][Dk], w f32 [T][Hq], score f32 [T][score_stride].
+ * Dk > 128 is rejected as in the reference. */
+int gs_idx_score(const float *q, const float *w, const float *P, float *score, int64_t score_stride, int pos0, int T,
+                 int kpool, int Hq, int Dk, float scale, void *stream);
+/* Replaces gs_idx_select, ops.cu:714-791 (lib.rs:109-112).  Query t (position pos0 + t) with n_pool = (pos+1)/kpool
+ * complete pools: n_pool <= top_k -> every position 0..pos; else the kpool positions of each of the top_k
+ * highest-scoring pools followed by the positions of the incomplete tail pool.  sel i32 [T][sel_stride], cnt i32 [T].
+ * The top-k is exact (radix select on the order-preserving integer image of the scores, as the reference).  Unlike
+ * the reference, whose list order and choice among pools tied at the k-th largest score depend on thread timing,
+ * the list here is deterministic: pools in ascending index, ties to the lowest indices. */
+int gs_idx_select(const float *score, int64_t score_stride, int pos0, int T, int kpool, int top_k, int *sel,
+                  int sel_stride, int *cnt, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Absorbed-MLA decode over the f16 latent cache.  Generalises gs_mla_attn (ops.cu:420-597) to
@@ -137,6 +162,28 @@ int64_t gs_mla_decode_workspace_bytes(int n_seq, int T, int H, int d_v);
 
 /* Enqueue the decode.  New entry point; the call it stands in for is forward.rs:902-906. */
 int gs_mla_decode(const gs_mla_decode_args *args /* host */, void *stream);
+
+/* One decode step's attention with the two per-head products around it (no counterpart as a single call in the
+ * reference, which issues them one by one: crates/engine/src/forward.rs:900 mm_heads(k_b), :902-906 gs_mla_attn,
+ * :907 mm_heads(v_b); mm_heads :716-733):
+ *   qabs[t][h] = k_b[h] . q[t][h];   olat[t][h] = attention of qabs over the latent rows;   ov[t][h] = v_b[h] . olat[t][h]
+ * for one sequence and T <= 8 query tokens (causal among themselves, the new rows already appended).  Four kernels in a
+ * programmatic-dependent-launch chain.  The weights are f16; the engine's quantised weight formats are not read here. */
+typedef struct gs_mla_fused_args {
+    const float *q;          /* f32 [T][H][d_q] queries before absorption (forward.rs:848) */
+    const void *k_b;         /* f16 [H][d_lat][d_q], 16-byte aligned */
+    const void *v_b;         /* f16 [H][d_out][d_lat], 16-byte aligned */
+    const void *cache;       /* f16 [cache_rows][d_lat] latent cache */
+    int64_t cache_rows;
+    const int32_t *seq_len;  /* device: rows attended by the last query token */
+    float scale;             /* 1/sqrt(d_q) in the engine (forward.rs:904) */
+    float *ov;               /* f32 [T][H][d_out] */
+    void *workspace;         /* gs_mla_fused_workspace_bytes(T, H) bytes, 256-byte aligned, zeroed once */
+    int64_t workspace_bytes;
+    int32_t T, H, d_q, d_lat, d_out; /* d_q = 256, d_lat = 512, d_out = 256 */
+} gs_mla_fused_args;
+int64_t gs_mla_fused_workspace_bytes(int T, int H);
+int gs_mla_decode_fused(const gs_mla_fused_args *args /* host */, void *stream);
 
 /* gs_mla_decode for callers that cannot allocate device memory.  It has no counterpart in the
  * reference, whose engine owns and passes every buffer (forward.rs:496-500).  Some hosts of this
@@ -262,6 +309,22 @@ typedef struct gs_mla_layer_graph gs_mla_layer_graph;
 int gs_mla_layer_graph_create(const gs_mla_layer_step *step /* host */, void *stream, gs_mla_layer_graph **out);
 int gs_mla_layer_graph_step(gs_mla_layer_graph *g, int64_t pos0, void *stream, int wait);
 int gs_mla_layer_graph_destroy(gs_mla_layer_graph *g);
+
+/* ------------------------------------------------------------------------------------------------
+ * Cache persistence for paged caches.  The reference saves and restores every per-position buffer of a layer as
+ * `unit` bytes per position, positions 0 .. upto-1 back to back (crates/engine/src/forward.rs:654-668
+ * position_caches, :672-681 save_state, :683-695 load_state; crates/engine/src/session.rs:152-204).  These two
+ * calls move a sequence between that layout and a paged pool (or a dense cache: pages == NULL, rows row0 ..),
+ * byte for byte: f16 latent rows (unit_bytes = 2 * row width), or the int8 rows and f16 scales of a Q8 cache
+ * (unit_bytes = row width, and row width / 32 * 2).
+ *   pool      [pool_rows][unit_bytes]          pages  i32 [n_pages] page ids of the sequence (device)
+ *   dst / src [upto][unit_bytes], device memory or page-locked host memory
+ *   status    optional int32 on the device: bit 19 is set (and the position skipped) when a page id points outside
+ *             the pool; read it with gs_mla_decode_status. */
+int gs_cache_export_rows(const void *pool, int64_t pool_rows, const int32_t *pages, int32_t n_pages, int32_t page_rows,
+                         int64_t row0, int64_t upto, int32_t unit_bytes, void *dst, int32_t *status, void *stream);
+int gs_cache_import_rows(void *pool, int64_t pool_rows, const int32_t *pages, int32_t n_pages, int32_t page_rows,
+                         int64_t row0, int64_t upto, int32_t unit_bytes, const void *src, int32_t *status, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Diagnostics.

@@ -710,3 +710,56 @@ void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T
         free(ord);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * The attention call with its two per-head products (crates/engine/src/forward.rs:900-907):
+ *   qabs[t][h][r] = sum_k k_b[h][r][k] * q[t][h][k]        mm_heads(&w.k_b, ...), forward.rs:900, :716-733
+ *   olat[t][h]    = attention of qabs over latent rows 0 .. n_t-1, n_t = seq_len - (T-1-t)   (forward.rs:902-906;
+ *                   dense list of ops.cu:728-731, new rows already appended)
+ *   ov[t][h][j]   = sum_r v_b[h][j][r] * olat[t][h][r]      mm_heads(&w.v_b, ...), forward.rs:907
+ * everything in fp32 as in the reference (its weights are quantised formats read into fp32 products; here they are
+ * f16 values widened exactly).  q f32 [T][H][d_q]; k_b f16 [H][R][d_q]; v_b f16 [H][d_out][R]; cache f16 [rows][R].
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+    const float *q;
+    const uint16_t *k_b, *v_b, *cache;
+    int seq_len;
+    float scale;
+    float *ov;
+    int T, H, d_q, R, d_out;
+} fused_ctx_t;
+
+static void fused_item(void *vctx, int64_t item) {
+    fused_ctx_t *c = (fused_ctx_t *) vctx;
+    const int t = (int) (item / c->H), h = (int) (item % c->H);
+    const float *lut = h2f_table();
+    float *qabs = (float *) malloc(sizeof(float) * (size_t) c->R);
+    float *olat = (float *) malloc(sizeof(float) * (size_t) c->R);
+    const float *qh = c->q + ((int64_t) t * c->H + h) * c->d_q;
+    for (int r = 0; r < c->R; r++) {
+        const uint16_t *w = c->k_b + ((int64_t) h * c->R + r) * c->d_q;
+        float a = 0.f;
+        for (int k = 0; k < c->d_q; k++) a += lut[w[k]] * qh[k];
+        qabs[r] = a;
+    }
+    int64_t n = (int64_t) c->seq_len - (c->T - 1 - t);
+    if (n < 0) n = 0;
+    float *buf = (float *) malloc(sizeof(float) * (size_t) (n > 0 ? n : 1));
+    attend_row(qabs, c->R, c->R, c->cache, c->R, c->cache, c->R, NULL, 0, n, c->scale, 1, olat, NULL, NULL, buf);
+    float *out = c->ov + ((int64_t) t * c->H + h) * c->d_out;
+    for (int j = 0; j < c->d_out; j++) {
+        const uint16_t *w = c->v_b + ((int64_t) h * c->d_out + j) * c->R;
+        float a = 0.f;
+        for (int r = 0; r < c->R; r++) a += lut[w[r]] * olat[r];
+        out[j] = a;
+    }
+    free(buf);
+    free(olat);
+    free(qabs);
+}
+
+int oracle_mla_fused(const float *q, const uint16_t *k_b, const uint16_t *v_b, const uint16_t *cache, int seq_len, float scale,
+                     float *ov, int T, int H, int d_q, int R, int d_out, int threads) {
+    fused_ctx_t c = {q, k_b, v_b, cache, seq_len, scale, ov, T, H, d_q, R, d_out};
+    return run_pool(fused_item, &c, (int64_t) T * H, threads);
+}

@@ -39,6 +39,9 @@ void oracle_norm_rope_append(const float *x, const float *w, float eps, uint16_t
                              int64_t pos0, double base);
 void oracle_rope_f16(uint16_t *x, int S, int H, int d, int d_rope, int64_t pos0, double base);
 
+/* attention with its two per-head products (forward.rs:900-907), fp32 */
+int oracle_mla_fused(const float *q, const uint16_t *k_b, const uint16_t *v_b, const uint16_t *cache, int seq_len, float scale,
+                     float *ov, int T, int H, int d_q, int R, int d_out, int threads);
 /* DSA k-pool indexer (ops.cu:619-791) */
 void oracle_idx_pool(const float *kc, const float *gc, float *rk, float *rg, const float *ape, float *P, int p0, int T,
                      int Dk, int kpool);

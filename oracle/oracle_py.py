@@ -47,6 +47,11 @@ def lib() -> C.CDLL:
     L.oracle_rope_append.argtypes = [vp, vp, i32, i32, i32, i64, C.c_double]
     L.oracle_norm_rope_append.argtypes = [vp, vp, f32, vp, i32, i32, i32, i64, C.c_double]
     L.oracle_rope_f16.argtypes = [vp, i32, i32, i32, i32, i64, C.c_double]
+    L.oracle_mla_fused.restype = i32
+    L.oracle_mla_fused.argtypes = [vp, vp, vp, vp, i32, f32, vp, i32, i32, i32, i32, i32, i32]
+    L.oracle_idx_pool.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
+    L.oracle_idx_score.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32]
+    L.oracle_idx_select.argtypes = [vp, i64, i32, i32, i32, i32, vp, i32, vp]
     _lib = L
     return L
 
@@ -197,3 +202,43 @@ def dequant_q8(q, d):
     out = np.empty(q.shape, np.uint16)
     lib().oracle_dequant_q8(_p(q), _p(db), _p(out), q.size // 32)
     return out.view(np.float16)
+
+
+# ---- DSA k-pool indexer (crates/cuda/kernels/ops.cu:619-791) -------------------------------------------
+
+def idx_pool(kc, gc, rk, rg, ape, P, p0, kpool):
+    """In place on rk, rg (rings [kpool,Dk]) and P ([pools,Dk]); kc, gc f32 [T,Dk] are the chunk's rows."""
+    kc, gc, ape = _c(kc, np.float32), _c(gc, np.float32), _c(ape, np.float32)
+    assert rk.flags.c_contiguous and rg.flags.c_contiguous and P.flags.c_contiguous
+    T, Dk = kc.shape
+    lib().oracle_idx_pool(_p(kc), _p(gc), _p(rk), _p(rg), _p(ape), _p(P), int(p0), T, Dk, int(kpool))
+
+
+def idx_score(q, w, P, score, pos0, kpool, scale):
+    """q f32 [T,Hq,Dk], w f32 [T,Hq], P f32 [pools,Dk]; fills score f32 [T,stride] in place."""
+    q, w, P = _c(q, np.float32), _c(w, np.float32), _c(P, np.float32)
+    T, Hq, Dk = q.shape
+    assert score.flags.c_contiguous and score.dtype == np.float32
+    lib().oracle_idx_score(_p(q), _p(w), _p(P), _p(score), score.shape[1], int(pos0), T, int(kpool), Hq, Dk, float(scale))
+
+
+def idx_select(score, pos0, kpool, top_k, sel_stride):
+    """score f32 [T,stride] -> (sel i32 [T,sel_stride], cnt i32 [T]); pools in ascending index, ties to the lowest."""
+    score = _c(score, np.float32)
+    T = score.shape[0]
+    sel = np.full((T, sel_stride), -1, np.int32)
+    cnt = np.zeros(T, np.int32)
+    lib().oracle_idx_select(_p(score), score.shape[1], int(pos0), T, int(kpool), int(top_k), _p(sel), sel_stride, _p(cnt))
+    return sel, cnt
+
+
+def mla_fused(q, k_b, v_b, cache, seq_len, scale, threads=0):
+    """q f32 [T,H,d_q]; k_b f16 [H,R,d_q]; v_b f16 [H,d_out,R]; cache f16 [rows,R] -> ov f32 [T,H,d_out]
+    (absorb, attend, expand: forward.rs:900-907)."""
+    q = _c(q, np.float32)
+    T, H, d_q = q.shape
+    kb, vb, cb = f16_bits(k_b), f16_bits(v_b), f16_bits(cache)
+    R, d_out = kb.shape[1], vb.shape[1]
+    ov = np.empty((T, H, d_out), np.float32)
+    lib().oracle_mla_fused(_p(q), _p(kb), _p(vb), _p(cb), int(seq_len), float(scale), _p(ov), T, H, d_q, R, d_out, threads)
+    return ov

@@ -1,10 +1,10 @@
 """Generate the golden fixtures that pin the CPU oracle: outputs of the reference engine's own CUDA
-kernels (gs_mla_attn, gs_f32_to_f16, gs_quant_q8_rows), compiled unmodified into oracle/_ref/libglmssd_ref.so by
+kernels (gs_mla_attn, gs_f32_to_f16, gs_quant_q8_rows, gs_idx_pool / gs_idx_score / gs_idx_select), compiled unmodified into oracle/_ref/libglmssd_ref.so by
 oracle/build.py and run on a GPU.
 
     python tests/golden/make_golden_from_ref.py <out_dir>
 
-writes ref_*.npz and refq8_cache.npz into <out_dir>; the committed copies live beside this script.  Inputs are seeded
+writes ref_*.npz, refq8_cache.npz and refidx_pool_score_select.npz into <out_dir>; the committed copies live beside this script.  Inputs are seeded
 (numpy default_rng) so the run is reproducible.  Needs a CUDA device; not used at test time.
 """
 import ctypes as C
@@ -87,6 +87,62 @@ def main(out_dir: str) -> None:
                         d=cs.cpu().numpy().view(np.uint16), q=q, sel=sel, cnt=cnt, scale=np.float32(1 / 16),
                         o=o.cpu().numpy())
     print("wrote q8_cache")
+    make_indexer(ref, out_dir)
+
+
+def make_indexer(ref, out_dir: str) -> None:
+    """DSA k-pool indexer: the reference's gs_idx_pool over three consecutive chunks (a pool straddling a chunk
+    boundary goes through the rings), gs_idx_score and gs_idx_select on the result (ops.cu:619-791).  Scores are
+    continuous random values, so the k-th largest is unique and the selected set is well defined; the order inside
+    sel is not fixed in the reference (slots are handed out by an atomic counter), so the fixture keeps each list
+    sorted."""
+    vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_int64
+    for fn, args in (("gs_idx_pool", [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+                     ("gs_idx_score", [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp]),
+                     ("gs_idx_select", [vp, i64, i32, i32, i32, i32, vp, i32, vp, vp])):
+        getattr(ref, fn).restype = i32
+        getattr(ref, fn).argtypes = args
+    rng = np.random.default_rng(301)
+    Dk, kpool, Hq, top_k = 128, 4, 8, 6  # top_k counts pools
+    chunks = [5, 9, 17]                   # tokens per chunk: 31 positions, 7 complete pools
+    n_pos = sum(chunks)
+    kc = rng.standard_normal((n_pos, Dk), dtype=np.float32)
+    gc = rng.standard_normal((n_pos, Dk), dtype=np.float32)
+    ape = rng.standard_normal((kpool, Dk), dtype=np.float32) * np.float32(0.3)
+    pools = n_pos // kpool + 1
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    rk, rg = torch.zeros((kpool, Dk), device="cuda"), torch.zeros((kpool, Dk), device="cuda")
+    P = torch.zeros((pools, Dk), device="cuda")
+    aped = dev(ape)
+    p0 = 0
+    for T in chunks:
+        kd, gd = dev(kc[p0:p0 + T]), dev(gc[p0:p0 + T])
+        assert ref.gs_idx_pool(kd.data_ptr(), gd.data_ptr(), rk.data_ptr(), rg.data_ptr(), aped.data_ptr(), P.data_ptr(), p0, T,
+                               Dk, kpool, None) == 0
+        torch.cuda.synchronize()
+        p0 += T
+    # queries at the last chunk's positions
+    T, pos0 = chunks[-1], n_pos - chunks[-1]
+    q = rng.standard_normal((T, Hq, Dk), dtype=np.float32)
+    w = rng.standard_normal((T, Hq), dtype=np.float32)
+    stride = pools
+    score = torch.zeros((T, stride), device="cuda")
+    assert ref.gs_idx_score(dev(q).data_ptr(), dev(w).data_ptr(), P.data_ptr(), score.data_ptr(), stride, pos0, T, kpool, Hq, Dk,
+                            1 / np.sqrt(Dk), None) == 0
+    sel_stride = (top_k + 1) * kpool
+    sel = torch.full((T, sel_stride), -1, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(T, dtype=torch.int32, device="cuda")
+    assert ref.gs_idx_select(score.data_ptr(), stride, pos0, T, kpool, top_k, sel.data_ptr(), sel_stride, cnt.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    sel_h, cnt_h = sel.cpu().numpy(), cnt.cpu().numpy()
+    for t in range(T):
+        sel_h[t, :cnt_h[t]] = np.sort(sel_h[t, :cnt_h[t]])
+        sel_h[t, cnt_h[t]:] = -1
+    np.savez_compressed(os.path.join(out_dir, "refidx_pool_score_select.npz"), kc=kc, gc=gc, ape=ape, chunks=np.array(chunks, np.int32),
+                        kpool=np.int32(kpool), top_k=np.int32(top_k), P=P.cpu().numpy(), rk=rk.cpu().numpy(), rg=rg.cpu().numpy(),
+                        q=q, w=w, pos0=np.int32(pos0), scale=np.float32(1 / np.sqrt(Dk)), score=score.cpu().numpy(),
+                        sel_sorted=sel_h, cnt=cnt_h)
+    print("wrote indexer")
 
 
 if __name__ == "__main__":

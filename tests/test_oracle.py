@@ -245,3 +245,115 @@ def test_decode_cut_into_key_ranges_equals_the_plain_decode(oracle):
         a = oracle.mla_decode(q, cache, [n], 1 / 16)
         b = oracle.mla_decode(q, cache, [n], 1 / 16, key_splits=ks)
         assert np.abs(a - b).max() <= 2e-6, (n, T, ks, np.abs(a - b).max())
+
+
+# ---- DSA k-pool indexer (crates/cuda/kernels/ops.cu:619-791) ------------------------------------------------
+
+def _np_pool(kc, gc, ape, kpool):
+    """float64 pooled keys of all complete pools of a whole sequence (no chunking, no rings)."""
+    n = kc.shape[0] // kpool
+    k = kc[:n * kpool].reshape(n, kpool, -1).astype(np.float64)
+    g = gc[:n * kpool].reshape(n, kpool, -1).astype(np.float64) + ape.astype(np.float64)[None]
+    e = np.exp(g - g.max(axis=1, keepdims=True))
+    return (e * k).sum(axis=1) / e.sum(axis=1)
+
+
+def test_idx_pool_chunked_with_rings_equals_whole_sequence_pooling(oracle):
+    rng = np.random.default_rng(31)
+    Dk, kpool = 32, 4
+    chunks = [5, 1, 1, 9, 3, 17, 2]  # pools straddle chunk boundaries: their older rows come back from the rings
+    n = sum(chunks)
+    kc = rng.standard_normal((n, Dk), dtype=np.float32)
+    gc = rng.standard_normal((n, Dk), dtype=np.float32) * np.float32(2)
+    ape = rng.standard_normal((kpool, Dk), dtype=np.float32)
+    rk, rg = np.zeros((kpool, Dk), np.float32), np.zeros((kpool, Dk), np.float32)
+    P = np.zeros((n // kpool + 1, Dk), np.float32)
+    p0 = 0
+    for T in chunks:
+        oracle.idx_pool(kc[p0:p0 + T], gc[p0:p0 + T], rk, rg, ape, P, p0, kpool)
+        p0 += T
+    want = _np_pool(kc, gc, ape, kpool)
+    assert np.abs(P[:n // kpool] - want).max() <= 1e-5
+    assert (P[n // kpool:] == 0).all()  # the incomplete tail pool is not written
+    tail = n - n % kpool
+    for pos in range(tail, n):  # and its raw rows wait in the rings
+        assert np.array_equal(rk[pos % kpool], kc[pos]) and np.array_equal(rg[pos % kpool], gc[pos])
+
+
+def test_idx_score_and_select_against_numpy(oracle):
+    rng = np.random.default_rng(32)
+    T, pos0, kpool, Hq, Dk, top_k = 5, 203, 4, 3, 16, 10
+    pools = (pos0 + T) // kpool + 1
+    q = rng.standard_normal((T, Hq, Dk), dtype=np.float32)
+    w = rng.standard_normal((T, Hq), dtype=np.float32)
+    P = rng.standard_normal((pools, Dk), dtype=np.float32)
+    score = np.full((T, pools), np.float32(7.5))
+    oracle.idx_score(q, w, P, score, pos0, kpool, 0.25)
+    sel, cnt = oracle.idx_select(score, pos0, kpool, top_k, (top_k + 1) * kpool)
+    for t in range(T):
+        n_pool = (pos0 + t + 1) // kpool
+        d = np.einsum("hc,pc->hp", q[t].astype(np.float64), P[:n_pool].astype(np.float64)) * 0.25
+        want = (w[t].astype(np.float64)[:, None] * np.maximum(d, 0)).sum(axis=0)
+        assert np.abs(score[t, :n_pool] - want).max() <= 1e-5
+        assert (score[t, n_pool:] == 7.5).all()  # pools not complete at this query's position are left alone
+        top = np.sort(np.argsort(-score[t, :n_pool], kind="stable")[:top_k])
+        lst = np.concatenate([np.arange(p * kpool, (p + 1) * kpool) for p in top] + [np.arange(n_pool * kpool, pos0 + t + 1)])
+        assert cnt[t] == lst.size and np.array_equal(sel[t, :cnt[t]], lst)
+    # below top_k pools every position is attended (ops.cu:728-731)
+    sel, cnt = oracle.idx_select(score, 10, kpool, top_k, (top_k + 1) * kpool)
+    assert cnt[0] == 11 and np.array_equal(sel[0, :11], np.arange(11))
+
+
+def test_idx_select_ties_go_to_the_lowest_indices(oracle):
+    score = np.array([[1.0, 2.0, 2.0, 2.0, 3.0, 2.0, -0.0, 0.0, 2.0]], np.float32)
+    sel, cnt = oracle.idx_select(score, 8, 1, 3, 4)  # kpool 1: nine complete pools, three taken
+    assert cnt[0] == 3 and sel[0, :3].tolist() == [1, 2, 4]  # 3.0 and the first two of the 2.0s
+    sel, cnt = oracle.idx_select(score, 8, 1, 8, 9)
+    assert sorted(sel[0, :8].tolist()) == [0, 1, 2, 3, 4, 5, 7, 8]  # -0.0 sorts below +0.0 (ops.cu:718-721)
+
+
+def test_indexer_golden_vectors_from_reference_kernels(oracle):
+    """Outputs of the reference's own gs_idx_pool / gs_idx_score / gs_idx_select (compiled unmodified, run on a B200)
+    pin the oracle's indexer functions.  The fixture is made by tests/golden/make_golden_from_ref.py."""
+    path = os.path.join(HERE, "golden", "refidx_pool_score_select.npz")
+    if not os.path.exists(path):
+        pytest.skip("no indexer golden fixture committed yet")
+    g = np.load(path)
+    kc, gc, ape, kpool, top_k = g["kc"], g["gc"], g["ape"], int(g["kpool"]), int(g["top_k"])
+    Dk = kc.shape[1]
+    rk, rg = np.zeros((kpool, Dk), np.float32), np.zeros((kpool, Dk), np.float32)
+    P = np.zeros_like(g["P"])
+    p0 = 0
+    for T in g["chunks"]:
+        oracle.idx_pool(kc[p0:p0 + T], gc[p0:p0 + T], rk, rg, ape, P, p0, kpool)
+        p0 += int(T)
+    assert np.abs(P - g["P"]).max() <= 1e-5
+    assert np.array_equal(rk, g["rk"]) and np.array_equal(rg, g["rg"])
+    score = np.zeros_like(g["score"])
+    oracle.idx_score(g["q"], g["w"], g["P"], score, int(g["pos0"]), kpool, float(g["scale"]))
+    assert np.abs(score - g["score"]).max() <= 1e-5
+    sel, cnt = oracle.idx_select(g["score"], int(g["pos0"]), kpool, top_k, g["sel_sorted"].shape[1])
+    assert np.array_equal(cnt, g["cnt"])
+    for t in range(cnt.size):
+        assert np.array_equal(np.sort(sel[t, :cnt[t]]), g["sel_sorted"][t, :cnt[t]])
+
+
+def test_fused_step_oracle_against_float64(oracle):
+    """absorb k_b, attend, expand v_b (crates/engine/src/forward.rs:900-907) against a float64 restatement."""
+    rng = np.random.default_rng(33)
+    T, H, n = 2, 3, 41
+    q = rng.standard_normal((T, H, 256), dtype=np.float32)
+    kb = (rng.standard_normal((H, 512, 256), dtype=np.float32) / 16).astype(np.float16)
+    vb = (rng.standard_normal((H, 256, 512), dtype=np.float32) / 22.6).astype(np.float16)
+    c = (rng.standard_normal((n, 512), dtype=np.float32) * 0.5).astype(np.float16)
+    got = oracle.mla_fused(q, kb, vb, c, n, 1 / 16)
+    qa = np.einsum("hrk,thk->thr", kb.astype(np.float64), q.astype(np.float64))
+    want = np.zeros((T, H, 256))
+    for t in range(T):
+        nt = n - (T - 1 - t)  # the T new rows are causal among themselves
+        for h in range(H):
+            s = (c[:nt].astype(np.float64) @ qa[t, h]) / 16
+            p = np.exp(s - s.max())
+            want[t, h] = vb[h].astype(np.float64) @ ((p / p.sum()) @ c[:nt].astype(np.float64))
+    assert np.abs(got - want).max() <= 2e-6
+    assert np.abs(oracle.mla_fused(q, kb, vb, c, 0, 1 / 16)).max() == 0.0  # nothing attended: zeros (ops.cu:535)

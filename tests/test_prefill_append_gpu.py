@@ -205,3 +205,50 @@ def test_norm_rope_append_vs_oracle(pkg, cuda, oracle, d_row, d_rope, with_w):
     # the sum of squares is added up in another order than the oracle's: at most one f16 step apart
     ulp = np.maximum(np.abs(v), 2.0 ** -14) * 2.0 ** -10
     assert np.all(np.abs(g - v) <= ulp + 4e-3 * (np.arange(d_row) >= d_row - d_rope))
+
+
+def test_checked_append_skips_what_is_out_of_range_and_flags_it(pkg, cuda, oracle):
+    """gs_rope_kv_append_checked: a position beyond the sequence's page-table row, a page id outside the pool and a
+    negative position write nothing and set bit 17 of the status word; the other rows land as with the plain call."""
+    import ctypes as C
+    rng = np.random.default_rng(13)
+    T, stride = 2, 3
+    pos0 = np.array([10, 3 * 64 - 1, -1, 64], np.int32)  # ok | second row falls off the table row | negative | bad page id
+    n_pages = 8
+    pt = np.array([[0, 1, 2], [3, 4, 5], [6, 6, 6], [7, 9999, 7]], np.int32)
+    pool = np.zeros((n_pages * 64, 576), np.float16)
+    kv = rng.standard_normal((len(pos0), T, 576), dtype=np.float32)
+    pd, st = to_dev(cuda, pool), cuda.zeros(1, dtype=cuda.int32, device="cuda")
+    kvd, posd, ptd = to_dev(cuda, kv), to_dev(cuda, pos0), to_dev(cuda, pt)  # held until the call has run
+    L = pkg._lib.load()
+    rc = L.gs_rope_kv_append_checked(kvd.data_ptr(), pd.data_ptr(), pool.shape[0], posd.data_ptr(), None,
+                                     ptd.data_ptr(), stride, 64, len(pos0), T, 576, 64, 10000.0, st.data_ptr(), None)
+    assert rc == 0, L.gs_attn_last_error_string()
+    cuda.cuda.synchronize()
+    assert int(st.item()) == 1 << 17
+    got = pd.cpu().numpy()
+    written = np.zeros(pool.shape[0], bool)
+    for b, t in ((0, 0), (0, 1), (1, 0), (2, 1)):  # the rows that are in range (sequence 2's second row is position 0)
+        pos = int(pos0[b]) + t
+        row = pt[b, pos // 64] * 64 + pos % 64
+        written[row] = True
+        want = oracle.rope_append(kv[b], int(pos0[b]))[t]
+        assert np.array_equal(got[row, :512].view(np.uint16), want[:512].view(np.uint16))
+    assert (got[~written] == 0).all()
+    st2 = C.c_int32(0)
+    assert L.gs_mla_decode_status(st.data_ptr(), C.byref(st2), None) != 0 and st2.value == 1 << 17
+
+
+def test_prefill_checked_leaves_status_clear(pkg, cuda, oracle):
+    Q, K, V = _qkv(5, 300, 2, 256)
+    o = cuda.zeros((300, 2, 256), dtype=cuda.float32, device="cuda")
+    st = cuda.zeros(1, dtype=cuda.int32, device="cuda")
+    L = pkg._lib.load()
+    Qd, Kd, Vd = to_dev(cuda, Q), to_dev(cuda, K), to_dev(cuda, V)  # held until the call has run
+    rc = L.gs_prefill_attn_checked(Qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), o.data_ptr(), 0,
+                                   300, 2, 256, 0, 1 / 16, 2, st.data_ptr(), None)
+    assert rc == 0, L.gs_attn_last_error_string()
+    cuda.cuda.synchronize()
+    assert int(st.item()) == 0
+    check_close(o.cpu().numpy(), oracle.prefill(Q, K, V, 1 / 16), "prefill (checked entry)")
+    assert L.gs_prefill_attn_checked(None, None, None, None, 0, 300, 2, 256, 0, 1 / 16, 2, None, None) == 1

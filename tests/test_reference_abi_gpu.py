@@ -14,6 +14,19 @@ pytestmark = pytest.mark.gpu
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "libglmssd_ref.so")
 
 
+class _Impl:
+    """gs_mla_attn_set_impl(impl) for the duration of a block; automatic choice afterwards."""
+
+    def __init__(self, L, impl):
+        self.L, self.impl = L, impl
+
+    def __enter__(self):
+        assert self.L.gs_mla_attn_set_impl(self.impl) == 0
+
+    def __exit__(self, *exc):
+        assert self.L.gs_mla_attn_set_impl(0) == 0
+
+
 def _legacy_inputs(seed, T, H, n, ctx, dense=True):
     rng = np.random.default_rng(seed)
     q = rng.standard_normal((T, H, 512), dtype=np.float32)
@@ -69,8 +82,9 @@ def test_gs_mla_attn_prefill_shape(pkg, cuda, oracle):
 ENGINE_PART_FLOATS = 128 * (16 * 512 + 32)  # the engine's `part` allocation (crates/engine/src/forward.rs:498)
 
 
+@pytest.mark.parametrize("impl", [0, 1])
 @pytest.mark.parametrize("T,H,splits", [(256, 64, 1), (8, 64, 4), (1, 64, 16), (2, 64, 4)])
-def test_gs_mla_attn_stays_inside_the_engines_part_buffer(pkg, cuda, oracle, T, H, splits):
+def test_gs_mla_attn_stays_inside_the_engines_part_buffer(pkg, cuda, oracle, T, H, splits, impl):
     """The engine passes one `part` buffer of 128 * (16*512 + 32) floats to every call: decode (T = 1, 16 splits),
     MTP verify (T = 2, 4 splits), chunks of up to 8 tokens with 4 splits, and prefill chunks of up to 256 tokens
     with splits = 1, where the reference never touches it (ops.cu:531-538).  A canary tail behind the usable part
@@ -82,8 +96,10 @@ def test_gs_mla_attn_stays_inside_the_engines_part_buffer(pkg, cuda, oracle, T, 
     o = torch.zeros((T, H, 512), dtype=torch.float32, device="cuda")
     tail = 1 << 16
     part = torch.full((ENGINE_PART_FLOATS + tail,), -7.25, dtype=torch.float32, device="cuda")
-    rc = pkg._lib.load().gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16,
-                                     o.data_ptr(), part.data_ptr(), T, H, 512, splits, None)
+    L = pkg._lib.load()
+    with _Impl(L, impl):  # the automatic choice (tcgen05 kernel, records or none in `part`) and the CUDA-core kernel
+        rc = L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1], nd.data_ptr(), 1 / 16,
+                           o.data_ptr(), part.data_ptr(), T, H, 512, splits, None)
     assert rc == 0
     torch.cuda.synchronize()
     assert bool((part[ENGINE_PART_FLOATS:] == -7.25).all()), "gs_mla_attn wrote past the engine's part buffer"
@@ -134,9 +150,13 @@ def test_reference_kernel_pins_oracle_and_agrees_with_ours(pkg, cuda, oracle, T,
     q, Cc, sel, cnt = _legacy_inputs(7 * T + n, T, H, n, max(n, 1) + 64, dense)
     o_ref = _call(cuda, ref.gs_mla_attn, q, Cc, sel, cnt, splits)
     o_orc = oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16)
-    o_new = _call(cuda, pkg._lib.load().gs_mla_attn, q, Cc, sel, cnt, splits)
+    L = pkg._lib.load()
+    with _Impl(L, 1):
+        o_new = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
+    o_auto = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
     check_close(o_orc, o_ref, "oracle vs reference kernel", 2e-5, 2e-6)
-    check_close(o_new, o_ref, "ours vs reference kernel", 2e-5, 2e-6)
+    check_close(o_new, o_ref, "ours (CUDA-core kernel, f32 queries) vs reference kernel", 2e-5, 2e-6)
+    check_close(o_auto, o_ref, "ours (automatic choice: tcgen05 kernel, f16-rounded queries) vs reference kernel")
 
 
 # ---- Q8 latent cache (int8 rows + one f16 scale per 32 values; crates/cuda/kernels/ops.cu:427, :461-477) ----
@@ -216,60 +236,62 @@ def test_reference_q8_kernels_pin_oracle(pkg, cuda, oracle):
     check_close(o_new, o_ref, "ours vs reference kernel (q8)", 2e-5, 2e-6)
 
 
-# ---- tensor-core path of gs_mla_attn (opt-in through a caller-lent scratch) --------------------------------
+# ---- kernel choice of gs_mla_attn: tcgen05 kernel by default for f16 caches, CUDA-core kernel as the second opinion ----
 
-@pytest.mark.parametrize("T,H,n,dense", [(1, 64, 2052, False), (2, 64, 2052, False), (1, 32, 700, False), (4, 16, 33, False),
-                                         (1, 64, 0, True), (2, 48, 1, True), (3, 64, 1000, True), (40, 64, 300, False),
-                                         (256, 16, 70, False)])
-def test_gs_mla_attn_tensor_path_vs_oracle_and_cuda_core_path(pkg, cuda, oracle, T, H, n, dense):
+@pytest.mark.parametrize("T,H,n,dense,splits", [
+    (1, 64, 2052, False, 16), (2, 64, 2052, False, 4), (1, 32, 700, False, 16), (4, 16, 33, False, 4),
+    (1, 64, 0, True, 16), (2, 48, 1, True, 4), (3, 64, 1000, True, 4), (40, 64, 300, False, 4), (256, 16, 70, False, 1),
+    (9, 80, 130, False, 1), (1, 16, 2052, False, 1), (8, 64, 515, False, 4), (2, 96, 64, True, 4), (5, 64, 63, False, 1),
+])
+def test_gs_mla_attn_tensor_kernel_vs_oracle_and_cuda_core_kernel(pkg, cuda, oracle, T, H, n, dense, splits):
+    """The same call on both kernels: the CUDA-core kernel (f32 queries) and the tcgen05 kernel fed from the position
+    lists by gather copies (queries rounded to f16 in the kernel).  splits > 1: records in `part`; splits == 1 or a
+    `part` too small for enough records: one CTA per (token, head group) that stores o itself."""
     q, Cc, sel, cnt = _legacy_inputs(T * 31 + n + H, T, H, n, max(n, 1) + 3000, dense)
     L = pkg._lib.load()
-    slow = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
-    scratch = pkg.mla_attn_scratch(max(T, 4), H, sel.shape[1] + 5)
-    try:
-        fast = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
-        cuda.cuda.synchronize()
-        st = int(scratch[:4].view(cuda.int32)[0])
-    finally:
-        pkg.mla_attn_scratch_off()
-    assert st == 0
+    with _Impl(L, 1):
+        slow = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
+    with _Impl(L, 2):
+        fast = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
+    st = C.c_int32(-1)
+    assert L.gs_mla_attn_status(C.byref(st), None) == 0 and st.value == 0
+    auto = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
     want = oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16)
-    check_close(slow, want, "CUDA-core path")
-    check_close(fast, want, "tensor-core path")          # f16-rounded queries: the tolerance of the f16-query entry points
+    check_close(slow, want, "CUDA-core kernel", 2e-5, 2e-6)
+    check_close(fast, want, "tcgen05 kernel")  # f16-rounded queries: the tolerance of the f16-query entry points
+    assert np.array_equal(auto, fast), "the automatic choice takes the tcgen05 kernel for an f16 cache"
     if n > 8:
-        check_not_degenerate(fast[-1], "tensor-core path")
-    # after unregistering, the exact path is back
-    again = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
-    assert np.array_equal(again, slow)
+        check_not_degenerate(fast[-1], "tcgen05 kernel")
 
 
-def test_gs_mla_attn_tensor_path_falls_back_when_the_call_does_not_fit(pkg, cuda, oracle):
+def test_gs_mla_attn_lists_with_scattered_unsorted_and_repeated_rows(pkg, cuda, oracle):
+    """Position lists are arbitrary: unsorted, with repeats, not in groups of four, different lengths per token."""
+    rng = np.random.default_rng(5)
+    T, H, ctx = 3, 32, 5000
+    q = rng.standard_normal((T, H, 512), dtype=np.float32)
+    Cc = (rng.standard_normal((ctx, 512), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+    cnt = np.array([777, 1, 130], np.int32)
+    sel = rng.integers(0, ctx, size=(T, 800)).astype(np.int32)
+    sel[0, 5:9] = sel[0, 4]  # one row named five times
     L = pkg._lib.load()
-    scratch = pkg.mla_attn_scratch(2, 64, 512)
-    try:
-        # five tokens > t_max, a list longer than max_rows, other head count, Q8 cache: all on the CUDA-core kernel
-        for T, H, n in ((5, 64, 100), (1, 64, 900), (1, 32, 100)):
-            q, Cc, sel, cnt = _legacy_inputs(T + n, T, H, n, n + 50, False)
-            got = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
-            check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "fallback", 2e-5, 2e-6)
-    finally:
-        pkg.mla_attn_scratch_off()
-    assert L.gs_mla_attn_scratch_bytes(513, 64, 100) == 0 and L.gs_mla_attn_scratch_bytes(4, 72, 100) == 0 and L.gs_mla_attn_scratch_bytes(4, 64, 100) > 0
-    assert L.gs_mla_attn_set_scratch(1 << 8, 16, 1, 64, 100, None) != 0  # too small
+    for splits in (1, 4):
+        with _Impl(L, 2):
+            got = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, splits)
+        check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), f"lists with repeats, splits {splits}")
 
 
-@pytest.mark.parametrize("T,H,n", [(1, 64, 2052), (2, 32, 700), (3, 16, 40)])
-def test_gs_mla_attn_tensor_path_q8_cache(pkg, cuda, oracle, T, H, n):
-    q, Cc, sel, cnt = _legacy_inputs(T * 13 + n, T, H, n, n + 3000, False)
-    cq, cs = oracle.quant_q8_rows(Cc.astype(np.float32))
+def test_gs_mla_attn_kernel_choice_limits(pkg, cuda, oracle):
     L = pkg._lib.load()
-    scratch = pkg.mla_attn_scratch(4, H, sel.shape[1] + 5)
-    try:
-        fast = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, 4, scales=cs)
-        cuda.cuda.synchronize()
-        assert int(scratch[:4].view(cuda.int32)[0]) == 0
-    finally:
-        pkg.mla_attn_scratch_off()
-    want = oracle.mla_attn_ref(q, oracle.dequant_q8(cq, cs), sel, cnt, 1 / 16)
-    check_close(fast, want, "tensor-core path, q8 cache")
-    check_not_degenerate(fast[-1], "tensor-core path, q8 cache")
+    # a Q8 cache and 128 heads (not cut into groups of 8..48) stay on the CUDA-core kernel: exact against the oracle
+    q, Cc, sel, cnt = _legacy_inputs(3, 1, 128, 100, 150, False)
+    got = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
+    check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "128 heads", 2e-5, 2e-6)
+    with _Impl(L, 2):
+        T, H, R = q.shape
+        o = cuda.zeros((T, H, R), dtype=cuda.float32, device="cuda")
+        part = cuda.zeros(T * H * 4 * (R + 2), dtype=cuda.float32, device="cuda")
+        qd, cd, sd, nd = to_dev(cuda, q), to_dev(cuda, Cc), to_dev(cuda, sel), to_dev(cuda, cnt)
+        rc = L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), sel.shape[1],
+                           nd.data_ptr(), 1 / 16, o.data_ptr(), part.data_ptr(), T, H, R, 4, None)
+        assert rc == 1  # cudaErrorInvalidValue: the tcgen05 kernel was demanded and does not take 128 heads
+    assert L.gs_mla_attn_set_impl(3) == 1
