@@ -7,6 +7,7 @@
 // trip to memory.
 #pragma once
 #include "internal.cuh"
+#include "sm100_prims.cuh"
 
 namespace gs {
 
@@ -233,6 +234,76 @@ __device__ __forceinline__ bool combine_item_compute(const CombinePlan &C, const
     col_out = col;
     __syncthreads();  // shared memory is reused by the next item
     return holds;
+}
+
+// The records of the tcgen05 kernel ([segment][row][d_v]) fetched by ONE tiled 3-D TMA copy: what an item (output row,
+// 128 columns) needs is one 512-byte piece per segment, a whole record apart from the next - a box
+// {128, 1, n_ctas} of the tensor {d_v, rows, segments}.  The box always spans n_ctas segments (a sequence has at most
+// one per CTA); segments past the sequence's last one belong to other sequences or lie outside the tensor (zero-filled)
+// and get weight 0.
+constexpr int32_t ST_COMBINE = 1 << 18;  // status bit: the copy of the records did not complete in time
+struct CombineBulk {
+    CUtensorMap tm;
+    CombinePlan c;
+};
+
+// All CB_NT threads call this with the same arguments.  `tile` is 128-byte aligned shared memory of n_ctas x 512 bytes,
+// `bar` an initialised mbarrier (count 1) in its first phase, *abort_flag zero.  Thread 0 issues the copy; meanwhile
+// thread i fetches (m, l) of segment i and the block forms M, the weights and L; after the copy has landed 8 segment
+// lanes x 32 column quads sum from shared memory.  Returns false when the copy did not complete in time (status bit
+// set, nothing may be written); else the threads of warp 0 hold the four merged (unnormalised) columns col0 + 4 lane
+// in `a`, and every thread M and L.
+__device__ __forceinline__ bool combine_item_fetch_tma(const CombinePlan &C, const CUtensorMap *tm, const SegRange &R, int col0,
+                                                       float4 *tile, uint64_t *bar, int *abort_flag, CombineSmem &S, float4 &a,
+                                                       float &M, float &L) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nseg = min(R.nseg, min(C.n_ctas, CB_NT));
+    if (tid == 0 && nseg > 0) {
+        sm100::mbar_arrive_expect_tx(bar, (uint32_t) C.n_ctas * CB_COLS * 4);  // the whole box, zero-filled rows included
+        sm100::tma_load_3d(tile, tm, bar, col0, R.row_in_seg, R.first);
+    }
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (tid < nseg) ml = __ldcg(reinterpret_cast<const float2 *>(combine_ml_ptr(C, R.first + tid, R.row_in_seg)));
+    const float mx = warp_max(ml.x);
+    if (lane == 0) S.red[warp] = mx;
+    __syncthreads();
+    M = S.red[0];
+#pragma unroll
+    for (int w = 1; w < CB_NT / 32; w++) M = fmaxf(M, S.red[w]);
+    const float wgt = ml.x == -INFINITY ? 0.f : expf(ml.x - M);
+    S.m[tid] = wgt;
+    const float ls = warp_sum(ml.y * wgt);
+    if (lane == 0) S.lred[warp] = ls;
+    if (nseg > 0 && !sm100::mbar_wait(bar, 0, abort_flag, const_cast<int32_t *>(C.status), ST_COMBINE)) *abort_flag = 1;
+    __syncthreads();
+    if (*abort_flag) return false;
+    L = 0.f;
+#pragma unroll
+    for (int w = 0; w < CB_NT / 32; w++) L += S.lred[w];
+    a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = warp; s < nseg; s += CB_LANES) {
+        const float w = S.m[s];
+        if (w != 0.f) {  // an empty segment's accumulator never enters the sum
+            const float4 u = tile[s * (CB_COLS / 4) + lane];
+            a.x = fmaf(u.x, w, a.x);
+            a.y = fmaf(u.y, w, a.y);
+            a.z = fmaf(u.z, w, a.z);
+            a.w = fmaf(u.w, w, a.w);
+        }
+    }
+    S.part[warp][lane] = a;
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int j = 1; j < CB_LANES; j++) {
+            const float4 u = S.part[j][lane];
+            a.x += u.x;
+            a.y += u.y;
+            a.z += u.z;
+            a.w += u.w;
+        }
+    }
+    return true;
 }
 
 // Output row of record row `row` = (sequence b, token t, head h of the records).  The records may cover a group of

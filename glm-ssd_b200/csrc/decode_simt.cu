@@ -8,6 +8,8 @@
 // Arithmetic follows the reference kernel's contract (crates/cuda/kernels/ops.cu:420-424):
 //   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
 // with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "combine.cuh"
@@ -241,14 +243,13 @@ __global__ void __launch_bounds__(CB_NT) k_combine(const CombinePlan C) {
     if (prof) prof[2] = sm100::global_timer_ns();
 }
 
-// Combine of records kept as [row][128-column chunk][segment][128] (the tcgen05 kernel's layout): everything an
-// item needs is one contiguous run of nseg x 512 bytes, fetched by a single bulk copy into shared memory while the
-// threads fetch the (m, l) pairs and form the weights; the copy engine keeps the L2 read at full rate with no
-// address arithmetic in the threads.  One item = (output row, 128 columns), at most CB_NT segments.
-constexpr int32_t ST_COMBINE = 1 << 18;  // status bit: the bulk copy of the records did not complete in time
-__global__ void __launch_bounds__(CB_NT) k_combine_bulk(const CombinePlan C) {
-    extern __shared__ __align__(128) unsigned char bulk_raw[];
-    float4 *tile = reinterpret_cast<float4 *>(bulk_raw);  // [nseg][32] column quads
+// Combine of the tcgen05 kernel's records with one tiled TMA copy per item (combine_item_fetch_tma): the copy engine
+// keeps the L2 read at full rate with no address arithmetic in the threads.
+__global__ void __launch_bounds__(CB_NT) k_combine_bulk(const __grid_constant__ CombineBulk CBk) {
+    const CombinePlan &C = CBk.c;
+    extern __shared__ unsigned char bulk_raw[];
+    // [n_ctas][32] column quads, 128-byte aligned for the TMA
+    float4 *tile = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(bulk_raw) + 127) & ~(uintptr_t) 127);
     __shared__ CombineSmem S;
     __shared__ __align__(8) uint64_t bar;
     __shared__ int s_abort;
@@ -269,61 +270,11 @@ __global__ void __launch_bounds__(CB_NT) k_combine_bulk(const CombinePlan C) {
     __syncthreads();
     cudaGridDependencySynchronize();  // the records are written by the preceding kernel
     if (prof) prof[1] = sm100::global_timer_ns();
-    const int nseg = min(R.nseg, CB_NT);
-    if (nseg > 0) {
-        if (C.seg_stride_acc == CB_COLS) {  // the item's segments lie back to back: one copy
-            if (tid == 0) {
-                sm100::mbar_arrive_expect_tx(&bar, (uint32_t) nseg * CB_COLS * 4);
-                sm100::bulk_load(tile, combine_acc_ptr(C, R.first, R.row_in_seg, col0), (uint32_t) nseg * CB_COLS * 4, &bar);
-            }
-        } else if (warp == 0) {  // one 512-byte copy per segment, issued by the lanes of a warp
-            if (lane == 0) sm100::mbar_arrive_expect_tx(&bar, (uint32_t) nseg * CB_COLS * 4);
-            __syncwarp();
-            for (int s = lane; s < nseg; s += 32)
-                sm100::bulk_load(tile + s * (CB_COLS / 4), combine_acc_ptr(C, R.first + s, R.row_in_seg, col0), CB_COLS * 4, &bar);
-        }
-    }
-    float2 ml = make_float2(-INFINITY, 0.f);
-    if (tid < nseg) ml = __ldcg(reinterpret_cast<const float2 *>(combine_ml_ptr(C, R.first + tid, R.row_in_seg)));
-    const float mx = warp_max(ml.x);
-    if (lane == 0) S.red[warp] = mx;
-    __syncthreads();
-    float M = S.red[0];
-#pragma unroll
-    for (int w = 1; w < CB_NT / 32; w++) M = fmaxf(M, S.red[w]);
-    const float wgt = ml.x == -INFINITY ? 0.f : expf(ml.x - M);
-    S.m[tid] = wgt;
-    const float ls = warp_sum(ml.y * wgt);
-    if (lane == 0) S.lred[warp] = ls;
-    if (nseg > 0 && !sm100::mbar_wait(&bar, 0, &s_abort, const_cast<int32_t *>(C.status), ST_COMBINE)) s_abort = 1;
-    __syncthreads();
-    if (s_abort) return;  // the status word says why; nothing is written
-    float L = 0.f;
-#pragma unroll
-    for (int w = 0; w < CB_NT / 32; w++) L += S.lred[w];
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = warp; s < nseg; s += CB_LANES) {
-        const float w = S.m[s];
-        if (w != 0.f) {  // an empty segment's accumulator never enters the sum
-            const float4 u = tile[s * (CB_COLS / 4) + lane];
-            a.x = fmaf(u.x, w, a.x);
-            a.y = fmaf(u.y, w, a.y);
-            a.z = fmaf(u.z, w, a.z);
-            a.w = fmaf(u.w, w, a.w);
-        }
-    }
-    S.part[warp][lane] = a;
-    __syncthreads();
+    float4 a;
+    float M, L;
+    if (!combine_item_fetch_tma(C, &CBk.tm, R, col0, tile, &bar, &s_abort, S, a, M, L)) return;  // the status word says why; nothing is written
     const int col = col0 + lane * 4;
     if (warp == 0 && col < C.d_v) {
-#pragma unroll
-        for (int j = 1; j < CB_LANES; j++) {
-            const float4 u = S.part[j][lane];
-            a.x += u.x;
-            a.y += u.y;
-            a.z += u.z;
-            a.w += u.w;
-        }
         int H_out;
         const int64_t orow = combine_out_row(C, row, H_out);
         if (C.part_out) {
@@ -417,15 +368,21 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // records of the tcgen05 kernel ([row][chunk][segment][128], at most one segment per CTA and sequence): bulk copy
-    const bool bulk = c.bulk && !by_rows && c.desc != nullptr && c.seq_lens != nullptr && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
-                      c.d_v % CB_COLS == 0 && c.seg_stride_acc % 4 == 0 && !(reinterpret_cast<uintptr_t>(c.acc) & 15);
+    // records of the tcgen05 kernel ([segment][row][d_v], at most one segment per CTA and sequence): tiled TMA fetch
+    const bool bulk = c.bulk && !getenv("GS_NO_BULK") && !by_rows && c.desc != nullptr && c.seq_lens != nullptr && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
+                      c.d_v % CB_COLS == 0 && c.n_segments > 0 && c.seg_stride_acc % 4 == 0 && !(reinterpret_cast<uintptr_t>(c.acc) & 15);
     if (bulk) {
-        const int smem = c.n_ctas * CB_COLS * 4;
+        CombineBulk cb;
+        cb.c = c;
+        const int rows_seg = (int) (c.seg_stride_acc / c.d_v);  // query rows per record
+        if (int e = encode_tmap_3d_f32(&cb.tm, c.acc, (uint64_t) c.d_v, (uint64_t) rows_seg, (uint64_t) c.n_segments, (uint64_t) c.d_v * 4,
+                                       (uint64_t) c.seg_stride_acc * 4, CB_COLS, 1, (uint32_t) c.n_ctas))
+            return e;
+        const int smem = c.n_ctas * CB_COLS * 4 + 128;
         // attributes are set on every call: a cached flag would go stale across a device reset
         GS_TRY(cudaFuncSetAttribute(k_combine_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         cfg.dynamicSmemBytes = smem;
-        GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_bulk, c));
+        GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_bulk, cb));
     } else if (by_rows) {
         GS_TRY(cudaLaunchKernelEx(&cfg, k_combine_rows, c));
     } else {

@@ -28,7 +28,6 @@
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status word and leaves
 // through the common exit, which frees tensor memory.
-#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -38,13 +37,13 @@
 
 namespace gs {
 
-int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
-                       uint32_t box_rows, uint32_t box_cols, int swizzle) {
-    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    // The entry point is a host function of the driver library: it stays valid for the life of the process
-    // (also across a device reset), so it is looked up once.  Racing first calls store the same value.
+typedef CUresult (*tmap_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The entry point is a host function of the driver library: it stays valid for the life of the process
+// (also across a device reset), so it is looked up once.  Racing first calls store the same value.
+static int tmap_encoder(tmap_encode_fn *out) {
     static std::atomic<void *> cached{nullptr};
     void *fn = cached.load(std::memory_order_acquire);
     if (!fn) {
@@ -56,16 +55,43 @@ int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64
         }
         cached.store(fn, std::memory_order_release);
     }
+    *out = (tmap_encode_fn) fn;
+    return 0;
+}
+
+int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                       uint32_t box_rows, uint32_t box_cols, int swizzle) {
+    tmap_encode_fn fn;
+    if (int e = tmap_encoder(&fn)) return e;
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {row_stride_bytes};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = ((encode_fn) fn)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides,
-                                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, (CUtensorMapSwizzle) swizzle,
-                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, (CUtensorMapSwizzle) swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows %llu cols %llu box %ux%u)", (int) r,
                   (unsigned long long) rows, (unsigned long long) cols, box_rows, box_cols);
+        return (int) cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
+int encode_tmap_3d_f32(CUtensorMap *out, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                       uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2) {
+    tmap_encode_fn fn;
+    if (int e = tmap_encoder(&fn)) return e;
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    const cuuint32_t box[3] = {b0, b1, b2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (3-D) failed with CUresult %d (dims %llu %llu %llu box %u %u %u)", (int) r,
+                  (unsigned long long) d0, (unsigned long long) d1, (unsigned long long) d2, b0, b1, b2);
         return (int) cudaErrorInvalidValue;
     }
     return 0;
@@ -127,12 +153,7 @@ struct UmmaParams {
     int whole_seq;                 // list form: every sequence is attended by one CTA, which normalises and stores o itself
     float *o;                      // whole_seq: output f32 [tokens][H_out][d_v]
     int H_out;
-    int seg_cap;                   // segments the record arrays are laid out for: acc [row][4 chunks][seg_cap][128], ml [row][seg_cap][2]
-    // record addressing: column c of query row q of segment s at ws_acc + s*acc_seg + q*acc_row + (c/128)*acc_chunk + c%128,
-    // its (m, l) pair at ws_ml + s*ml_seg + q*ml_row
-    // (element strides; the record arrays hold fewer than 2^31 floats, so offsets are formed in 32 bits)
-    int acc_seg, acc_row, acc_chunk, ml_seg, ml_row;
-    int tune;                      // tuning switches of the record path, see launch_decode_umma
+    int seg_cap;                   // segments the record arrays hold
     int seq_div;                   // >= 1: kernel sequence b reads the length / base / pages of caller sequence b / seq_div
                                    // (T = 1 only: the head groups of a sequence as sequences of their own)
     int64_t cache_rows;
@@ -903,52 +924,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             if (wg_tid < P.rows_q) {
                 const int q = wg_tid;
                 const float m = M.mref[q];
-                float *ml = P.ws_ml + (sg.seg_id * P.ml_seg + q * P.ml_row);
+                float *ml = P.ws_ml + ((int64_t) sg.seg_id * P.rows_q + q) * 2;
                 ml[0] = m == -INFINITY ? -INFINITY : m * LN2;
                 ml[1] = (M.sl[0][q] + M.sl[1][q]) + (M.sl[2][q] + M.sl[3][q]);
             }
-            // records are kept as [query row][128-column chunk][segment][128]: what one (row, chunk) item of the combine
-            // kernel reads is then one contiguous run
-            float *acc = P.ws_acc + (sg.seg_id * P.acc_seg + qt * 32 + lane);
-            const int acc_row = P.acc_row, acc_chunk = P.acc_chunk;
+            // one record per segment, [query row][d_v] f32: a CTA's stores stay inside one contiguous block
+            float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
             // one value tile (NQ columns of this lane's row) per step; the loads of the next tile are in flight
             // while the current one is stored
             uint32_t rbuf[2][NQ];
 #pragma unroll
             for (int c = 0; c < NQ / 16; c++) tmem_ld16(tmem + lane_base + O_SLOT0 * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
-            if (pos >= end && (P.tune & 1)) {
-                // The CTA's last segment: nothing will be loaded any more and every MMA that read the ring has
-                // completed, so the ring's first stage serves as a staging area [2][NQ][128] f32.  A thread holds one
-                // value column of all query rows; through the staging area a warp stores whole 512-byte pieces
-                // (one query row, 128 columns) with 16 bytes per lane - a quarter of the store instructions.
-                float *stg = reinterpret_cast<float *>(kv_smem);
-                // every CTA starts at another query row, so that at any moment the CTAs write to different parts of the arrays
-                const int rot = (int) (blockIdx.x % (NQ / 4));
-                float *piece0 = P.ws_acc + (sg.seg_id * P.acc_seg + lane * 4);
-#pragma unroll
-                for (int mt = 0; mt < NVT; mt++) {
-                    tmem_wait_ld();
-                    if (mt + 1 < NVT) {
-#pragma unroll
-                        for (int c = 0; c < NQ / 16; c++)
-                            tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
-                                      *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
-                    }
-                    float *buf = stg + (mt & 1) * (NQ * 128);
-#pragma unroll
-                    for (int q = 0; q < NQ; q++)
-                        if (q < P.rows_q) buf[q * 128 + qt * 32 + lane] = __uint_as_float(rbuf[mt & 1][q]);
-                    named_bar_sync(1, 128);  // one barrier per value tile: the other buffer was last read before the previous one
-#pragma unroll
-                    for (int i = 0; i < NQ / 4; i++) {
-                        int ii = i + rot;
-                        if (ii >= NQ / 4) ii -= NQ / 4;
-                        const int q = qt + 4 * ii;
-                        if (q < P.rows_q)
-                            st_global_hint_v4(piece0 + (q * acc_row + mt * acc_chunk), *reinterpret_cast<const float4 *>(buf + q * 128 + lane * 4), pol_keep);
-                    }
-                }
-            } else {
+            {
 #pragma unroll
                 for (int mt = 0; mt < NVT; mt++) {
                     tmem_wait_ld();
@@ -960,7 +947,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     }
 #pragma unroll
                     for (int q = 0; q < NQ; q++)
-                        if (q < P.rows_q) st_global_hint(acc + (q * acc_row + mt * acc_chunk), __uint_as_float(rbuf[mt & 1][q]), pol_keep);
+                        if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(rbuf[mt & 1][q]), pol_keep);
                 }
             }
             tc_fence_before();
@@ -1029,7 +1016,7 @@ static int list_head_groups(int H) {
 // kernel), or a cudaError_t.  Every (token, head group) is a kernel sequence over the token's list.  With one split, or
 // when the caller's `part` cannot hold enough records, every sequence is attended by one CTA that stores o itself;
 // otherwise the rows are dealt to CTAs as in the dense form and the records live in `part`
-// (T*H*splits*(R+2) floats, crates/cuda/kernels/ops.cu:578), as [row][chunk][segment][128], then [row][segment][2], then
+// (T*H*splits*(R+2) floats, crates/cuda/kernels/ops.cu:578): accumulators [segment][row][R], then (m, l) [segment][row][2], then
 // the per-sequence descriptors.
 int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
                             float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st) {
@@ -1088,21 +1075,14 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
     if (!whole) {
         P.seg_cap = grid + (int) n_seq_k;
         P.ws_acc = part;
-        P.ws_ml = part + (int64_t) Hg * NVT * P.seg_cap * 128;
+        P.ws_ml = part + (int64_t) Hg * P.seg_cap * R;
         P.ws_desc = reinterpret_cast<int2 *>(P.ws_ml + (int64_t) Hg * P.seg_cap * 2);
-        P.acc_seg = 128;
-        P.acc_chunk = P.seg_cap * 128;
-        P.acc_row = NVT * P.seg_cap * 128;
-        P.ml_seg = 2;
-        P.ml_row = P.seg_cap * 2;
         c.acc = P.ws_acc;
         c.ml = P.ws_ml;
         c.desc = P.ws_desc;
-        c.seg_stride_acc = P.acc_seg;
-        c.row_stride_acc = P.acc_row;
-        c.chunk_stride_acc = P.acc_chunk;
-        c.seg_stride_ml = P.ml_seg;
-        c.row_stride_ml = P.ml_row;
+        c.seg_stride_acc = (int64_t) Hg * R;
+        c.seg_stride_ml = (int64_t) Hg * 2;
+        c.n_segments = P.seg_cap;
         c.n_seq = (int) n_seq_k;
         c.T = 1;
         c.H = Hg;
@@ -1116,7 +1096,6 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
         c.n_ctas = grid;
         c.len_cap = sel_stride;
         c.bulk = true;
-        P.tune = 1;  // staged record stores
     }
     int e;
     if (Hg <= 32) e = launch_cfg<32, 8, true>(P, grid, st);
@@ -1196,11 +1175,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
     if (((int64_t) grid + n_seq_k) * p.T * (seq_div > 1 || n_groups > 1 ? Hg : p.H) > p.max_record_rows)
         return fail_invalid("decode: workspace too small for the segment records");
     P.seg_cap = grid + n_seq_k;
-    // tuning switches (environment, read per call): bit 0 = staged 16-byte record stores on a CTA's last segment,
-    // bit 1 = records as [row][chunk][segment][128] instead of [segment][row][d_v], bit 2 = bulk-copy combine
-    P.tune = 7;
-    if (const char *e = getenv("GS_TUNE")) P.tune = atoi(e);
-    const bool seg_major = (P.tune & 2) == 0;
+
     for (int g = 0; g < n_groups; g++) {
         const int h0 = g * Hg;
         const int hg = p.H - h0 < Hg ? p.H - h0 : Hg;
@@ -1218,24 +1193,9 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.ml = p.ws_ml;
         c.desc = p.ws_desc;
         c.regular_segments = 0;
-        if (seg_major) {
-            c.seg_stride_acc = (int64_t) rows_q * p.d_v;
-            c.row_stride_acc = p.d_v;
-            c.chunk_stride_acc = 128;
-            c.seg_stride_ml = (int64_t) rows_q * 2;
-            c.row_stride_ml = 2;
-        } else {
-            c.seg_stride_acc = 128;  // [row][chunk][segment][128]
-            c.chunk_stride_acc = (int64_t) P.seg_cap * 128;
-            c.row_stride_acc = (int64_t) NVT * P.seg_cap * 128;
-            c.seg_stride_ml = 2;     // [row][segment][2]
-            c.row_stride_ml = (int64_t) P.seg_cap * 2;
-        }
-        P.acc_seg = (int) c.seg_stride_acc;
-        P.acc_row = (int) c.row_stride_acc;
-        P.acc_chunk = (int) c.chunk_stride_acc;
-        P.ml_seg = (int) c.seg_stride_ml;
-        P.ml_row = (int) c.row_stride_ml;
+        c.seg_stride_acc = (int64_t) rows_q * p.d_v;  // records as [segment][row][d_v], (m, l) as [segment][row][2]
+        c.seg_stride_ml = (int64_t) rows_q * 2;
+        c.n_segments = P.seg_cap;
         c.n_seq = n_seq_k;
         c.T = p.T;
         c.H = hg;
@@ -1250,7 +1210,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.unit_rows = P.paged ? TILE : 16;
         c.n_ctas = grid;
         c.len_cap = P.paged ? (int64_t) P.page_table_stride * TILE : P.cache_rows;
-        c.bulk = (P.tune & 4) != 0;
+        c.bulk = true;
         int e;
         if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
         else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);

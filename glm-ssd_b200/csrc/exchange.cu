@@ -80,13 +80,34 @@ __device__ __forceinline__ void exchange_block_done(const ExchangeParams &X) {
     }
 }
 
-__global__ void __launch_bounds__(CB_NT) k_exchange_combine(const CombinePlan C, const ExchangeParams X) {
+struct ExchangeLaunch {
+    CUtensorMap tm;  // records as the 3-D tensor {d_v, rows, segments}; used when `tma` is set
+    CombinePlan c;
+    ExchangeParams x;
+    int tma;
+};
+
+__global__ void __launch_bounds__(CB_NT) k_exchange_combine(const __grid_constant__ ExchangeLaunch EL) {
+    const CombinePlan &C = EL.c;
+    const ExchangeParams &X = EL.x;
+    extern __shared__ unsigned char xraw[];
+    float4 *tile = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(xraw) + 127) & ~(uintptr_t) 127);
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_fetch_abort;
     __shared__ CombineSmem S;
     __shared__ float s_m[kMaxWorld], s_l[kMaxWorld], s_w[kMaxWorld];
     __shared__ int s_abort;
     const int row = blockIdx.x, chunk = blockIdx.y;
     const int tid = threadIdx.x;
-    if (tid == 0) s_abort = 0;
+    if (tid == 0) {
+        s_abort = 0;
+        s_fetch_abort = 0;
+        if (EL.tma) {
+            sm100::mbar_init(&bar, 1);
+            sm100::fence_barrier_init();
+        }
+    }
+    __syncthreads();
 #if __CUDA_ARCH__ >= 900
     cudaGridDependencySynchronize();  // the split partials are written by the preceding kernel
 #endif
@@ -101,7 +122,19 @@ __global__ void __launch_bounds__(CB_NT) k_exchange_combine(const CombinePlan C,
         float M, L;
         int col;
         const SegRange R = combine_locate(C, row, S);
-        if (combine_item_compute(C, R, chunk * CB_COLS, S, a, M, L, col)) {
+        bool holds;
+        if (EL.tma) {  // the item's pieces of all local segments by one tiled TMA copy
+            if (!combine_item_fetch_tma(C, &EL.tm, R, chunk * CB_COLS, tile, &bar, &s_fetch_abort, S, a, M, L)) {
+                exchange_block_done(X);
+                return;  // status bit 18 says why; nothing is sent, the other ranks' waits run out
+            }
+            col = chunk * CB_COLS + (tid & 31) * 4;
+            holds = tid < 32 && col < C.d_v;
+            __syncthreads();  // shared memory is reused below
+        } else {
+            holds = combine_item_compute(C, R, chunk * CB_COLS, S, a, M, L, col);
+        }
+        if (holds) {
             for (int r = 0; r < X.world; r++) {
                 uint2 *dst = reinterpret_cast<uint2 *>(X.bufs[r]) + slot + (int64_t) X.rank * X.block_words;
                 uint2 *w = dst + (int64_t) row * X.d_v + col;
@@ -206,12 +239,9 @@ int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o,
         set_error("exchange: buffers of %lld bytes needed, %lld given", (long long) L.total, (long long) x.buf_bytes);
         return (int) cudaErrorInvalidValue;
     }
-    // blocks of one rank wait for blocks of the others: every block of the grid must be resident
-    int per_sm = 0;
-    GS_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_exchange_combine, CB_NT, 0));
-    if (L.items > per_sm * sm_count)
-        return fail_invalid("exchange: more (row, chunk) items than blocks the GPU can hold at once; use the all-gather path");
-    ExchangeParams X{};
+    ExchangeLaunch EL;
+    memset(&EL, 0, sizeof(EL));
+    ExchangeParams &X = EL.x;
     for (int r = 0; r < x.world; r++) {
         if (!x.peer_bufs[r]) return fail_invalid("exchange: null peer buffer");
         X.bufs[r] = (unsigned char *) x.peer_bufs[r];
@@ -228,16 +258,39 @@ int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o,
     X.wait_limit = x.wait_limit_cycles > 0 ? x.wait_limit_cycles : sm100::kWaitLimitCycles;
     X.o = o;
     X.status = status;
+    EL.c = c;
+    // records of the tcgen05 kernel: fetched like the plain combine does, one tiled TMA copy per item
+    EL.tma = c.bulk && c.desc != nullptr && c.seq_lens != nullptr && c.n_seq < 16 && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
+             c.d_v % CB_COLS == 0 && c.n_segments > 0 && c.seg_stride_acc % c.d_v == 0 && !(reinterpret_cast<uintptr_t>(c.acc) & 15);
+    int smem = 0;
+    if (EL.tma) {
+        if (int e = encode_tmap_3d_f32(&EL.tm, c.acc, (uint64_t) c.d_v, (uint64_t) (c.seg_stride_acc / c.d_v), (uint64_t) c.n_segments,
+                                       (uint64_t) c.d_v * 4, (uint64_t) c.seg_stride_acc * 4, CB_COLS, 1, (uint32_t) c.n_ctas))
+            return e;
+        smem = c.n_ctas * CB_COLS * 4 + 128;
+        GS_TRY(cudaFuncSetAttribute(k_exchange_combine, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    }
+    // blocks of one rank wait for blocks of the others: every block of the grid must be resident
+    int per_sm = 0;
+    GS_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_exchange_combine, CB_NT, smem));
+    if (L.items > per_sm * sm_count && EL.tma) {  // the staging area of the tiled copy costs residency: plain loads instead
+        EL.tma = 0;
+        smem = 0;
+        GS_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_exchange_combine, CB_NT, 0));
+    }
+    if (L.items > per_sm * sm_count)
+        return fail_invalid("exchange: more (row, chunk) items than blocks the GPU can hold at once; use the all-gather path");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows, (c.d_v + CB_COLS - 1) / CB_COLS);
     cfg.blockDim = dim3(CB_NT);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GS_TRY(cudaLaunchKernelEx(&cfg, k_exchange_combine, c, X));
+    GS_TRY(cudaLaunchKernelEx(&cfg, k_exchange_combine, EL));
     return 0;
 }
 

@@ -51,7 +51,8 @@ struct CombinePlan {
     // ml + s*seg_stride_ml + r*row_stride_ml.  The tcgen05 kernel keeps its records as [row][128-column chunk][segment][128],
     // so that everything one (row, chunk) item of the combine needs is one contiguous run of memory.
     int64_t row_stride_acc, chunk_stride_acc, row_stride_ml;
-    bool bulk;             // fetch an item's accumulators with bulk copies into shared memory (k_combine_bulk)
+    bool bulk;             // fetch an item's accumulators with one tiled TMA copy into shared memory (k_combine_bulk)
+    int n_segments;        // bulk: segments the record arrays hold (extent of the tensor map)
     int n_seq, T, H, d_v;  // H: heads in the records being merged
     int H_out, h0;         // the output has H_out heads per token and these are heads h0 .. h0+H-1 (0, 0: H_out = H)
     float *o;              // may be nullptr

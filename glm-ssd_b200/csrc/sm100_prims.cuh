@@ -136,6 +136,13 @@ __device__ __forceinline__ void tma_gather4_hint(void *smem_dst, const CUtensorM
         "l"(policy)
         : "memory");
 }
+// 3-D tiled load global -> this CTA's shared memory (no multicast), completion counted in bytes on `bar`.
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
 // L2 eviction policies: data streamed once (the latent cache) should leave L2 first, data another kernel
 // reads next (the partial records) last.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
@@ -276,5 +283,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
 // swizzle (CU_TENSOR_MAP_SWIZZLE_*).  Returns 0 or a cudaError_t value.
 int encode_tmap_2d_f16(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
                        uint32_t box_rows, uint32_t box_cols, int swizzle);
+// Encodes a 3-D f32 tensor [d2][d1][d0] (d0 contiguous; stride1 / stride2 in bytes) with a box of [b2][b1][b0], no swizzle.
+int encode_tmap_3d_f32(CUtensorMap *out, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                       uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
 
 }  // namespace gs

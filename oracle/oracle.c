@@ -678,7 +678,7 @@ void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T
         const int n_pool = (pos + 1) / kpool;
         int32_t *out = sel + (int64_t) t * sel_stride;
         if (n_pool <= top_k) {
-            for (int i = 0; i <= pos; i++) out[i] = i;
+            for (int i = 0; i <= pos && i < sel_stride; i++) out[i] = i;
             cnt[t] = pos + 1;
             continue;
         }
@@ -688,7 +688,7 @@ void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T
         uint32_t *sorted = (uint32_t *) malloc(sizeof(uint32_t) * (size_t) n_pool);
         memcpy(sorted, ord, sizeof(uint32_t) * (size_t) n_pool);
         qsort(sorted, (size_t) n_pool, sizeof(uint32_t), cmp_u32_desc);
-        const uint32_t U = sorted[top_k - 1]; /* the k-th largest value */
+        const uint32_t U = top_k > 0 ? sorted[top_k - 1] : 0xffffffffu; /* the k-th largest value; nothing is taken when top_k is 0 */
         int above = 0;
         for (int p = 0; p < n_pool; p++) above += ord[p] > U;
         int need_eq = top_k - above, slot = 0;
@@ -698,13 +698,15 @@ void oracle_idx_select(const float *score, int64_t score_stride, int pos0, int T
                 take = 1;
                 need_eq--;
             }
-            if (take) {
-                for (int m = 0; m < kpool; m++) out[slot * kpool + m] = p * kpool + m;
+            if (take && slot < top_k) { /* never more than top_k pools, whatever the scores hold */
+                for (int m = 0; m < kpool; m++)
+                    if ((int64_t) slot * kpool + m < sel_stride) out[slot * kpool + m] = p * kpool + m;
                 slot++;
             }
         }
         const int base = top_k * kpool, tail0 = n_pool * kpool;
-        for (int i = 0; tail0 + i <= pos; i++) out[base + i] = tail0 + i;
+        for (int i = 0; tail0 + i <= pos; i++)
+            if (base + i < sel_stride) out[base + i] = tail0 + i;
         cnt[t] = base + (pos + 1 - tail0);
         free(sorted);
         free(ord);

@@ -52,7 +52,10 @@ def test_protocol_with_ranks_played_in_turn(pkg, cuda, oracle, T):
         return pkg.decode_status(ws[r])
 
     want = oracle.mla_decode(q, cache, [n], 1 / 16)
-    for epoch in (1, 2):  # the second call meets the first call's records and flags
+    # consecutive epochs (the record slots alternate with the epoch's parity); every epoch begins with a wait that runs
+    # out on rank 1, after which both ranks complete that epoch and carry on with the next one: resynchronising after
+    # a timed-out step needs nothing but the next consecutive epoch
+    for epoch in (1, 2, 3):
         for w in ws:
             w[:8].zero_()
         assert run(1, epoch, 2_000_000) & ST_EXCHANGE      # nothing has set rank 0's flags yet
