@@ -155,7 +155,7 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
     DecodeProblem p{};
     if (int e = device_sm_count(&p.sm_count)) return e;
-    // f16 cache: the tcgen05 kernel reads the listed rows four at a time with gather copies and rounds the queries to
+    // f16 cache: the tcgen05 kernel's producer warp fetches the listed rows itself and the kernel rounds the queries to
     // f16 itself; it needs nothing beyond the reference's own arguments.  Q8 caches and shapes it does not take run on
     // the CUDA-core kernel below.
     const int impl = g_attn_impl.load(std::memory_order_relaxed);

@@ -8,8 +8,6 @@
 // Arithmetic follows the reference kernel's contract (crates/cuda/kernels/ops.cu:420-424):
 //   score = scale * q . K[row]; online softmax over the attended rows; o = sum p V[row] / sum p,
 // with split-KV partials (unnormalised acc, m, l) merged as in ops.cu:552-574.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "combine.cuh"
@@ -369,7 +367,7 @@ int launch_combine(const CombinePlan &c, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // records of the tcgen05 kernel ([segment][row][d_v], at most one segment per CTA and sequence): tiled TMA fetch
-    const bool bulk = c.bulk && !getenv("GS_NO_BULK") && !by_rows && c.desc != nullptr && c.seq_lens != nullptr && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
+    const bool bulk = c.bulk && !by_rows && c.desc != nullptr && c.seq_lens != nullptr && c.n_ctas > 0 && c.n_ctas <= CB_NT &&
                       c.d_v % CB_COLS == 0 && c.n_segments > 0 && c.seg_stride_acc % 4 == 0 && !(reinterpret_cast<uintptr_t>(c.acc) & 15);
     if (bulk) {
         CombineBulk cb;

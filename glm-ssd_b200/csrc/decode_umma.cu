@@ -145,8 +145,8 @@ struct UmmaParams {
     int n_seq, T, H, rows_q, d_v;  // H: heads handled by this launch (a group of the H_full heads of q)
     int H_full, h0;                // q holds H_full heads per token; this launch takes heads h0 .. h0+H-1
     // position-list form (the reference's sel / cnt): kernel sequence b attends rows sel[(b / seq_div) * sel_stride + i],
-    // i < seq_lens[b / seq_div]; the rows are fetched four at a time with gather copies through tm_kv1
-    CUtensorMap tm_kv1;
+    // i < seq_lens[b / seq_div]; the rows are fetched by the producer warp with 16-byte asynchronous copies
+    const void *list_cache;        // the cache as a plain pointer (rows of d_qk f16)
     const int32_t *sel;
     int sel_stride;
     const float *q_f32;            // list form: f32 queries [tokens][H_full][d_qk], rounded to f16 inside the kernel
@@ -324,9 +324,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tma_prefetch_desc(&P.tm_kv64);
         tma_prefetch_desc(&P.tm_kv16);
         tma_prefetch_desc(&P.tm_q);
-        if (LIST) tma_prefetch_desc(&P.tm_kv1);
         for (int s = 0; s < STAGES; s++) {
-            for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], 1);
+            for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], LIST ? 32 : 1);  // list form: one arrival per producer lane
             mbar_init(&B.kv_empty[s], N_MMA_WARPS);
         }
         for (int s = 0; s < 2; s++) {
@@ -488,27 +487,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
                 if (LIST) {
-                    // Rows named by the position list: lane l fetches the four indices of row quad l % 16 once and issues the
-                    // gather copies of that quad for the column blocks l / 16, l / 16 + 2, ...  An index past the list's end
-                    // repeats the quad's first row (the copy always moves four rows); those rows are masked in the scores.
-                    const int nq4 = (valid + 3) >> 2;
-                    if (elect_one()) {
+                    // Rows named by the position list.  Lane l holds the cache rows of tile rows l and l + 32; every warp
+                    // instruction copies 512 contiguous bytes of one listed row (16 bytes per lane) to the place the tiled
+                    // copy of the dense form would have put them: 64-column block c / 8, 16-byte chunk (c % 8) xor (r % 8)
+                    // of row r.  Each lane's arrival on the stage's barrier follows its own copies.
+                    const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row;
+                    const int ra = lane < valid ? max(lp[lane], 0) : 0, rb = lane + 32 < valid ? max(lp[lane + 32], 0) : 0;
+                    constexpr int CPR = NBLK * 8;  // 16-byte chunks per row
+                    const char *cbase = reinterpret_cast<const char *>(P.list_cache);
+#pragma unroll 4
+                    for (int r = 0; r < valid; r++) {
+                        const int grow = __shfl_sync(0xffffffffu, r < 32 ? ra : rb, r & 31);
+                        const char *src = cbase + (int64_t) grow * (NBLK * 128);
+                        uint8_t *drow = dst + r * 128;
 #pragma unroll
-                        for (int g = 0; g < NGRP; g++) {
-                            const int k_lo = g * GRP, k_hi = min(NBLK, g * GRP + GRP);
-                            mbar_arrive_expect_tx(&B.kv_full[s][g], (uint32_t) (nq4 * (k_hi - k_lo) * 512));
+                        for (int c0 = 0; c0 < CPR; c0 += 32) {
+                            const int c = c0 + lane;
+                            if (c < CPR) cp_async16_hint(drow + (c >> 3) * BLK_BYTES + (((c & 7) ^ (r & 7)) << 4), src + c * 16, pol_stream);
                         }
                     }
-                    __syncwarp();
-                    const int quad = lane & 15;
-                    if (quad < nq4) {
-                        const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row + quad * 4;
-                        const int left = valid - quad * 4;  // >= 1
-                        const int r0 = lp[0];
-                        const int r1 = left > 1 ? lp[1] : r0, r2 = left > 2 ? lp[2] : r0, r3 = left > 3 ? lp[3] : r0;
-                        for (int k = lane >> 4; k < NBLK; k += 2)
-                            tma_gather4_hint(dst + k * BLK_BYTES + quad * 512, &P.tm_kv1, &B.kv_full[s][k / GRP], k * 64, r0, r1, r2, r3, pol_stream);
-                    }
+                    cp_async_mbar_arrive(&B.kv_full[s][0]);
                     __syncwarp();
                 } else if (P.paged || valid == TILE) {
                     const int grow = P.paged ? P.page_table[(int64_t) (sg.b / P.seq_div) * P.page_table_stride +
@@ -593,6 +591,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int s = i & 1;
                 const uint32_t kv_lo = kv_lo0 + s * (STAGE_BYTES >> 4);
                 tc_fence_after();
+                if (LIST) fence_proxy_async_smem();  // the stage was filled by ordinary asynchronous copies, not by the TMA
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < K_PER; k++) {
@@ -644,6 +643,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 if (!ok) break;
                 if (mw == 0 && lane == 0) GS_STAMP(it, PF_P_FULL_SEEN);
                 tc_fence_after();
+                if (LIST) fence_proxy_async_smem();
                 const int valid = min(TILE, sg.r1 - (sg.r0 + j * TILE));
                 const int nk = (valid + 15) >> 4;
                 const uint32_t p_lo = p_lo0 + s * (SM::P_BYTES >> 4);
@@ -1028,13 +1028,14 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
     const int Hg = H / n_groups;
     UmmaParams P;
     memset(&P, 0, sizeof(P));
-    // The entry point is not told how many rows the cache holds; the map spans the whole index range of a row
-    // coordinate, and the lists are trusted as the reference trusts them.
-    if (encode_tmap_2d_f16(&P.tm_kv1, C, (uint64_t) 0x7fffffff, (uint64_t) R, (uint64_t) R * 2, 1, 64, (int) CU_TENSOR_MAP_SWIZZLE_128B))
+    // The entry point is not told how many rows the cache holds: the lists are trusted as the reference trusts them
+    // (a negative index is read as 0).  The tensor maps are unused in this form; one valid map keeps the descriptor
+    // prefetches of the set-up harmless.
+    if (encode_tmap_2d_f16(&P.tm_kv64, C, (uint64_t) 64, (uint64_t) R, (uint64_t) R * 2, 16, 64, (int) CU_TENSOR_MAP_SWIZZLE_128B))
         return -1;
-    P.tm_kv64 = P.tm_kv1;  // unused in this form; kept valid for the descriptor prefetches
-    P.tm_kv16 = P.tm_kv1;
-    P.tm_q = P.tm_kv1;
+    P.tm_kv16 = P.tm_kv64;
+    P.tm_q = P.tm_kv64;
+    P.list_cache = C;
     P.seq_lens = cnt;
     P.sel = sel;
     P.sel_stride = sel_stride;

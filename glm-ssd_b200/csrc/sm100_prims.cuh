@@ -125,18 +125,15 @@ __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint
                  ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-// Four rows of a 2-D tensor, named one by one, into four consecutive rows of shared memory (the tensor map's box is
-// one row high; no multicast).  c0 is the column offset, r0..r3 the row indices.
-__device__ __forceinline__ void tma_gather4_hint(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int32_t c0, int32_t r0, int32_t r1,
-                                                 int32_t r2, int32_t r3, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
-        "l"(policy)
-        : "memory");
+// 16 bytes global -> shared by the asynchronous copy unit (bypassing L1), and the arrival that lets an mbarrier track
+// all copies the executing thread has issued so far (the arrival counts against the barrier's expected count).
+__device__ __forceinline__ void cp_async16_hint(void *smem_dst, const void *gsrc, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "l"(policy) : "memory");
 }
-// 3-D tiled load global -> this CTA's shared memory (no multicast), completion counted in bytes on `bar`.
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 3-D tiled load global -> this CTA's shared memory, completion counted in bytes on `bar`.
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int32_t c0, int32_t c1, int32_t c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -169,10 +166,6 @@ __device__ __forceinline__ int ld_global_hint(const int *p, uint64_t policy) {
 }
 __device__ __forceinline__ void st_global_hint(float *p, float v, uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void st_global_hint_v4(float *p, float4 v, uint64_t policy) {
-    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(policy)
-                 : "memory");
 }
 // Ask for one box of a tiled tensor to be brought into L2 (no destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *m, int32_t c0, int32_t c1) {

@@ -42,8 +42,8 @@ int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *
                 float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
 
 /* Which kernel gs_mla_attn runs (no counterpart in the reference).  With an f16 cache (C_scales == NULL) the call
- * runs on the tcgen05 decode kernel whenever that kernel takes the shape: the rows a list names are fetched four at a
- * time by gather copies straight from the cache, the f32 queries are rounded to f16 inside the kernel (the precision
+ * runs on the tcgen05 decode kernel whenever that kernel takes the shape: the rows a list names are fetched straight
+ * from the cache by the kernel's producer warp, the f32 queries are rounded to f16 inside the kernel (the precision
  * of the f16-query entry points; outputs stay within max-abs 2e-3 of the f32-query result), and nothing beyond the
  * reference's own arguments is needed: with splits > 1 the split records live in `part` (as many segments as fit its
  * T*H*splits*(R+2) floats), with splits == 1 every (token, head group) is attended by one CTA that stores o itself.

@@ -277,25 +277,29 @@ int oracle_mla_attn_ref(const float *q, const uint16_t *C, const int32_t *sel, i
  * ------------------------------------------------------------------------------------------ */
 void oracle_combine(const float *part, int64_t n_rows, int n_parts, int d_v, float *o) {
     const int64_t rec = d_v + 2;
+    float *w = (float *) malloc(sizeof(float) * (size_t) (n_parts > 0 ? n_parts : 1));
     for (int64_t r = 0; r < n_rows; r++) {
         const float *base = part + r * n_parts * rec;
         float M = -INFINITY;
         for (int s = 0; s < n_parts; s++) M = fmaxf(M, base[s * rec + d_v]);
         float L = 0.f;
-        for (int s = 0; s < n_parts; s++) {
+        for (int s = 0; s < n_parts; s++) { /* the weight of a part, once per part; an empty part (m = -inf) has none */
             const float m = base[s * rec + d_v];
-            if (m != -INFINITY) L += base[s * rec + d_v + 1] * expf(m - M);
+            w[s] = m != -INFINITY ? expf(m - M) : 0.f;
+            if (m != -INFINITY) L += base[s * rec + d_v + 1] * w[s];
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
-        for (int c = 0; c < d_v; c++) {
-            float a = 0.f;
-            for (int s = 0; s < n_parts; s++) {
-                const float m = base[s * rec + d_v];
-                if (m != -INFINITY) a += base[s * rec + c] * expf(m - M);
-            }
-            o[r * d_v + c] = a * inv;
+        float *out = o + r * d_v;
+        for (int c = 0; c < d_v; c++) out[c] = 0.f;
+        for (int s = 0; s < n_parts; s++) {
+            if (base[s * rec + d_v] == -INFINITY) continue;
+            const float ws = w[s];
+            const float *a = base + s * rec;
+            for (int c = 0; c < d_v; c++) out[c] += a[c] * ws;
         }
+        for (int c = 0; c < d_v; c++) out[c] *= inv;
     }
+    free(w);
 }
 
 /* ------------------------------------------------------------------------------------------
@@ -383,9 +387,10 @@ int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const in
 }
 
 /* The same decode with the attended rows of every (sequence, token, head) cut into `key_splits` ranges by the
- * reference's split rule (per = ceil(n / splits), ops.cu:447-449), one work item per range, merged by
- * oracle_combine (ops.cu:558-573): the form that keeps every host core busy when n_seq*T*H is small.
- * `scratch` holds n_seq*T*H*key_splits*(d_v+2) floats. */
+ * reference's split rule (per = ceil(n / splits), ops.cu:447-449) and merged by oracle_combine (ops.cu:558-573).
+ * One work item is (sequence, key range) and walks all T*H query rows over that range, so the range's cache rows are
+ * read from memory once and serve every head from the core's cache - the order a CPU wants, and the form that keeps
+ * every host core busy when n_seq*T*H is small.  `scratch` holds n_seq*T*H*key_splits*(d_v+2) floats. */
 typedef struct {
     dec_ctx_t d;
     int key_splits;
@@ -396,35 +401,38 @@ static void dec_split_item(void *vctx, int64_t item) {
     dec_split_ctx_t *sc = (dec_split_ctx_t *) vctx;
     const dec_ctx_t *c = &sc->d;
     const int ks = sc->key_splits;
-    const int64_t row_item = item / ks;
+    const int b = (int) (item / ks);
     const int split = (int) (item % ks);
-    const int h = (int) (row_item % c->H);
-    const int t = (int) ((row_item / c->H) % c->T);
-    const int b = (int) (row_item / ((int64_t) c->H * c->T));
-    int64_t n = (int64_t) c->seq_lens[b] - (c->T - 1 - t);
-    if (n < 0) n = 0;
-    const int64_t per = (n + ks - 1) / ks;
-    const int64_t lo = split * per < n ? split * per : n;
-    const int64_t hi = lo + per < n ? lo + per : n;
-    const int64_t cnt = hi - lo;
+    const int64_t len = c->seq_lens[b] > 0 ? c->seq_lens[b] : 0;
+    const int64_t per_max = (len + ks - 1) / ks;
     float *qf = (float *) malloc(sizeof(float) * (size_t) c->d_qk);
-    oracle_f16_to_f32_array(c->q + (((int64_t) b * c->T + t) * c->H + h) * c->d_qk, qf, c->d_qk);
-    float *buf = (float *) malloc(sizeof(float) * (size_t) (cnt > 0 ? cnt : 1));
-    int32_t *rows = NULL;
-    int64_t row0 = 0;
-    if (c->page_table) {
-        rows = (int32_t *) malloc(sizeof(int32_t) * (size_t) (cnt > 0 ? cnt : 1));
-        const int32_t *pt = c->page_table + (int64_t) b * c->page_table_stride;
-        for (int64_t i = 0; i < cnt; i++) {
-            const int64_t pos = lo + i;
-            rows[i] = pt[pos / c->page_rows] * c->page_rows + (int32_t) (pos % c->page_rows);
+    float *buf = (float *) malloc(sizeof(float) * (size_t) (per_max > 0 ? per_max : 1));
+    int32_t *rows = c->page_table ? (int32_t *) malloc(sizeof(int32_t) * (size_t) (per_max > 0 ? per_max : 1)) : NULL;
+    for (int t = 0; t < c->T; t++) {
+        int64_t n = len - (c->T - 1 - t);
+        if (n < 0) n = 0;
+        const int64_t per = (n + ks - 1) / ks;
+        const int64_t lo = split * per < n ? split * per : n;
+        const int64_t hi = lo + per < n ? lo + per : n;
+        const int64_t cnt = hi - lo;
+        int64_t row0 = 0;
+        if (c->page_table) {
+            const int32_t *pt = c->page_table + (int64_t) b * c->page_table_stride;
+            for (int64_t i = 0; i < cnt; i++) {
+                const int64_t pos = lo + i;
+                rows[i] = pt[pos / c->page_rows] * c->page_rows + (int32_t) (pos % c->page_rows);
+            }
+        } else {
+            row0 = (c->seq_base ? (int64_t) c->seq_base[b] : 0) + lo;
         }
-    } else {
-        row0 = (c->seq_base ? (int64_t) c->seq_base[b] : 0) + lo;
+        for (int h = 0; h < c->H; h++) {
+            const int64_t row_item = ((int64_t) b * c->T + t) * c->H + h;
+            oracle_f16_to_f32_array(c->q + row_item * c->d_qk, qf, c->d_qk);
+            float *rec = sc->scratch + (row_item * ks + split) * (c->d_v + 2);
+            attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 0, rec,
+                       rec + c->d_v, rec + c->d_v + 1, buf);
+        }
     }
-    float *rec = sc->scratch + (row_item * ks + split) * (c->d_v + 2);
-    attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 0, rec,
-               rec + c->d_v, rec + c->d_v + 1, buf);
     free(rows);
     free(buf);
     free(qf);
@@ -438,7 +446,7 @@ int oracle_mla_decode_split(const uint16_t *q, const uint16_t *cache, const int3
                           0, n_seq, T, H, d_qk, d_v},
                          key_splits, scratch};
     const int64_t n_rows = (int64_t) n_seq * T * H;
-    const int used = run_pool(dec_split_item, &c, n_rows * key_splits, threads);
+    const int used = run_pool(dec_split_item, &c, (int64_t) n_seq * key_splits, threads);
     oracle_combine(scratch, n_rows, key_splits, d_v, o);
     return used;
 }
