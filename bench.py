@@ -277,11 +277,25 @@ def _sparse_list_shape(torch, dev, fn, label, scratch=None):
         for i in range(3):
             call(i)
         torch.cuda.synchronize()
+        # one pass over the cache copies captured in a CUDA graph and replayed: the device's time, not the caller's launch rate
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            st = side.cuda_stream
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(6):
+                    call(i)
+        torch.cuda.current_stream().wait_stream(side)
+        st = torch.cuda.current_stream().cuda_stream
+        graph.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 30 if T <= 4 else 6
+        n_replays = 5 if T <= 4 else 2
+        reps = 6 * n_replays
         e0.record()
-        for i in range(reps):
-            call(i)
+        for _ in range(n_replays):
+            graph.replay()
         e1.record()
         torch.cuda.synchronize()
         res[f"sparse2052_T{T}_H64_{label}"] = {"us_per_call": e0.elapsed_time(e1) * 1e3 / reps, "splits": splits}

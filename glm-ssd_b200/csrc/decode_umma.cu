@@ -491,6 +491,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     // instruction copies 512 contiguous bytes of one listed row (16 bytes per lane) to the place the tiled
                     // copy of the dense form would have put them: 64-column block c / 8, 16-byte chunk (c % 8) xor (r % 8)
                     // of row r.  Each lane's arrival on the stage's barrier follows its own copies.
+                    // (Measured per 64-row tile of 64 KB, rows already in L2: these copies 2.6 us, the same when four warps
+                    // share the issuing; TMA gather copies of four rows x 64 columns, 128 per tile, 5.9 us issued lane by
+                    // lane from one warp, 3.6 us with one copy per lane from four warps.  A listed row is 1 KB somewhere:
+                    // about 20-25 GB/s per SM whatever issues the requests, against 44 GB/s and more for the tiled copies
+                    // of consecutive rows.)
                     const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row;
                     const int ra = lane < valid ? max(lp[lane], 0) : 0, rb = lane + 32 < valid ? max(lp[lane + 32], 0) : 0;
                     constexpr int CPR = NBLK * 8;  // 16-byte chunks per row
