@@ -209,6 +209,61 @@ static inline void axpy_f16(float *o, float p, const uint16_t *v, int d) {
 }
 #endif
 
+/* Register-blocked forms used by the timed CPU baseline only: four query rows against one key row (the key row is widened
+ * once), and four weighted key rows into one output row (the output row is loaded and stored once). */
+#if defined(__F16C__) && defined(__AVX2__) && defined(__FMA__)
+static inline float hsum8(__m256 v) {
+    float t[8];
+    _mm256_storeu_ps(t, v);
+    return ((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7]));
+}
+static inline void dot4_f32_f16(const float *q, int64_t q_stride, const uint16_t *k, int d, float out[4]) {
+    __m256 a0 = _mm256_setzero_ps(), a1 = a0, a2 = a0, a3 = a0, b0 = a0, b1 = a0, b2 = a0, b3 = a0;
+    int r = 0;
+    for (; r + 16 <= d; r += 16) {
+        const __m256 k0 = _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (k + r)));
+        const __m256 k1 = _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (k + r + 8)));
+        a0 = _mm256_fmadd_ps(_mm256_loadu_ps(q + r), k0, a0);
+        b0 = _mm256_fmadd_ps(_mm256_loadu_ps(q + r + 8), k1, b0);
+        a1 = _mm256_fmadd_ps(_mm256_loadu_ps(q + q_stride + r), k0, a1);
+        b1 = _mm256_fmadd_ps(_mm256_loadu_ps(q + q_stride + r + 8), k1, b1);
+        a2 = _mm256_fmadd_ps(_mm256_loadu_ps(q + 2 * q_stride + r), k0, a2);
+        b2 = _mm256_fmadd_ps(_mm256_loadu_ps(q + 2 * q_stride + r + 8), k1, b2);
+        a3 = _mm256_fmadd_ps(_mm256_loadu_ps(q + 3 * q_stride + r), k0, a3);
+        b3 = _mm256_fmadd_ps(_mm256_loadu_ps(q + 3 * q_stride + r + 8), k1, b3);
+    }
+    out[0] = hsum8(_mm256_add_ps(a0, b0));
+    out[1] = hsum8(_mm256_add_ps(a1, b1));
+    out[2] = hsum8(_mm256_add_ps(a2, b2));
+    out[3] = hsum8(_mm256_add_ps(a3, b3));
+    const float *lut = h2f_table();
+    for (; r < d; r++)
+        for (int i = 0; i < 4; i++) out[i] += q[i * q_stride + r] * lut[k[r]];
+}
+static inline void axpy4_f16(float *o, const float p[4], const uint16_t *const v[4], int d) {
+    const __m256 p0 = _mm256_set1_ps(p[0]), p1 = _mm256_set1_ps(p[1]), p2 = _mm256_set1_ps(p[2]), p3 = _mm256_set1_ps(p[3]);
+    int c = 0;
+    for (; c + 8 <= d; c += 8) {
+        __m256 a = _mm256_loadu_ps(o + c);
+        a = _mm256_fmadd_ps(p0, _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (v[0] + c))), a);
+        a = _mm256_fmadd_ps(p1, _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (v[1] + c))), a);
+        a = _mm256_fmadd_ps(p2, _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (v[2] + c))), a);
+        a = _mm256_fmadd_ps(p3, _mm256_cvtph_ps(_mm_loadu_si128((const __m128i *) (v[3] + c))), a);
+        _mm256_storeu_ps(o + c, a);
+    }
+    const float *lut = h2f_table();
+    for (; c < d; c++)
+        for (int i = 0; i < 4; i++) o[c] += p[i] * lut[v[i][c]];
+}
+#else
+static inline void dot4_f32_f16(const float *q, int64_t q_stride, const uint16_t *k, int d, float out[4]) {
+    for (int i = 0; i < 4; i++) out[i] = dot_f32_f16(q + i * q_stride, k, d);
+}
+static inline void axpy4_f16(float *o, const float p[4], const uint16_t *const v[4], int d) {
+    for (int i = 0; i < 4; i++) axpy_f16(o, p[i], v[i], d);
+}
+#endif
+
 static void attend_row(const float *q, int d_qk, int d_v, const uint16_t *K, int64_t k_stride, const uint16_t *V,
                        int64_t v_stride, const int32_t *rows, int64_t row0, int64_t n, float scale, int normalise,
                        float *o, float *m_out, float *l_out, float *score_buf) {
@@ -388,9 +443,10 @@ int oracle_mla_decode_partial(const uint16_t *q, const uint16_t *cache, const in
 
 /* The same decode with the attended rows of every (sequence, token, head) cut into `key_splits` ranges by the
  * reference's split rule (per = ceil(n / splits), ops.cu:447-449) and merged by oracle_combine (ops.cu:558-573).
- * One work item is (sequence, key range) and walks all T*H query rows over that range, so the range's cache rows are
- * read from memory once and serve every head from the core's cache - the order a CPU wants, and the form that keeps
- * every host core busy when n_seq*T*H is small.  `scratch` holds n_seq*T*H*key_splits*(d_v+2) floats. */
+ * One work item is (sequence, key range): it walks the range in blocks of 32 keys and passes all T*H query rows over each
+ * block with an online softmax (running maximum and rescale, ops.cu:503-517), so every cache row is read from memory
+ * once and serves every head from the core's cache - the order a CPU wants, and the form that keeps every host core
+ * busy when n_seq*T*H is small.  `scratch` holds n_seq*T*H*key_splits*(d_v+2) floats. */
 typedef struct {
     dec_ctx_t d;
     int key_splits;
@@ -404,37 +460,94 @@ static void dec_split_item(void *vctx, int64_t item) {
     const int b = (int) (item / ks);
     const int split = (int) (item % ks);
     const int64_t len = c->seq_lens[b] > 0 ? c->seq_lens[b] : 0;
-    const int64_t per_max = (len + ks - 1) / ks;
-    float *qf = (float *) malloc(sizeof(float) * (size_t) c->d_qk);
-    float *buf = (float *) malloc(sizeof(float) * (size_t) (per_max > 0 ? per_max : 1));
-    int32_t *rows = c->page_table ? (int32_t *) malloc(sizeof(int32_t) * (size_t) (per_max > 0 ? per_max : 1)) : NULL;
-    for (int t = 0; t < c->T; t++) {
+    const int n_q = c->T * c->H;
+    enum { KB = 32 }; /* keys per block: a block's rows stay in the core's cache while all query rows pass over them */
+    float *qf = (float *) malloc(sizeof(float) * (size_t) n_q * c->d_qk);
+    float *acc = (float *) calloc((size_t) n_q * c->d_v, sizeof(float));
+    float *m = (float *) malloc(sizeof(float) * (size_t) n_q);
+    float *l = (float *) calloc((size_t) n_q, sizeof(float));
+    float *sc_blk = (float *) malloc(sizeof(float) * (size_t) n_q * KB);
+    int64_t *lo_q = (int64_t *) malloc(sizeof(int64_t) * (size_t) c->T), *hi_q = (int64_t *) malloc(sizeof(int64_t) * (size_t) c->T);
+    oracle_f16_to_f32_array(c->q + (int64_t) b * n_q * c->d_qk, qf, (int64_t) n_q * c->d_qk);
+    int64_t lo_all = len, hi_all = 0;
+    for (int t = 0; t < c->T; t++) { /* the key range of this split for every query token (ops.cu:447-449) */
         int64_t n = len - (c->T - 1 - t);
         if (n < 0) n = 0;
         const int64_t per = (n + ks - 1) / ks;
-        const int64_t lo = split * per < n ? split * per : n;
-        const int64_t hi = lo + per < n ? lo + per : n;
-        const int64_t cnt = hi - lo;
-        int64_t row0 = 0;
-        if (c->page_table) {
-            const int32_t *pt = c->page_table + (int64_t) b * c->page_table_stride;
-            for (int64_t i = 0; i < cnt; i++) {
-                const int64_t pos = lo + i;
-                rows[i] = pt[pos / c->page_rows] * c->page_rows + (int32_t) (pos % c->page_rows);
-            }
-        } else {
-            row0 = (c->seq_base ? (int64_t) c->seq_base[b] : 0) + lo;
+        lo_q[t] = split * per < n ? split * per : n;
+        hi_q[t] = lo_q[t] + per < n ? lo_q[t] + per : n;
+        if (lo_q[t] < lo_all) lo_all = lo_q[t];
+        if (hi_q[t] > hi_all) hi_all = hi_q[t];
+    }
+    for (int i = 0; i < n_q; i++) m[i] = -INFINITY;
+    const int32_t *pt = c->page_table ? c->page_table + (int64_t) b * c->page_table_stride : NULL;
+    const int64_t base = c->page_table ? 0 : (c->seq_base ? (int64_t) c->seq_base[b] : 0);
+    for (int64_t k0 = lo_all; k0 < hi_all; k0 += KB) {
+        const int64_t k1 = k0 + KB < hi_all ? k0 + KB : hi_all;
+        const uint16_t *rows[KB];
+        for (int64_t k = k0; k < k1; k++) {
+            const int64_t row = pt ? (int64_t) pt[k / c->page_rows] * c->page_rows + k % c->page_rows : base + k;
+            rows[k - k0] = c->cache + row * c->d_qk;
         }
-        for (int h = 0; h < c->H; h++) {
-            const int64_t row_item = ((int64_t) b * c->T + t) * c->H + h;
-            oracle_f16_to_f32_array(c->q + row_item * c->d_qk, qf, c->d_qk);
-            float *rec = sc->scratch + (row_item * ks + split) * (c->d_v + 2);
-            attend_row(qf, c->d_qk, c->d_v, c->cache, c->d_qk, c->cache, c->d_qk, rows, row0, cnt, c->scale, 0, rec,
-                       rec + c->d_v, rec + c->d_v + 1, buf);
+        /* scores of the block: four query rows at a time against each key row; a row's keys outside its own causal
+         * range are computed and then ignored */
+        for (int q0 = 0; q0 < n_q; q0 += 4) {
+            if (q0 + 4 <= n_q) {
+                for (int64_t k = k0; k < k1; k++) {
+                    float s4[4];
+                    dot4_f32_f16(qf + (int64_t) q0 * c->d_qk, c->d_qk, rows[k - k0], c->d_qk, s4);
+                    for (int i = 0; i < 4; i++) sc_blk[(q0 + i) * KB + (k - k0)] = s4[i] * c->scale;
+                }
+            } else {
+                for (int qi = q0; qi < n_q; qi++)
+                    for (int64_t k = k0; k < k1; k++)
+                        sc_blk[qi * KB + (k - k0)] = dot_f32_f16(qf + (int64_t) qi * c->d_qk, rows[k - k0], c->d_qk) * c->scale;
+            }
+        }
+        for (int qi = 0; qi < n_q; qi++) {
+            const int t = qi / c->H;
+            const int64_t a0 = k0 > lo_q[t] ? k0 : lo_q[t], a1 = k1 < hi_q[t] ? k1 : hi_q[t];
+            if (a1 <= a0) continue;
+            const float *sc_k = sc_blk + qi * KB;
+            float mx = m[qi];
+            for (int64_t k = a0; k < a1; k++)
+                if (sc_k[k - k0] > mx) mx = sc_k[k - k0];
+            float *o = acc + (int64_t) qi * c->d_v;
+            if (mx > m[qi]) { /* running maximum moved: rescale what was summed so far (ops.cu:503-517) */
+                const float f = m[qi] == -INFINITY ? 0.f : expf(m[qi] - mx);
+                for (int d = 0; d < c->d_v; d++) o[d] *= f;
+                l[qi] *= f;
+                m[qi] = mx;
+            }
+            int64_t k = a0;
+            for (; k + 4 <= a1; k += 4) {
+                float p4[4];
+                for (int i = 0; i < 4; i++) {
+                    p4[i] = expf(sc_k[k + i - k0] - mx);
+                    l[qi] += p4[i];
+                }
+                axpy4_f16(o, p4, rows + (k - k0), c->d_v);
+            }
+            for (; k < a1; k++) {
+                const float p = expf(sc_k[k - k0] - mx);
+                l[qi] += p;
+                axpy_f16(o, p, rows[k - k0], c->d_v);
+            }
         }
     }
-    free(rows);
-    free(buf);
+    for (int qi = 0; qi < n_q; qi++) {
+        const int64_t row_item = (int64_t) b * n_q + qi;
+        float *rec = sc->scratch + (row_item * ks + split) * (c->d_v + 2);
+        memcpy(rec, acc + (int64_t) qi * c->d_v, sizeof(float) * (size_t) c->d_v);
+        rec[c->d_v] = m[qi];
+        rec[c->d_v + 1] = l[qi];
+    }
+    free(hi_q);
+    free(lo_q);
+    free(sc_blk);
+    free(l);
+    free(m);
+    free(acc);
     free(qf);
 }
 
