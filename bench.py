@@ -746,11 +746,31 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
     O = torch.empty((S, H, d), dtype=torch.float32, device=dev)
     sec = time_loop(lambda i: pkg.prefill_attn(Q, K, V, out=O), min(steps, 20), 3)
     flops = H * S * (S + 1) / 2 * (2 * d + 2 * d)
+    # one launch after an idle pause (the board is below its power cap), then the clock during half a second of launches
+    single = []
+    for _ in range(5):
+        torch.cuda.synchronize()
+        time.sleep(0.05)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        pkg.prefill_attn(Q, K, V, out=O)
+        e1.record()
+        torch.cuda.synchronize()
+        single.append(e0.elapsed_time(e1))
+    load = ClockSampler(dev.index or 0)
+    load.start()
+    t_end = time.perf_counter() + 0.5
+    while time.perf_counter() < t_end:
+        for _ in range(20):
+            pkg.prefill_attn(Q, K, V, out=O)
+        torch.cuda.synchronize()
+    load_clocks = load.stop()
     res["prefill8k"] = {"metric": "TFLOP/s (causal FLOPs)", "value": flops / sec / 1e12, "ms_per_step": sec * 1e3,
                         "frac_of_tensor_peak": flops / sec / 1e12 / tf_peak[0],
                         "frac_of_sustained_tensor_peak": flops / sec / 1e12 / tf_peak[1],
                         "note": "timed back to back, i.e. under the power cap: the sustained figure is the fitting denominator",
-                        "flops": flops, "scaling": "replicas"}
+                        "flops": flops, "scaling": "replicas", "ms_single_launch_after_idle": min(single),
+                        "tflops_single_launch_after_idle": flops / (min(single) * 1e-3) / 1e12, "clocks_under_load": load_clocks}
     return res
 
 

@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     // share the issuing; TMA gather copies of four rows x 64 columns, 128 per tile, 5.9 us issued lane by
                     // lane from one warp, 3.6 us with one copy per lane from four warps.  A listed row is 1 KB somewhere:
                     // about 20-25 GB/s per SM whatever issues the requests, against 44 GB/s and more for the tiled copies
-                    // of consecutive rows.)
+                    // of consecutive rows.  Splitting a tile between the two paths does not add them up: with 16, 24 or 32
+                    // of the 64 rows on gather copies and the rest on these copies the T = 256 shape took 468, 549 and 589 us
+                    // against 343 us, and an evict-last hint on the listed rows 367 us.)
                     const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row;
                     const int ra = lane < valid ? max(lp[lane], 0) : 0, rb = lane + 32 < valid ? max(lp[lane + 32], 0) : 0;
                     constexpr int CPR = NBLK * 8;  // 16-byte chunks per row

@@ -15,11 +15,28 @@
 // the scores run up to three tiles ahead of the softmax.  Shared memory holds the 64 KB query tile, three 32 KB
 // K stages and two 32 KB V stages, fed by two independent TMA producers: every load has more than a tile period
 // to land (128-key tiles in single buffers left the tensor pipe waiting for every load).  Three warps issue
-// MMAs (scores of even tiles, scores of odd tiles, P.V): a single thread issues one MMA per ~65 cycles whatever
-// its size, which for 20 MMAs per 64-key tile is more than the tensor time.  What bounds the steady state now is
-// the tensor pipe itself: an M = 128, N = 64 MMA with both operands in shared memory occupies it for ~49
+// MMAs (scores of even tiles, scores of odd tiles, P.V): an issuing thread is held while the pipe works off its
+// MMAs, so one thread cannot keep the queue filled with both kinds.  What bounds the tensor time is the pipe itself: an M = 128, N = 64 MMA with both operands in shared memory occupies it for ~49
 // cycles (it is bound by reading (M + N) x 32 operand bytes, not by the math, which would take 32), so a
 // tile takes about 16 x 49 + 4 x 129 = 1300 cycles (measured 1240) against 1049 at peak.
+// Measured on the heaviest CTA with all SMs busy (clock stamps, GS_PF_PROF): a tile takes 1240-1330 cycles; the
+// softmax threads are busy 1130 of them (80 reading the scores, 255 row maximum, 630 exponentials - 64 per thread at
+// the special-function rate of 4 per cycle and quarter - and 160 writing P), and a hand-over through an mbarrier
+// (MMA done -> waiting warp runs on) costs 200-300 cycles.  So the tensor time and the softmax time nearly coincide,
+// and what keeps both busy is the depth of the score buffers.  Measured alternatives, all with correct results:
+//  * score MMAs over 128 keys (N = 128: 65 cycles where two N = 64 take 98), fed by a ring of [128 keys x 64 columns]
+//    blocks: 7 % slower with the probabilities written over two double-width score buffers (the next scores then wait
+//    for the P.V of the pair before), 12 % slower with one double-width score buffer and four probability buffers;
+//  * the query block kept in tensor memory (128 columns; an N = 64 MMA then takes 33 cycles instead of 49), which
+//    leaves room for one score buffer and two probability buffers: the same speed with P.V issued as soon as its
+//    probabilities are there, 6 % slower with P.V held back until the scores two tiles on are issued, 7 % slower
+//    with one thread issuing both kinds (an issuing thread is held while the pipe works off its MMAs).
+//  * the first half of the query block in tensor memory (64 columns) beside three score buffers: a tile takes 1168
+//    cycles instead of 1245, and the S = 8192, H = 20 chunk takes the same 0.60 ms.  83200 tiles over 148 SMs at 1245
+//    cycles in 0.60 ms is an SM clock of 1.17 GHz (1.97 GHz unloaded): back-to-back launches of this kernel run under
+//    the board's power cap, where fewer cycles buy a lower clock, not a shorter time.
+// Cycles per MMA from one issuing thread, long runs: M = 128, K = 16, both operands in shared memory N = 64 49,
+// N = 128 65, N = 256 129; A in tensor memory N = 32 24, N = 64 33, N = 128 65, N = 256 129.
 // The accumulator is rescaled lazily (only when a row maximum grows by more than 2^8), decided per warp.
 // Every mbarrier wait is bounded and ends in an error status instead of a hang.
 #include <string.h>
@@ -157,8 +174,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_prefill_umma(const __grid_con
         }
     } else if (warp == 1 || warp == 7) {
         // ---- score MMA issuers: S = Q . K^T, warp 1 the even tiles, warp 7 the odd ones --------------------------
-        // One thread issues an MMA about every 65 cycles whatever its size, and a tile needs 16 of these (N = 64)
-        // besides the 4 P.V MMAs: three issuing warps keep the issue time below the tensor time.
+        // An issuing thread is held while the pipe works off its MMAs; a tile needs 16 of these (N = 64) besides the
+        // 4 P.V MMAs: three issuing warps keep the pipe's queue filled.
         constexpr uint32_t idesc_s = make_idesc_f16(BM, BN, 0, 0);
         const uint64_t d_kmaj = make_smem_desc(0, 16, 1024, kSwizzle128B);
         const uint32_t q_lo = smem_u32(q_smem) >> 4, k_lo = smem_u32(k_smem) >> 4;
@@ -385,3 +402,10 @@ int launch_prefill_umma(const __half *q, const __half *k, const __half *v, void 
 }
 
 }  // namespace gs
+
+#ifdef GS_PF_PROF
+// timing probe only: copies the clock stamps of the heaviest CTA to the host
+extern "C" __attribute__((visibility("default"))) int gs_pf_prof_read(long long *host) {
+    return (int) cudaMemcpyFromSymbol(host, gs::g_pf_prof, sizeof(long long) * 32 * 8);
+}
+#endif
