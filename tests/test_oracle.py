@@ -247,6 +247,32 @@ def test_decode_cut_into_key_ranges_equals_the_plain_decode(oracle):
         assert np.abs(a - b).max() <= 2e-6, (n, T, ks, np.abs(a - b).max())
 
 
+def test_key_range_decode_on_ragged_paged_batches_and_odd_row_counts(oracle):
+    """The key-range form walks blocks of 32 keys with four query rows at a time: row counts that are no multiple of
+    four, empty and short sequences, pages out of order and ranges that end inside a block must all agree with the
+    single-pass decode, and with float64 numpy on the dense case."""
+    rng = np.random.default_rng(23)
+    lens = [100, 0, 777, 33]
+    pt = np.array([[3, 1] + [0] * 11, [0] * 13, list(range(2, 15)), [15] + [0] * 12], np.int32)
+    cache = (rng.standard_normal((16 * 64, 576), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+    for T, Hh, ks in ((2, 4, 5), (3, 5, 2), (1, 1, 9), (2, 7, 1), (4, 3, 64)):
+        q = rng.standard_normal((4, T, Hh, 576), dtype=np.float32).astype(np.float16)
+        a = oracle.mla_decode(q, cache, lens, 1 / 16, page_table=pt)
+        b = oracle.mla_decode(q, cache, lens, 1 / 16, page_table=pt, key_splits=ks)
+        assert np.abs(a - b).max() <= 2e-6, (T, Hh, ks, np.abs(a - b).max())
+        assert not b[1].any()  # the empty sequence
+    n, T, Hh = 300, 2, 5
+    q = rng.standard_normal((1, T, Hh, 576), dtype=np.float32).astype(np.float16)
+    c = cache[:n]
+    got = oracle.mla_decode(q, c, [n], 1 / 16, key_splits=3).astype(np.float64)
+    for t in range(T):
+        k = c[:n - (T - 1 - t)].astype(np.float64)
+        sc = q[0, t].astype(np.float64) @ k.T / 16
+        p = np.exp(sc - sc.max(1, keepdims=True))
+        want = (p / p.sum(1, keepdims=True)) @ k[:, :512]
+        assert np.abs(got[0, t] - want).max() <= 2e-6
+
+
 # ---- DSA k-pool indexer (crates/cuda/kernels/ops.cu:619-791) ------------------------------------------------
 
 def _np_pool(kc, gc, ape, kpool):
