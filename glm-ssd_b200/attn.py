@@ -244,6 +244,7 @@ class MlaDecodeLayer:
         # stream of the layer's own; the kernels read and write the page-locked host tensors in place
         self.use_graph = bool(use_graph)
         self._graphs = {}
+        self._fast = None  # (q_host, kv_host, T, graph handle, output view) of the last graph step
         self._graph_stream = None
         if self.use_graph:
             torch.cuda.synchronize(self.device)
@@ -280,6 +281,19 @@ class MlaDecodeLayer:
         """q_host f16 [T,H,d_qk], kv_host f32 [T,d_qk] in pinned host memory -> f32 [T,H,d_v] (host).
         One C call enqueues copy-in, append, attention and copy-out; then the stream is drained.  In graph
         mode the host buffers are part of the recorded graph: reuse the same two tensors every step."""
+        fast = self._fast
+        if fast is not None and q_host is fast[0] and kv_host is fast[1]:
+            # the same two host tensors as in the step before (the graph names their memory): nothing to look up.
+            # A step is tens of microseconds, so the interpreter's share of this method is measurable (2.5 us before).
+            _, _, T, h, out = fast
+            pos = self.pos
+            if pos + T > self.ctx:
+                raise RuntimeError(f"context full ({self.ctx} tokens)")
+            rc = self._graph_step(h, pos, self._graph_stream_handle, 1)
+            if rc:
+                _lib.check(rc, "gs_mla_layer_graph_step")
+            self.pos = pos + T
+            return out
         T = q_host.shape[0]
         if T > self.T_max:
             raise ValueError("T exceeds T_max")
@@ -295,7 +309,10 @@ class MlaDecodeLayer:
             if rc:
                 _lib.check(rc, "gs_mla_layer_graph_step")
             self.pos += T
-            return self._o_host[0, :T]
+            out = self._o_host[0, :T]
+            # remembered by identity; a tensor whose storage or shape was changed in place must not be passed again
+            self._fast = (q_host, kv_host, T, h, out)
+            return out
         s = self._step
         s.q_host, s.kv_host = q_host.data_ptr(), kv_host.data_ptr()
         s.pos0, s.T = self.pos, T
