@@ -32,9 +32,9 @@
 //    probabilities are there, 6 % slower with P.V held back until the scores two tiles on are issued, 7 % slower
 //    with one thread issuing both kinds (an issuing thread is held while the pipe works off its MMAs).
 //  * the first half of the query block in tensor memory (64 columns) beside three score buffers: a tile takes 1168
-//    cycles instead of 1245, and the S = 8192, H = 20 chunk takes the same 0.60 ms.  83200 tiles over 148 SMs at 1245
-//    cycles in 0.60 ms is an SM clock of 1.17 GHz (1.97 GHz unloaded): back-to-back launches of this kernel run under
-//    the board's power cap, where fewer cycles buy a lower clock, not a shorter time.
+//    cycles instead of 1245, and the S = 8192, H = 20 chunk takes the same 0.60 ms.  During back-to-back launches of
+//    this kernel the SM clock reads 1567 MHz of 1965 with the software power cap as the only reason: at the board's
+//    power limit fewer cycles buy a lower clock, not a shorter time.
 // Cycles per MMA from one issuing thread, long runs: M = 128, K = 16, both operands in shared memory N = 64 49,
 // N = 128 65, N = 256 129; A in tensor memory N = 32 24, N = 64 33, N = 128 65, N = 256 129.
 // The accumulator is rescaled lazily (only when a row maximum grows by more than 2^8), decided per warp.
