@@ -497,7 +497,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                     // about 20-25 GB/s per SM whatever issues the requests, against 44 GB/s and more for the tiled copies
                     // of consecutive rows.  Splitting a tile between the two paths does not add them up: with 16, 24 or 32
                     // of the 64 rows on gather copies and the rest on these copies the T = 256 shape took 468, 549 and 589 us
-                    // against 343 us, and an evict-last hint on the listed rows 367 us.)
+                    // against 343 us, and an evict-last hint on the listed rows 367 us.  Asking for the next tile's list
+                    // entries a tile ahead (346 us) or dropping the eviction hint (339 us) changes nothing either: for that
+                    // shape the profiler shows L2 at 7 %, DRAM at 4 % and the L1 fill path at 8 % of their peaks - the
+                    // copies are bound by what one SM keeps in flight, two 64 KB tiles against 3.2 us of latency each.)
                     const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row;
                     const int ra = lane < valid ? max(lp[lane], 0) : 0, rb = lane + 32 < valid ? max(lp[lane + 32], 0) : 0;
                     constexpr int CPR = NBLK * 8;  // 16-byte chunks per row
