@@ -103,7 +103,6 @@ using namespace sm100;
 constexpr int TILE = 64;                 // cache rows per tile
 constexpr int BLK_BYTES = TILE * 128;    // one 64-column block of a tile: 64 rows x 128 B
 constexpr int NBLK_MAX = 9;              // 576 / 64
-constexpr int STAGE_BYTES = NBLK_MAX * BLK_BYTES;
 constexpr int STAGES = 2;
 // A tile's blocks may complete separate barriers (groups of GRP blocks) so that the score MMAs of a group are issued as
 // soon as it has landed.  Measured on the B200 with three groups of three: the boxes of a tile are requested together and
@@ -112,12 +111,12 @@ constexpr int STAGES = 2;
 constexpr int GRP = NBLK_MAX;
 constexpr int NGRP = (NBLK_MAX + GRP - 1) / GRP;
 constexpr int AHEAD = 2;                 // tiles of a CTA's range asked into L2 before the inputs are final (1-3 measured: 2 best)
-constexpr int N_MMA_WARPS = 3;           // concurrently issuing MMA warps
+constexpr int N_MMA_WARPS = 3;           // MMA warp slots (warps 1-3); a kernel form issues from the first NI of them
 constexpr int NTHREADS = 32 * (1 + N_MMA_WARPS + 4);  // warp 0 producer, warps 1-3 MMA, warps 4-7 softmax group
 constexpr int TMEM_COLS = 512;
-// TMEM columns (slots of NQ columns): S^T partials [2 buffers][N_MMA_WARPS issuers], then the 4 O^T tiles:
-// 10 x 48 = 480 of the 512 columns for NQ = 48
-constexpr int O_SLOT0 = 2 * N_MMA_WARPS;
+// TMEM columns (slots of NQ columns): S^T partials [2 buffers][NI issuers], then the 4 O^T tiles:
+// 10 x 48 = 480 of the 512 columns for NQ = 48 with three issuers, 8 x 64 = 512 for NQ = 64 with two
+__host__ __device__ constexpr int issuers_for(int nq) { return nq > 48 ? 2 : 3; }
 constexpr int NVT = 4;                   // 128-column value tiles (d_v = 512)
 constexpr int MAX_SEQ = 1024;
 constexpr int UNIT_CAP = 1 << 29;         // the running sum of units saturates here (two such values still add in an int)
@@ -165,11 +164,15 @@ struct Barriers {
     uint64_t q_full, q_empty, o_full, o_empty;
 };
 
-template <int NQ>
+// NQ <= 48: stages and query rows sized for the widest row (576 columns), one layout for both row widths.  NQ = 64 (only
+// built for 512-column rows): sized by the row width, or two stages, the query rows and P would not fit.
+template <int NQ, int NBLK = NBLK_MAX>
 struct Smem {
-    static constexpr int Q_BYTES = NBLK_MAX * NQ * 128;
+    static constexpr int SBLK = NQ > 48 ? NBLK : NBLK_MAX;   // 64-column blocks a stage and the query rows are sized for
+    static constexpr int STAGE = SBLK * BLK_BYTES;
+    static constexpr int Q_BYTES = SBLK * NQ * 128;
     static constexpr int P_BYTES = NQ * TILE * 2;
-    static constexpr int OFF_Q = STAGES * STAGE_BYTES;
+    static constexpr int OFF_Q = STAGES * STAGE;
     static constexpr int OFF_P = OFF_Q + Q_BYTES;
     static constexpr int OFF_MISC = OFF_P + 2 * P_BYTES;
     struct Misc {
@@ -187,6 +190,7 @@ struct Smem {
         int lim[NQ];
     };
     static constexpr int TOTAL = OFF_MISC + (int) sizeof(Misc) + 1024;  // + slack for the 1024-byte alignment
+    static_assert(TOTAL <= 232448, "shared memory of one CTA");
 };
 
 struct Segment {
@@ -260,7 +264,7 @@ __device__ __forceinline__ bool group_any(int id, int n_threads, bool pred) {
 }
 
 // P.V for the O^T tiles [MT_LO, MT_HI): nk 16-row k-steps, fully unrolled
-template <int NQ, int MT_LO, int MT_HI>
+template <int NQ, int MT_LO, int MT_HI, int O_SLOT0>
 __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t d_pt, uint32_t kv_lo, uint32_t p_lo,
                                          uint32_t idesc, int nk, bool acc0) {
     if (nk == 4) {
@@ -284,7 +288,11 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t 
 
 template <int NQ, int NBLK, bool LIST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
-    using SM = Smem<NQ>;
+    using SM = Smem<NQ, NBLK>;
+    constexpr int NI = issuers_for(NQ);   // issuing MMA warps
+    constexpr int O_SLOT0 = 2 * NI;       // first O^T slot in tensor memory
+    constexpr int STAGE_BYTES = SM::STAGE;
+    static_assert((O_SLOT0 + 4) * NQ <= TMEM_COLS, "tensor memory columns");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     uint8_t *kv_smem = smem;
@@ -326,17 +334,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tma_prefetch_desc(&P.tm_q);
         for (int s = 0; s < STAGES; s++) {
             for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], LIST ? 32 : 1);  // list form: one arrival per producer lane
-            mbar_init(&B.kv_empty[s], N_MMA_WARPS);
+            mbar_init(&B.kv_empty[s], NI);
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(&B.s_full[s], N_MMA_WARPS);
+            mbar_init(&B.s_full[s], NI);
             mbar_init(&B.s_empty[s], 4);
             mbar_init(&B.p_full[s], 4);
-            mbar_init(&B.p_empty[s], N_MMA_WARPS);
+            mbar_init(&B.p_empty[s], NI);
         }
         mbar_init(&B.q_full, (LIST && P.q_f32) ? 4 : 1);  // f32 queries are converted by the four softmax warps
-        mbar_init(&B.q_empty, N_MMA_WARPS);
-        mbar_init(&B.o_full, N_MMA_WARPS);
+        mbar_init(&B.q_empty, NI);
+        mbar_init(&B.o_full, NI);
         mbar_init(&B.o_empty, 4);
         M.abort_flag = 0;
         M.flag[0] = M.flag[1] = 0;
@@ -574,7 +582,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             }
             sgc++;
         }
-    } else if (warp <= N_MMA_WARPS) {
+    } else if (warp <= NI) {
         // =================================== MMA issuers ====================================================
         // Three warps issue concurrently: one issuer cannot keep the tensor pipe busy with MMAs this
         // small.  Each warp owns its accumulators: a third of the 16-column k-steps of S^T (partial sums,
@@ -584,7 +592,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         constexpr uint32_t idesc_s = make_idesc_f16(64, NQ, 0, 0);    // A, B K-major
         constexpr uint32_t idesc_pv = make_idesc_f16(128, NQ, 1, 1);  // A (V^T) and B (P^T) MN-major
         constexpr int KSTEPS = NBLK * 4;
-        constexpr int K_PER = (KSTEPS + N_MMA_WARPS - 1) / N_MMA_WARPS;
+        constexpr int K_PER = (KSTEPS + NI - 1) / NI;
         // the landing groups this warp's score k-steps read
         const int g_lo = ((mw * K_PER) >> 2) / GRP, g_hi = ((min(KSTEPS, (mw + 1) * K_PER) - 1) >> 2) / GRP;
         constexpr int g_all = NGRP;
@@ -608,7 +616,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                         const int kidx = mw * K_PER + k;
                         if (kidx < KSTEPS) {
                             const int kb = kidx >> 2, ks = kidx & 3;
-                            umma_ss(tmem + (s * N_MMA_WARPS + mw) * NQ, d_kmaj + (kv_lo + kb * (BLK_BYTES >> 4) + ks * 2),
+                            umma_ss(tmem + (s * NI + mw) * NQ, d_kmaj + (kv_lo + kb * (BLK_BYTES >> 4) + ks * 2),
                                     d_kmaj + (q_lo + kb * (NQ * 128 >> 4) + ks * 2), idesc_s, k != 0);
                         }
                     }
@@ -660,9 +668,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const bool acc0 = j > 0;
                 const bool last = j == sg.n_tiles - 1;
                 if (elect_one()) {
-                    if (mw == 0) issue_pv<NQ, 0, 2>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
-                    else if (mw == 1) issue_pv<NQ, 2, 3>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
-                    else issue_pv<NQ, 3, 4>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    if (mw == 0) issue_pv<NQ, 0, 2, O_SLOT0>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    else if (NI == 2) issue_pv<NQ, 2, 4, O_SLOT0>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    else if (mw == 1) issue_pv<NQ, 2, 3, O_SLOT0>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
+                    else issue_pv<NQ, 3, 4, O_SLOT0>(tmem, d_vt, d_pt, kv_lo, p_lo, idesc_pv, nk, acc0);
                     umma_commit(&B.kv_empty[s]);
                     umma_commit(&B.p_empty[s]);
                     if (last) {
@@ -675,7 +684,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             }
             sgc++;
         }
-    } else {
+    } else if (warp > N_MMA_WARPS) {  // (with two issuers warp 3 has no part)
         // =================================== softmax / epilogue group ==========================================
         const int wg_tid = tid - 32 * (1 + N_MMA_WARPS);
         const int qt = warp & 3;                      // TMEM lane quarter this warp may touch
@@ -755,14 +764,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #pragma unroll
                 for (int c = 0; c < NQ / 16; c++) {
                     uint32_t r0[16], r1[16], r2[16];
-                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 0) * NQ + c * 16, r0);
-                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 1) * NQ + c * 16, r1);
-                    tmem_ld16(tmem + lane_base + (s * N_MMA_WARPS + 2) * NQ + c * 16, r2);
+                    tmem_ld16(tmem + lane_base + (s * NI + 0) * NQ + c * 16, r0);
+                    tmem_ld16(tmem + lane_base + (s * NI + 1) * NQ + c * 16, r1);
+                    if (NI > 2) tmem_ld16(tmem + lane_base + (s * NI + 2) * NQ + c * 16, r2);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const int q = c * 16 + i;
-                        const float v = (__uint_as_float(r0[i]) + __uint_as_float(r1[i])) + __uint_as_float(r2[i]);
+                        float v = __uint_as_float(r0[i]) + __uint_as_float(r1[i]);
+                        if (NI > 2) v += __uint_as_float(r2[i]);
                         // lanes 0..15 keep query rows [0, HQ), lanes 16..31 fetch [HQ, NQ) from lane - 16
                         if (q < HQ) {
                             if (!hi) sv[q] = v;
@@ -942,22 +952,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             float *acc = P.ws_acc + (int64_t) sg.seg_id * P.rows_q * P.d_v + qt * 32 + lane;
             // one value tile (NQ columns of this lane's row) per step; the loads of the next tile are in flight
             // while the current one is stored
-            uint32_t rbuf[2][NQ];
+            constexpr int NB = NQ > 48 ? 1 : 2;  // (64 columns twice over would not leave the registers for the rest)
+            uint32_t rbuf[NB][NQ];
+            if (NB == 2) {
 #pragma unroll
-            for (int c = 0; c < NQ / 16; c++) tmem_ld16(tmem + lane_base + O_SLOT0 * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
+                for (int c = 0; c < NQ / 16; c++) tmem_ld16(tmem + lane_base + O_SLOT0 * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
+            }
             {
 #pragma unroll
                 for (int mt = 0; mt < NVT; mt++) {
+                    if (NB == 1) {
+#pragma unroll
+                        for (int c = 0; c < NQ / 16; c++)
+                            tmem_ld16(tmem + lane_base + (O_SLOT0 + mt) * NQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rbuf[0] + c * 16));
+                    }
                     tmem_wait_ld();
-                    if (mt + 1 < NVT) {
+                    if (NB == 2 && mt + 1 < NVT) {
 #pragma unroll
                         for (int c = 0; c < NQ / 16; c++)
                             tmem_ld16(tmem + lane_base + (O_SLOT0 + mt + 1) * NQ + c * 16,
-                                      *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & 1] + c * 16));
+                                      *reinterpret_cast<uint32_t(*)[16]>(rbuf[(mt + 1) & (NB - 1)] + c * 16));
                     }
 #pragma unroll
                     for (int q = 0; q < NQ; q++)
-                        if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(rbuf[mt & 1][q]), pol_keep);
+                        if (q < P.rows_q) st_global_hint(acc + (int64_t) q * P.d_v + mt * 128, __uint_as_float(rbuf[mt & (NB - 1)][q]), pol_keep);
                 }
             }
             tc_fence_before();
@@ -991,7 +1009,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 
 template <int NQ, int NBLK, bool LIST = false>
 int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
-    const int smem = Smem<NQ>::TOTAL;
+    const int smem = Smem<NQ, NBLK>::TOTAL;
     // attributes are set on every call: a cached flag would go stale across a device reset
     GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK, LIST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
@@ -1028,11 +1046,53 @@ static int list_head_groups(int H) {
 // otherwise the rows are dealt to CTAs as in the dense form and the records live in `part`
 // (T*H*splits*(R+2) floats, crates/cuda/kernels/ops.cu:578): accumulators [segment][row][R], then (m, l) [segment][row][2], then
 // the per-sequence descriptors.
+// What a cut into n_groups head groups gives: the grid, whether every (token, group) is attended whole by one CTA, and
+// the longest run of tiles one CTA walks (what the call's time follows).
+struct ListPlan {
+    int n_groups, grid, grid_rec, grid_whole;
+    bool whole;
+    int64_t depth;
+};
+static ListPlan list_plan(int n_groups, int T, int H, int R, int sel_stride, int splits, const float *part, int grid_max) {
+    ListPlan L{};
+    L.n_groups = n_groups;
+    const int Hg = H / n_groups;
+    const int64_t n_seq_k = (int64_t) T * n_groups;
+    const int64_t tiles_seq = (sel_stride + TILE - 1) / TILE;
+    // records that fit the caller's buffer
+    if (splits > 1 && part && !(reinterpret_cast<uintptr_t>(part) & 15)) {
+        const int64_t part_floats = (int64_t) T * H * splits * (R + 2);
+        const int64_t desc_floats = (n_seq_k * 2 + 3) / 4 * 4;
+        const int64_t segs = (part_floats - desc_floats) / ((int64_t) Hg * (R + 2));
+        const int64_t tiles = n_seq_k * tiles_seq;
+        int64_t g = segs - n_seq_k;
+        if (g > grid_max) g = grid_max;
+        if (g > tiles) g = tiles;
+        L.grid_rec = (int) (g > 0 ? g : 0);
+    }
+    L.grid_whole = (int) (n_seq_k < grid_max ? n_seq_k : grid_max);
+    L.whole = L.grid_rec <= L.grid_whole;
+    L.grid = L.whole ? L.grid_whole : L.grid_rec;
+    L.depth = L.whole ? (n_seq_k + L.grid - 1) / L.grid * tiles_seq : (n_seq_k * tiles_seq + L.grid - 1) / L.grid;
+    return L;
+}
+
 int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
                             float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st) {
-    const int n_groups = list_head_groups(H);
-    if (R != 512 || n_groups == 0 || sel_stride <= 0 || !(scale > 0.f)) return -1;
+    const int g48 = list_head_groups(H);
+    if (R != 512 || g48 == 0 || sel_stride <= 0 || !(scale > 0.f)) return -1;
     if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(q) & 15)) return -1;
+    int grid_max = sm_count < kMaxCtas ? sm_count : kMaxCtas;
+    if (grid_max < 1) grid_max = 1;
+    // 49..64 heads: two groups of at most 32 heads (the listed rows are copied once per group), or all heads in one
+    // pass with 64 query columns and two issuing warps.  Listed rows arrive at a latency-bound rate per SM, so the
+    // cut with the shorter longest run of tiles wins; the two-group form on a tie.
+    ListPlan L = list_plan(g48, T, H, R, sel_stride, splits, part, grid_max);
+    if (H > 48 && H <= 64) {
+        const ListPlan L1 = list_plan(1, T, H, R, sel_stride, splits, part, grid_max);
+        if (L1.depth < L.depth) L = L1;
+    }
+    const int n_groups = L.n_groups;
     const int64_t n_seq_k = (int64_t) T * n_groups;
     if (n_seq_k > MAX_SEQ) return -1;
     const int Hg = H / n_groups;
@@ -1064,23 +1124,8 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
     P.cache_rows = sel_stride;  // caps a length word: a list holds at most sel_stride entries
     P.o = o;
     P.status = nullptr;
-    int grid_max = sm_count < kMaxCtas ? sm_count : kMaxCtas;
-    if (grid_max < 1) grid_max = 1;
-    // records that fit the caller's buffer
-    int grid_rec = 0;
-    if (splits > 1 && part && !(reinterpret_cast<uintptr_t>(part) & 15)) {
-        const int64_t part_floats = (int64_t) T * H * splits * (R + 2);
-        const int64_t desc_floats = (n_seq_k * 2 + 3) / 4 * 4;
-        const int64_t segs = (part_floats - desc_floats) / ((int64_t) Hg * (R + 2));
-        const int64_t tiles = n_seq_k * ((sel_stride + TILE - 1) / TILE);
-        int64_t g = segs - n_seq_k;
-        if (g > grid_max) g = grid_max;
-        if (g > tiles) g = tiles;
-        grid_rec = (int) (g > 0 ? g : 0);
-    }
-    const int grid_whole = (int) (n_seq_k < grid_max ? n_seq_k : grid_max);
-    const bool whole = grid_rec <= grid_whole;
-    const int grid = whole ? grid_whole : grid_rec;
+    const bool whole = L.whole;
+    const int grid = L.grid;
     P.whole_seq = whole ? 1 : 0;
     CombinePlan c{};
     if (!whole) {
@@ -1110,7 +1155,8 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
     }
     int e;
     if (Hg <= 32) e = launch_cfg<32, 8, true>(P, grid, st);
-    else e = launch_cfg<48, 8, true>(P, grid, st);
+    else if (Hg <= 48) e = launch_cfg<48, 8, true>(P, grid, st);
+    else e = launch_cfg<64, 8, true>(P, grid, st);
     if (e) return e;
     if (!whole) return launch_combine(c, st);
     return 0;

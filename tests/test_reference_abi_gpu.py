@@ -242,6 +242,8 @@ def test_reference_q8_kernels_pin_oracle(pkg, cuda, oracle):
     (1, 64, 2052, False, 16), (2, 64, 2052, False, 4), (1, 32, 700, False, 16), (4, 16, 33, False, 4),
     (1, 64, 0, True, 16), (2, 48, 1, True, 4), (3, 64, 1000, True, 4), (40, 64, 300, False, 4), (256, 16, 70, False, 1),
     (9, 80, 130, False, 1), (1, 16, 2052, False, 1), (8, 64, 515, False, 4), (2, 96, 64, True, 4), (5, 64, 63, False, 1),
+    # 64 heads in one pass (64 query columns, two issuing warps): taken when it shortens the longest run of tiles
+    (80, 64, 130, False, 1), (150, 64, 70, True, 1), (30, 64, 1000, False, 8), (256, 64, 200, False, 1),
 ])
 def test_gs_mla_attn_tensor_kernel_vs_oracle_and_cuda_core_kernel(pkg, cuda, oracle, T, H, n, dense, splits):
     """The same call on both kernels: the CUDA-core kernel (f32 queries) and the tcgen05 kernel fed from the position
