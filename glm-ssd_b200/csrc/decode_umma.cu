@@ -11,7 +11,8 @@
 //  * A producer warp streams 64-row cache tiles into a two-stage shared-memory ring with TMA
 //    (128-byte swizzle, one 64x64 box per 64-column block); the ragged last tile of a segment is
 //    fetched in 16-row boxes so no row outside the segment is read.
-//  * The contraction is small on the query side (T*H = 20..48 rows), so the cache rows fill the
+//  * The contraction is small on the query side (T*H = 20..48 rows; 64 in the position-list form for 64
+//    heads over 512-column rows, with two issuing warps instead of three), so the cache rows fill the
 //    128-lane datapath and the packed query rows (all heads of all query tokens) ride on the MMA's
 //    N side:  S^T[64 x NQ] = C_tile[64 x d_qk] . Q^T   (M = 64 cache rows, K-major operands),
 //             O^T[128 x NQ] += V^T[128 x 64] . P^T     (M = 128 value columns; the SAME shared-memory
@@ -1035,6 +1036,7 @@ int read_list_status(int32_t *out) {
 }
 
 // Position lists on the tensor cores.  Head groups of at most 48 heads (a multiple of 8 each): 0 = not cut that way.
+// (49..64 heads may also run as one group of 64 query columns, see launch_decode_umma_list.)
 static int list_head_groups(int H) {
     const int n = (H + 47) / 48;
     return (n > 0 && H % n == 0 && (H / n) % 8 == 0) ? n : 0;
