@@ -1168,7 +1168,8 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
     if (p.q_is_f32) { *why = "f32 queries"; return false; }
     if (p.sel) { *why = "explicit position lists"; return false; }
     if (!((p.d_qk == 576 || p.d_qk == 512) && p.d_v == 512)) { *why = "row widths other than 576/512 or 512/512"; return false; }
-    if (p.T * p.H > 48) {
+    const bool one64 = p.d_qk == 512 && p.T * p.H <= 64;  // 512-column rows: up to 64 query rows ride in one pass
+    if (p.T * p.H > 48 && !one64) {
         // wider blocks run as head groups of at most 48 rows, one launch each (the cache is read once per group)
         if (p.T > 4 || p.H % 8 != 0) { *why = "more than 48 query rows per sequence with T > 4 or H % 8 != 0"; return false; }
         if (p.exchange) { *why = "more than 48 query rows per sequence together with a cross-GPU exchange"; return false; }
@@ -1182,9 +1183,11 @@ bool decode_umma_supported(const DecodeProblem &p, const char **why) {
 }
 
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
-    // Head groups: up to 48 query rows (T tokens x Hg heads) ride on the N side of one launch.
+    // Head groups: up to 48 query rows (T tokens x Hg heads) ride on the N side of one launch; up to 64 over
+    // 512-column rows (the stages and the query rows are then sized by the row width, see Smem).
     int Hg = p.H, n_groups = 1, seq_div = 1;
-    if (p.T * p.H > 48) {
+    const bool one64 = p.d_qk == 512 && p.T * p.H <= 64;
+    if (p.T * p.H > 48 && !one64) {
         const int hg_max = (48 / p.T) & ~7;          // a multiple of 8 heads
         n_groups = (p.H + hg_max - 1) / hg_max;
         Hg = (((p.H + n_groups - 1) / n_groups) + 7) & ~7;  // balanced, rounded up to 8
@@ -1240,7 +1243,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         const int hg = p.H - h0 < Hg ? p.H - h0 : Hg;
         if (hg <= 0) break;
         const int rows_q = p.T * hg;
-        const int NQ = rows_q <= 32 ? 32 : 48;
+        const int NQ = rows_q <= 32 ? 32 : rows_q <= 48 ? 48 : 64;
         // one box of NQ rows when the rows of a sequence are contiguous, else one box of hg rows per token
         if (int e = encode_tmap_2d_f16(&P.tm_q, p.q, (uint64_t) p.n_seq * p.T * p.H, (uint64_t) p.d_qk, (uint64_t) p.d_qk * 2,
                                        (uint32_t) (P.H_full == hg ? NQ : hg), 64, kSw128)) return e;
@@ -1272,7 +1275,7 @@ int launch_decode_umma(const DecodeProblem &p, cudaStream_t st) {
         c.bulk = true;
         int e;
         if (p.d_qk == 576) e = NQ == 32 ? launch_cfg<32, 9>(P, grid, st) : launch_cfg<48, 9>(P, grid, st);
-        else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : launch_cfg<48, 8>(P, grid, st);
+        else e = NQ == 32 ? launch_cfg<32, 8>(P, grid, st) : NQ == 48 ? launch_cfg<48, 8>(P, grid, st) : launch_cfg<64, 8>(P, grid, st);
         if (e) return e;
         if (p.ev_after_main && g == n_groups - 1) GS_TRY(cudaEventRecord(p.ev_after_main, st));
         if (p.no_combine) continue;

@@ -154,6 +154,35 @@ def test_reference_twin_shape_64_heads_runs_on_the_tensor_core_kernel(pkg, cuda,
     check_close(o.cpu().numpy(), oracle.mla_decode(q, cache, [4096], 1 / 16, d_v=512), "R=512 H=64")
 
 
+@pytest.mark.parametrize("n_seq,T,H,paged", [(1, 2, 32, False), (3, 1, 56, False), (5, 1, 64, True), (2, 4, 16, False), (1, 1, 80, False)])
+def test_512_column_rows_with_49_to_64_query_rows_in_one_pass(pkg, cuda, oracle, n_seq, T, H, paged):
+    """Over 512-column rows up to 64 query rows (tokens x heads) ride in one pass of the tcgen05 kernel (64 query
+    columns, two issuing warps); 80 heads still run as head groups.  Ragged lengths, dense with bases and paged."""
+    rng = np.random.default_rng(n_seq * 100 + T * 10 + H)
+    lens = rng.integers(1, 700, size=n_seq).astype(np.int32)
+    lens[0] = 643
+    q = rng.standard_normal((n_seq, T, H, 512), dtype=np.float32).astype(np.float16)
+    if paged:
+        pages_per = -(-lens // 64)
+        n_pages = int(pages_per.sum()) + 3
+        cache = (rng.standard_normal((n_pages * 64, 512), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+        perm = rng.permutation(n_pages)
+        pt = np.zeros((n_seq, int(pages_per.max())), np.int32)
+        k = 0
+        for b in range(n_seq):
+            pt[b, :pages_per[b]] = perm[k:k + pages_per[b]]
+            k += int(pages_per[b])
+        o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, lens), page_table=to_dev(cuda, pt), impl=2, d_v=512)
+        want = oracle.mla_decode(q, cache, lens, 1 / 16, d_v=512, page_table=pt)
+    else:
+        base = (np.arange(n_seq) * 704).astype(np.int32)
+        cache = (rng.standard_normal((n_seq * 704, 512), dtype=np.float32) * np.float32(0.5)).astype(np.float16)
+        o = pkg.mla_decode(to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, lens), seq_base=to_dev(cuda, base), impl=2, d_v=512)
+        want = oracle.mla_decode(q, cache, lens, 1 / 16, d_v=512, seq_base=base)
+    cuda.cuda.synchronize()
+    check_close(o.cpu().numpy(), want, f"R=512, {T}x{H} query rows")
+
+
 @pytest.mark.parametrize("T", [1, 2])
 def test_length_beyond_the_cache_is_taken_as_the_cache_size(pkg, cuda, oracle, T):
     """Input hardening: a length word larger than the cache allocation (or negative) must not be followed past the
