@@ -331,12 +331,24 @@ def _paged_twin(torch, dev, ref_fn):
     return res
 
 
-def _sparse_list_shape(torch, dev, fn, label, profile=False):
+def _sparse_list_shape(torch, dev, fn, label, profile=False, q8=False):
     """The engine's own decode shape: 64 heads, f32 queries, a sparse list of 2052 positions per query token
     out of a 32768-row cache (forward.rs:461, :873), through the reference's entry point gs_mla_attn."""
     res = {}
     ctx, n, Hh = 32768, 2052, 64
     caches = [(torch.randn((ctx, 512), device=dev) * 0.5).half() for _ in range(6)]
+    scales = [None] * 6
+    if q8:  # the reference's Q8 cache (ops.cu:599-610): int8 rows and one f16 scale per 32 values, quantised on the device
+        pkg = importlib.import_module("glm-ssd_b200")
+        q8c, q8s = [], []
+        for c in caches:
+            qq = torch.empty((ctx, 512), dtype=torch.int8, device=dev)
+            dd = torch.empty((ctx, 16), dtype=torch.float16, device=dev)
+            pkg.quant_q8_rows(c.float().contiguous(), qq, dd, ctx * 512)
+            q8c.append(qq)
+            q8s.append(dd)
+        torch.cuda.synchronize()
+        caches, scales = q8c, q8s
     st = torch.cuda.current_stream().cuda_stream
     for T, splits in ((1, 16), (2, 4), (256, 1)):  # decode, MTP verify, a prefill chunk (forward.rs:898-901)
         q = torch.randn((T, Hh, 512), device=dev, dtype=torch.float32)
@@ -346,7 +358,8 @@ def _sparse_list_shape(torch, dev, fn, label, profile=False):
         part = torch.empty(T * Hh * splits * 514, dtype=torch.float32, device=dev)  # the reference's size (ops.cu:578)
 
         def call(i):
-            rc = fn(q.data_ptr(), caches[i % 6].data_ptr(), None, sel.data_ptr(), n, cnt.data_ptr(), SCALE, o.data_ptr(),
+            rc = fn(q.data_ptr(), caches[i % 6].data_ptr(), None if scales[i % 6] is None else scales[i % 6].data_ptr(), sel.data_ptr(), n,
+                    cnt.data_ptr(), SCALE, o.data_ptr(),
                     part.data_ptr(), T, Hh, 512, splits, st)
             assert rc == 0, rc
 
@@ -820,6 +833,12 @@ def run_others(pkg, torch, dist, dev, world, rank, randn_f16, time_loop, hbm_pea
         finally:
             pkg.mla_attn_impl(0)
         sp.update(_sparse_list_shape(torch, dev, fn, "tensor_path"))
+        sp.update(_sparse_list_shape(torch, dev, fn, "q8_tensor_path", q8=True))
+        pkg.mla_attn_impl(1)
+        try:
+            sp.update(_sparse_list_shape(torch, dev, fn, "q8_cuda_core", q8=True))
+        finally:
+            pkg.mla_attn_impl(0)
         torch.cuda.synchronize()
         sp["tensor_path_status"] = pkg.mla_attn_status()
         res["gs_mla_attn_sparse"] = sp

@@ -155,16 +155,16 @@ GS_EXPORT int gs_mla_attn(const float *q, const void *C, const void *C_scales, c
     if (splits > 1 && !part) return fail_invalid("gs_mla_attn: part workspace required when splits > 1");
     DecodeProblem p{};
     if (int e = device_sm_count(&p.sm_count)) return e;
-    // f16 cache: the tcgen05 kernel's producer warp fetches the listed rows itself and the kernel rounds the queries to
-    // f16 itself; it needs nothing beyond the reference's own arguments.  Q8 caches and shapes it does not take run on
-    // the CUDA-core kernel below.
+    // The tcgen05 kernel's producer warp fetches the listed rows itself (f16 rows, or int8 rows and their scales, which
+    // the kernel widens in shared memory) and the kernel rounds the queries to f16 itself; it needs nothing beyond the
+    // reference's own arguments.  Shapes it does not take run on the CUDA-core kernel below.
     const int impl = g_attn_impl.load(std::memory_order_relaxed);
-    if (!C_scales && impl != 1) {
-        const int e = launch_decode_umma_list(q, (const __half *) C, sel, sel_stride, cnt, scale, o, part, T, H, R, splits,
+    if (impl != 1) {
+        const int e = launch_decode_umma_list(q, C, (const __half *) C_scales, sel, sel_stride, cnt, scale, o, part, T, H, R, splits,
                                               p.sm_count, (cudaStream_t) stream);
         if (e >= 0) return e;
     }
-    if (impl == 2) return fail_invalid("gs_mla_attn: the tcgen05 kernel does not take this call (Q8 cache, head count, alignment or scale)");
+    if (impl == 2) return fail_invalid("gs_mla_attn: the tcgen05 kernel does not take this call (head count, alignment or scale)");
     p.q = q;
     p.q_is_f32 = true;
     p.cache = (const __half *) C;

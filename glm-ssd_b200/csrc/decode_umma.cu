@@ -146,7 +146,8 @@ struct UmmaParams {
     int H_full, h0;                // q holds H_full heads per token; this launch takes heads h0 .. h0+H-1
     // position-list form (the reference's sel / cnt): kernel sequence b attends rows sel[(b / seq_div) * sel_stride + i],
     // i < seq_lens[b / seq_div]; the rows are fetched by the producer warp with 16-byte asynchronous copies
-    const void *list_cache;        // the cache as a plain pointer (rows of d_qk f16)
+    const void *list_cache;        // the cache as a plain pointer (rows of d_qk f16, or of d_qk int8 when list_scales is set)
+    const __half *list_scales;     // Q8 cache (crates/cuda/kernels/ops.cu:427): one f16 scale per 32 values, [rows][d_qk / 32]
     const int32_t *sel;
     int sel_stride;
     const float *q_f32;            // list form: f32 queries [tokens][H_full][d_qk], rounded to f16 inside the kernel
@@ -161,21 +162,24 @@ struct UmmaParams {
 
 struct Barriers {
     uint64_t kv_full[STAGES][NGRP], kv_empty[STAGES];
+    uint64_t kv_raw[STAGES];  // Q8 list form: the int8 rows and scales of a tile have landed (not yet widened)
     uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
     uint64_t q_full, q_empty, o_full, o_empty;
 };
 
 // NQ <= 48: stages and query rows sized for the widest row (576 columns), one layout for both row widths.  NQ = 64 (only
 // built for 512-column rows): sized by the row width, or two stages, the query rows and P would not fit.
-template <int NQ, int NBLK = NBLK_MAX>
+template <int NQ, int NBLK = NBLK_MAX, bool Q8 = false>
 struct Smem {
-    static constexpr int SBLK = NQ > 48 ? NBLK : NBLK_MAX;   // 64-column blocks a stage and the query rows are sized for
+    static constexpr int SBLK = (NQ > 48 || Q8) ? NBLK : NBLK_MAX;   // 64-column blocks a stage and the query rows are sized for
     static constexpr int STAGE = SBLK * BLK_BYTES;
     static constexpr int Q_BYTES = SBLK * NQ * 128;
     static constexpr int P_BYTES = NQ * TILE * 2;
     static constexpr int OFF_Q = STAGES * STAGE;
     static constexpr int OFF_P = OFF_Q + Q_BYTES;
-    static constexpr int OFF_MISC = OFF_P + 2 * P_BYTES;
+    static constexpr int QS_BYTES = Q8 ? TILE * (NBLK * 2) * 2 : 0;  // Q8: the tile's scales, NBLK * 2 halves per row
+    static constexpr int OFF_QS = OFF_P + 2 * P_BYTES;
+    static constexpr int OFF_MISC = OFF_QS + STAGES * QS_BYTES;
     struct Misc {
         Barriers bar;
         uint32_t tmem_base;
@@ -287,9 +291,10 @@ __device__ __forceinline__ void issue_pv(uint32_t tmem, uint64_t d_vt, uint64_t 
     }
 }
 
-template <int NQ, int NBLK, bool LIST>
+template <int NQ, int NBLK, bool LIST, bool Q8 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_constant__ UmmaParams P) {
-    using SM = Smem<NQ, NBLK>;
+    static_assert(!Q8 || LIST, "the Q8 cache comes with position lists only");
+    using SM = Smem<NQ, NBLK, Q8>;
     constexpr int NI = issuers_for(NQ);   // issuing MMA warps
     constexpr int O_SLOT0 = 2 * NI;       // first O^T slot in tensor memory
     constexpr int STAGE_BYTES = SM::STAGE;
@@ -299,6 +304,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
     uint8_t *kv_smem = smem;
     uint8_t *q_smem = smem + SM::OFF_Q;
     uint8_t *p_smem = smem + SM::OFF_P;
+    uint8_t *qs_smem = smem + SM::OFF_QS;
     typename SM::Misc &M = *reinterpret_cast<typename SM::Misc *>(smem + SM::OFF_MISC);
     Barriers &B = M.bar;
     volatile int *abort_flag = &M.abort_flag;
@@ -334,7 +340,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
         tma_prefetch_desc(&P.tm_kv16);
         tma_prefetch_desc(&P.tm_q);
         for (int s = 0; s < STAGES; s++) {
-            for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], LIST ? 32 : 1);  // list form: one arrival per producer lane
+            // list form: one arrival per producer lane; Q8 list form: one per softmax warp, after the widening
+            for (int g = 0; g < NGRP; g++) mbar_init(&B.kv_full[s][g], Q8 ? 4 : LIST ? 32 : 1);
+            mbar_init(&B.kv_raw[s], 32);
             mbar_init(&B.kv_empty[s], NI);
         }
         for (int s = 0; s < 2; s++) {
@@ -495,7 +503,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 const int row = sg.r0 + j * TILE;
                 const int valid = min(TILE, sg.r1 - row);
                 uint8_t *dst = kv_smem + s * STAGE_BYTES;
-                if (LIST) {
+                if (LIST && Q8) {
+                    // Q8 cache: the listed rows arrive as they are - 512 bytes of int8 per row (one 16-byte copy per lane)
+                    // into the upper half of the stage, their scales (32 bytes per row) beside the stages - and the
+                    // softmax warps widen them to f16 in place before the MMAs see the stage (see there).
+                    const int32_t *lp = P.sel + (int64_t) (sg.b / P.seq_div) * P.sel_stride + row;
+                    const int ra = lane < valid ? max(lp[lane], 0) : 0, rb = lane + 32 < valid ? max(lp[lane + 32], 0) : 0;
+                    const char *qbase = reinterpret_cast<const char *>(P.list_cache);
+                    const char *sbase = reinterpret_cast<const char *>(P.list_scales);
+                    uint8_t *raw = dst + STAGE_BYTES / 2;
+                    uint8_t *qs = qs_smem + s * SM::QS_BYTES;
+#pragma unroll 4
+                    for (int r = 0; r < valid; r++) {
+                        const int grow = __shfl_sync(0xffffffffu, r < 32 ? ra : rb, r & 31);
+                        cp_async16_hint(raw + r * (NBLK * 64) + lane * 16, qbase + (int64_t) grow * (NBLK * 64) + lane * 16, pol_stream);
+                    }
+#pragma unroll
+                    for (int k = 0; k < TILE / 16; k++) {  // scales: two 16-byte halves per row, sixteen rows per instruction
+                        const int r = k * 16 + (lane >> 1);
+                        const int ga = __shfl_sync(0xffffffffu, ra, r & 31), gb = __shfl_sync(0xffffffffu, rb, r & 31);
+                        const int grow = r < 32 ? ga : gb;
+                        if (r < valid)
+                            cp_async16_hint(qs + r * (NBLK * 4) + (lane & 1) * 16, sbase + (int64_t) grow * (NBLK * 4) + (lane & 1) * 16, pol_stream);
+                    }
+                    cp_async_mbar_arrive(&B.kv_raw[s]);
+                    __syncwarp();
+                } else if (LIST) {
                     // Rows named by the position list.  Lane l holds the cache rows of tile rows l and l + 32; every warp
                     // instruction copies 512 contiguous bytes of one listed row (16 bytes per lane) to the place the tiled
                     // copy of the dense form would have put them: 64-column block c / 8, 16-byte chunk (c % 8) xor (r % 8)
@@ -751,9 +784,61 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 nm[i] = UNSET;
             }
             named_bar_sync(1, 128);
+            // Q8 cache: widen tile i (the jj-th of this segment): int8 rows (upper half of the stage) x f16 scales ->
+            // half_rn(scale * q) in the operand layout the f16 form's copies produce (crates/cuda/kernels/ops.cu:461-477 attends over
+            // these values).  Each of the four warps takes 16 rows into registers; only when every raw row is in
+            // registers are the f16 rows written, since they cover the raw area.  Rows past the segment's end become
+            // zeros.  Done for the segment's first tile before its scores are awaited and for every further tile right
+            // after the probabilities of the tile before are handed over, so that it runs beside that tile's P.V.
+            auto widen_tile = [&](uint32_t i, int jj) {
+                const int s = i & 1;
+                (void) mbar_wait(&B.kv_raw[s], (i >> 1) & 1, abort_flag, status_w, ST_SOFTMAX);
+                const int valid_q = min(TILE, sg.r1 - (sg.r0 + jj * TILE));
+                uint8_t *stage = kv_smem + s * STAGE_BYTES;
+                const uint8_t *raw = stage + STAGE_BYTES / 2;
+                const uint8_t *qs = qs_smem + s * SM::QS_BYTES;
+                uint4 rv[16];
+#pragma unroll
+                for (int k = 0; k < 16; k++) rv[k] = *reinterpret_cast<const uint4 *>(raw + (qt * 16 + k) * (NBLK * 64) + lane * 16);
+                named_bar_sync(1, 128);
+#pragma unroll
+                for (int k = 0; k < 16; k++) {
+                    const int r = qt * 16 + k;
+                    // scale * q as an f16 product: q (|q| <= 127) is exact in f16 and the product of an 11-bit by a 7-bit
+                    // significand is exact before the one rounding, so this is half_rn(scale * q) bit for bit.  The bytes
+                    // become f16 through the 1024-offset trick: 0x6400 | (q + 128) is the f16 number 1152 + q.
+                    const __half sc = r < valid_q ? *reinterpret_cast<const __half *>(qs + r * (NBLK * 4) + (lane >> 1) * 2) : __ushort_as_half(0);
+                    const __half2 sc2 = __half2half2(sc), off2 = __half2half2(__ushort_as_half(0x6480));  // 1152
+                    auto widen4 = [&](uint32_t w, uint32_t &h01, uint32_t &h23) {
+                        const uint32_t u = w ^ 0x80808080u;
+                        uint32_t a = __byte_perm(u, 0x64646464u, 0x5140), b2 = __byte_perm(u, 0x64646464u, 0x7362);
+                        const __half2 x = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&a), off2), sc2);
+                        const __half2 y = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&b2), off2), sc2);
+                        h01 = *reinterpret_cast<const uint32_t *>(&x);
+                        h23 = *reinterpret_cast<const uint32_t *>(&y);
+                    };
+                    uint4 lo, hi;
+                    widen4(rv[k].x, lo.x, lo.y);
+                    widen4(rv[k].y, lo.z, lo.w);
+                    widen4(rv[k].z, hi.x, hi.y);
+                    widen4(rv[k].w, hi.z, hi.w);
+                    if (r >= valid_q) lo = hi = make_uint4(0, 0, 0, 0);  // (a stale byte times a zero scale is zero too; this says so)
+                    // 16-byte chunks 2 * lane and 2 * lane + 1 of the row.  Lanes of every other 64-column block store
+                    // their odd chunk first, so that one store instruction covers all eight chunk positions of the
+                    // 128-byte lines (four lanes each) instead of four positions (eight lanes each).
+                    const int flip = (lane >> 2) & 1;
+                    const int c0 = lane * 2 + flip, c1 = lane * 2 + 1 - flip;
+                    *reinterpret_cast<uint4 *>(stage + (c0 >> 3) * BLK_BYTES + r * 128 + (((c0 & 7) ^ (r & 7)) << 4)) = flip ? hi : lo;
+                    *reinterpret_cast<uint4 *>(stage + (c1 >> 3) * BLK_BYTES + r * 128 + (((c1 & 7) ^ (r & 7)) << 4)) = flip ? lo : hi;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&B.kv_full[s][0]);
+            };
             for (int j = 0; j < sg.n_tiles; j++, it++) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
+                if (Q8 && j == 0) widen_tile(it, 0);
                 (void) mbar_wait(&B.s_full[s], ph, abort_flag, status_w, ST_SOFTMAX);
                 GS_STAMP(it, PF_S_FULL);
                 tc_fence_after();
@@ -897,6 +982,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&B.p_full[s]);
                 GS_STAMP(it, PF_P_WRITTEN);
+                if (Q8 && j + 1 < sg.n_tiles) widen_tile(it + 1, j + 1);
             }
             if (!ok) break;
             // ---- end of segment: drain the accumulators into this segment's partial record ----------------
@@ -1008,11 +1094,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
 #undef GS_CTA_STAMP
 }
 
-template <int NQ, int NBLK, bool LIST = false>
+template <int NQ, int NBLK, bool LIST = false, bool Q8 = false>
 int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
-    const int smem = Smem<NQ, NBLK>::TOTAL;
+    const int smem = Smem<NQ, NBLK, Q8>::TOTAL;
     // attributes are set on every call: a cached flag would go stale across a device reset
-    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK, LIST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GS_TRY(cudaFuncSetAttribute(k_decode_umma<NQ, NBLK, LIST, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NTHREADS);
@@ -1024,7 +1110,7 @@ int launch_cfg(const UmmaParams &P, int grid, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    GS_TRY(cudaLaunchKernelEx(&cfg, k_decode_umma<NQ, NBLK, LIST>, P));
+    GS_TRY(cudaLaunchKernelEx(&cfg, k_decode_umma<NQ, NBLK, LIST, Q8>, P));
     return 0;
 }
 
@@ -1079,18 +1165,18 @@ static ListPlan list_plan(int n_groups, int T, int H, int R, int sel_stride, int
     return L;
 }
 
-int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
-                            float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st) {
+int launch_decode_umma_list(const float *q, const void *C, const __half *C_scales, const int32_t *sel, int sel_stride, const int32_t *cnt,
+                            float scale, float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st) {
     const int g48 = list_head_groups(H);
     if (R != 512 || g48 == 0 || sel_stride <= 0 || !(scale > 0.f)) return -1;
-    if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(q) & 15)) return -1;
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(C_scales) & 15)) return -1;
     int grid_max = sm_count < kMaxCtas ? sm_count : kMaxCtas;
     if (grid_max < 1) grid_max = 1;
     // 49..64 heads: two groups of at most 32 heads (the listed rows are copied once per group), or all heads in one
     // pass with 64 query columns and two issuing warps.  Listed rows arrive at a latency-bound rate per SM, so the
     // cut with the shorter longest run of tiles wins; the two-group form on a tie.
     ListPlan L = list_plan(g48, T, H, R, sel_stride, splits, part, grid_max);
-    if (H > 48 && H <= 64) {
+    if (H > 48 && H <= 64 && !C_scales) {  // (the 64-column form is built for the f16 cache only)
         const ListPlan L1 = list_plan(1, T, H, R, sel_stride, splits, part, grid_max);
         if (L1.depth < L.depth) L = L1;
     }
@@ -1108,6 +1194,7 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
     P.tm_kv16 = P.tm_kv64;
     P.tm_q = P.tm_kv64;
     P.list_cache = C;
+    P.list_scales = C_scales;
     P.seq_lens = cnt;
     P.sel = sel;
     P.sel_stride = sel_stride;
@@ -1156,7 +1243,8 @@ int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel,
         c.bulk = true;
     }
     int e;
-    if (Hg <= 32) e = launch_cfg<32, 8, true>(P, grid, st);
+    if (C_scales) e = Hg <= 32 ? launch_cfg<32, 8, true, true>(P, grid, st) : launch_cfg<48, 8, true, true>(P, grid, st);
+    else if (Hg <= 32) e = launch_cfg<32, 8, true>(P, grid, st);
     else if (Hg <= 48) e = launch_cfg<48, 8, true>(P, grid, st);
     else e = launch_cfg<64, 8, true>(P, grid, st);
     if (e) return e;

@@ -73,8 +73,8 @@ int launch_exchange_combine(CombinePlan c, const gs_shard_exchange &x, float *o,
                             cudaStream_t st);
 bool decode_umma_supported(const DecodeProblem &p, const char **why);
 // position lists (the reference's sel / cnt) with f32 queries on the tcgen05 kernel: 0 launched, -1 shape not taken, else an error
-int launch_decode_umma_list(const float *q, const __half *C, const int32_t *sel, int sel_stride, const int32_t *cnt, float scale,
-                            float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st);
+int launch_decode_umma_list(const float *q, const void *C, const __half *C_scales, const int32_t *sel, int sel_stride, const int32_t *cnt,
+                            float scale, float *o, float *part, int T, int H, int R, int splits, int sm_count, cudaStream_t st);
 int read_list_status(int32_t *out);
 int launch_decode_umma(const DecodeProblem &p, cudaStream_t st);
 

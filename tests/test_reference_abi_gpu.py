@@ -183,17 +183,26 @@ def test_gs_quant_q8_rows_bit_exact(pkg, cuda, oracle):
 
 @pytest.mark.parametrize("T,H,n,splits,dense", [
     (1, 64, 4096, 16, True), (2, 64, 1500, 4, True), (1, 32, 2052, 16, False), (5, 16, 300, 1, False),
-    (1, 16, 0, 16, True), (2, 64, 33, 4, False),
+    (1, 16, 0, 16, True), (2, 64, 33, 4, False), (200, 64, 130, 1, False), (8, 48, 515, 4, False), (3, 96, 65, 2, False),
 ])
 def test_gs_mla_attn_q8_cache_vs_oracle(pkg, cuda, oracle, T, H, n, splits, dense):
     q, Cc, sel, cnt = _legacy_inputs(T * 77 + n, T, H, n, max(n, 1) + 100, dense)
     cq, cs = oracle.quant_q8_rows(Cc.astype(np.float32))
-    got = _call(cuda, pkg._lib.load().gs_mla_attn, q, cq, sel, cnt, splits, scales=cs)
-    # the oracle attends over exactly the f16 rows the kernel rebuilds from (q, scale)
+    L = pkg._lib.load()
+    got = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, splits, scales=cs)
+    # the oracle attends over exactly the f16 rows the kernels rebuild from (q, scale)
     want = oracle.mla_attn_ref(q, oracle.dequant_q8(cq, cs), sel, cnt, 1 / 16)
-    check_close(got, want, "gs_mla_attn q8")
+    check_close(got, want, "gs_mla_attn q8")  # the automatic choice: the tcgen05 kernel, queries rounded to f16
+    with _Impl(L, 1):
+        slow = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, splits, scales=cs)
+    check_close(slow, want, "gs_mla_attn q8, CUDA-core kernel", 2e-5, 2e-6)
+    with _Impl(L, 2):
+        fast = _call(cuda, L.gs_mla_attn, q, cq, sel, cnt, splits, scales=cs)
+    assert np.array_equal(fast, got), "the automatic choice takes the tcgen05 kernel for a Q8 cache too"
+    st = C.c_int32(-1)
+    assert L.gs_mla_attn_status(C.byref(st), None) == 0 and st.value == 0
     if n > 8:
-        check_not_degenerate(got, "gs_mla_attn q8")
+        check_not_degenerate(got[-1], "gs_mla_attn q8")
 
 
 def test_q8_append_then_attend_round_trip(pkg, cuda, oracle):
@@ -231,9 +240,13 @@ def test_reference_q8_kernels_pin_oracle(pkg, cuda, oracle):
     q, _, sel, cnt = _legacy_inputs(9, T, H, n, 257, False)
     o_ref = _call(cuda, ref.gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
     o_orc = oracle.mla_attn_ref(q, oracle.dequant_q8(oq, od), sel, cnt, 1 / 16)
-    o_new = _call(cuda, pkg._lib.load().gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
+    L = pkg._lib.load()
+    with _Impl(L, 1):
+        o_new = _call(cuda, L.gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
+    o_tc = _call(cuda, L.gs_mla_attn, q, oq, sel, cnt, 4, scales=od)
     check_close(o_orc, o_ref, "oracle vs reference kernel (q8)", 2e-5, 2e-6)
-    check_close(o_new, o_ref, "ours vs reference kernel (q8)", 2e-5, 2e-6)
+    check_close(o_new, o_ref, "CUDA-core kernel vs reference kernel (q8)", 2e-5, 2e-6)
+    check_close(o_tc, o_ref, "tcgen05 kernel vs reference kernel (q8)")
 
 
 # ---- kernel choice of gs_mla_attn: tcgen05 kernel by default for f16 caches, CUDA-core kernel as the second opinion ----
@@ -284,7 +297,7 @@ def test_gs_mla_attn_lists_with_scattered_unsorted_and_repeated_rows(pkg, cuda, 
 
 def test_gs_mla_attn_kernel_choice_limits(pkg, cuda, oracle):
     L = pkg._lib.load()
-    # a Q8 cache and 128 heads (not cut into groups of 8..48) stay on the CUDA-core kernel: exact against the oracle
+    # 128 heads (not cut into groups of 8..48) stay on the CUDA-core kernel: exact against the oracle
     q, Cc, sel, cnt = _legacy_inputs(3, 1, 128, 100, 150, False)
     got = _call(cuda, L.gs_mla_attn, q, Cc, sel, cnt, 4)
     check_close(got, oracle.mla_attn_ref(q, Cc, sel, cnt, 1 / 16), "128 heads", 2e-5, 2e-6)
