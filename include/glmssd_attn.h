@@ -41,13 +41,14 @@ extern "C" {
 int gs_mla_attn(const float *q, const void *C, const void *C_scales, const int *sel, int sel_stride, const int *cnt,
                 float scale, float *o, float *part, int T, int H, int R, int splits, void *stream);
 
-/* Which kernel gs_mla_attn runs (no counterpart in the reference).  With an f16 cache (C_scales == NULL) the call
- * runs on the tcgen05 decode kernel whenever that kernel takes the shape: the rows a list names are fetched straight
- * from the cache by the kernel's producer warp, the f32 queries are rounded to f16 inside the kernel (the precision
+/* Which kernel gs_mla_attn runs (no counterpart in the reference).  The call runs on the tcgen05 decode kernel whenever
+ * that kernel takes the shape: the rows a list names are fetched straight from the cache by the kernel's producer warp
+ * (f16 rows, or the int8 rows and scales of a Q8 cache, which the kernel widens to half_rn(scale * q) in shared
+ * memory), the f32 queries are rounded to f16 inside the kernel (the precision
  * of the f16-query entry points; outputs stay within max-abs 2e-3 of the f32-query result), and nothing beyond the
  * reference's own arguments is needed: with splits > 1 the split records live in `part` (as many segments as fit its
  * T*H*splits*(R+2) floats), with splits == 1 every (token, head group) is attended by one CTA that stores o itself.
- * Q8 caches, head counts that cannot be cut into groups of 8..48 heads and misaligned q / C run on the CUDA-core
+ * Head counts that cannot be cut into groups of 8..48 heads and misaligned q / C / C_scales run on the CUDA-core
  * kernel, which keeps the queries in f32.
  *   gs_mla_attn_set_impl(impl): 0 = automatic (default), 1 = always the CUDA-core kernel, 2 = the tcgen05 kernel or
  *     cudaErrorInvalidValue.  A process-wide setting; it changes no result beyond the rounding described above.

@@ -65,16 +65,21 @@ def test_random_position_lists_through_the_reference_entry_point(pkg, cuda, orac
         sel = rng.integers(0, ctx, size=(T, stride)).astype(np.int32)
         cnt = rng.integers(max(0, n - 70), n + 1, size=T).astype(np.int32)
         qd, cd, sd, nd = to_dev(cuda, q), to_dev(cuda, cache), to_dev(cuda, sel), to_dev(cuda, cnt)
+        scd, attended = None, cache
+        if rng.random() < 0.5:  # the Q8 cache: int8 rows + f16 scales; the oracle attends over the rows rebuilt from them
+            cq, cs = oracle.quant_q8_rows(cache.astype(np.float32))
+            cd, scd = to_dev(cuda, cq), to_dev(cuda, cs)
+            attended = oracle.dequant_q8(cq, cs)
         o = cuda.zeros((T, H, 512), dtype=cuda.float32, device="cuda")
         part_floats = T * H * splits * 514  # crates/cuda/kernels/ops.cu:578
         part = cuda.zeros(part_floats + 64, dtype=cuda.float32, device="cuda")
         part[part_floats:] = 7.0
-        rc = L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None, sd.data_ptr(), stride, nd.data_ptr(), 1 / 16, o.data_ptr(),
-                           part.data_ptr(), T, H, 512, splits, None)
+        rc = L.gs_mla_attn(qd.data_ptr(), cd.data_ptr(), None if scd is None else scd.data_ptr(), sd.data_ptr(), stride, nd.data_ptr(),
+                           1 / 16, o.data_ptr(), part.data_ptr(), T, H, 512, splits, None)
         cuda.cuda.synchronize()
-        what = f"seed {seed} case {it}: T={T} H={H} n={n} splits={splits}"
+        what = f"seed {seed} case {it}: T={T} H={H} n={n} splits={splits} q8={scd is not None}"
         assert rc == 0, what
         assert bool((part[part_floats:] == 7.0).all()), what + ": wrote past the caller's part buffer"
-        check_close(o.cpu().numpy(), oracle.mla_attn_ref(q, cache, sel, cnt, 1 / 16), what)
+        check_close(o.cpu().numpy(), oracle.mla_attn_ref(q, attended, sel, cnt, 1 / 16), what)
     st = C.c_int32(-1)
     assert L.gs_mla_attn_status(C.byref(st), None) == 0 and st.value == 0
