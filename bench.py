@@ -915,10 +915,11 @@ def run_profile_case(name: str) -> None:
         for i in range(4):
             pkg.mla_decode(q, pool, torch.from_numpy(lens_h.astype(np.int32)).to(dev), page_table=torch.from_numpy(pt).to(dev),
                            out=out, workspace=ws, max_seq_len=int(lens_h.max()))
-    elif name == "sparse":
+    elif name in ("sparse", "sparse_q8"):
         # the engine's sparse decode shape through the reference's entry point: 64 heads, 2052 listed rows per token
+        # (sparse_q8: over the Q8 cache)
         fn = pkg._lib.load().gs_mla_attn
-        _sparse_list_shape(torch, dev, fn, "profile", profile=True)
+        _sparse_list_shape(torch, dev, fn, "profile", profile=True, q8=name == "sparse_q8")
     else:
         S, Hh = 4096, 8
         Q, K, V = (torch.randn((S, Hh, 256), device=dev).half() for _ in range(3))
@@ -939,7 +940,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the 128K / paged / prefill extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["decode32k", "decode128k", "paged", "prefill", "sparse"],
+    ap.add_argument("--profile-case", default=None, choices=["decode32k", "decode128k", "paged", "prefill", "sparse", "sparse_q8"],
                     help="run a handful of eager launches of one kernel on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.warmup < 3:
