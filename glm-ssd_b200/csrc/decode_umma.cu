@@ -791,7 +791,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_decode_umma(const __grid_consta
             // zeros.  Done for the segment's first tile before its scores are awaited and for every further tile right
             // after the probabilities of the tile before are handed over, so that it runs beside that tile's P.V.
             // (Measured on 2052-row lists, 64 heads, T = 1 / 2 / 256: 24.9 / 53.4 / 473 us this way; 26.7 / 66.7 / 684 us
-            // with the three issuing warps widening instead - fewer threads, two more barriers, and their MMAs late.)
+            // with the three issuing warps widening instead - fewer threads, two more barriers, and their MMAs late;
+            // 24.2 / 55.1 / 484 us with one f16 stage filled from a ring of three stand-alone raw buffers - the copies
+            // then never wait for a stage, but widening, scores, softmax and P.V of consecutive tiles no longer
+            // overlap: the chain of hand-overs per tile, not the copies, is what the time follows.)
             auto widen_tile = [&](uint32_t i, int jj) {
                 const int s = i & 1;
                 (void) mbar_wait(&B.kv_raw[s], (i >> 1) & 1, abort_flag, status_w, ST_SOFTMAX);
